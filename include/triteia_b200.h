@@ -1,0 +1,156 @@
+/*
+ * triteia_b200 — C ABI of the B200 (sm_100a) indexed low-precision delta matmul library.
+ *
+ * Every entry point takes raw DEVICE pointers, plain integers and a CUDA stream handle
+ * (cudaStream_t passed as void*), returns an int status (0 = ok) and allocates nothing:
+ * outputs, workspaces and scratch buffers are owned by the caller, exactly as in the
+ * reference, whose launchers these functions replace.  Citations name files of the
+ * reference project (eth-easl/triteia).
+ *
+ * Tensor conventions (K = input features, N = output features, T = tokens, D = deltas):
+ *   x / A      fp16 [T, K] row-major
+ *   qweight    int32 [K/32, 2N]        (stacked: [D, K/32, 2N])
+ *   meta       int16 [N, K/16]         (stacked: [D, N, K/16])
+ *   scales     fp16 [G, N], G = 1 (per output channel) or K/128 (per group of 128 K),
+ *              stacked [D, G, N]; `groupsize` below is -1 or 128 (dense-K units)
+ *   y / C      fp16 [T, N] row-major
+ */
+#ifndef TRITEIA_B200_H_
+#define TRITEIA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes.  1 and 2 keep the reference's values (csrc/ops/marlin_nm.cu:39-40). */
+#define TRB_OK 0
+#define TRB_ERR_PROB_SHAPE 1   /* problem shape not supported (N % 128, K % 128, group size) */
+#define TRB_ERR_KERN_SHAPE 2   /* no kernel instantiation for the request */
+#define TRB_ERR_BAD_ARG 3      /* null pointer, misaligned pointer, negative size */
+#define TRB_ERR_CUDA 4         /* a CUDA runtime / driver call failed */
+#define TRB_ERR_TIMEOUT 5      /* a bounded device-side wait expired (see trb_device_status) */
+#define TRB_ERR_SCRATCH 6      /* caller-provided scratch buffer too small */
+
+/* dtype tags for the LoRA entry points */
+#define TRB_F16 0
+#define TRB_BF16 1
+
+int trb_version(void);
+const char* trb_status_string(int status);
+
+/* Reads and clears the device-side error word of device `dev` (synchronises `dev`).
+ * 0 = no kernel reported a problem since the last call; TRB_ERR_TIMEOUT = a bounded wait
+ * inside a kernel expired and that launch's output is invalid.
+ * No counterpart in the reference (its device code spins without bound,
+ * csrc/ops/common/mem.h:112-124). */
+int trb_device_status(int dev, int* status_out);
+
+/* C[T,N] = A[T,K] @ dequant(B, meta, s).  Overwrites C.
+ * Replaces marlin::marlin_cuda_2_4 (csrc/ops/marlin_nm.cu:42-119), same argument order:
+ * prob_m = N (output features), prob_n = T (tokens), prob_k = K.  `groupsize` is in dense-K
+ * units here (-1 or 128).  `workspace`, thread_k, thread_m, sms (limits the CTA count when
+ * > 0) and max_par are accepted for call compatibility; workspace is not touched. */
+int trb_mul_2_4(const void* A, const void* B, const void* meta, void* C, const void* s,
+                int prob_m, int prob_n, int prob_k, void* workspace, int groupsize, int dev,
+                void* stream, int thread_k, int thread_m, int sms, int max_par);
+
+/* Selective batched matmul over R segments: for r < prob_r,
+ *   C[starts[r] : starts[r]+counts[r]] = A[same rows] @ dequant(B[indices[r]], ...).
+ * Rows of C outside every segment are not written.  indices/starts/counts: int32 [R] on the
+ * device.  Replaces triteia::triteia_cuda_sbmm_2_4 (csrc/ops/triteia_nm_sbmm.cu:809-847),
+ * same argument order (prob_m = N, prob_n = T, prob_k = K, prob_r = R).  Unlike the
+ * reference, per-group scales are honoured and all segments run concurrently in ONE launch. */
+int trb_sbmm_2_4(const void* A, const void* B, const void* meta, void* C, const void* s,
+                 const void* indices, const void* starts, const void* counts, int prob_m,
+                 int prob_n, int prob_k, int prob_r, void* workspace, int groupsize, int dev,
+                 void* stream, int thread_k, int thread_m, int sms, int max_par);
+
+/* One weight per request: C[b, 0, :] = A[b, 0, :] @ dequant(B[b], meta[b], s[b]), b < prob_n.
+ * Replaces triteia::triteia_cuda_bmm_2_4 (csrc/ops/triteia_nm_bmm.cu:760-834). */
+int trb_bmm_2_4(const void* A, const void* B, const void* meta, void* C, const void* s,
+                int prob_m, int prob_n, int prob_k, void* workspace, int groupsize, int dev,
+                void* stream, int thread_k, int thread_m, int sms, int max_par);
+
+/* Token router: groups T tokens by delta id (stable, id -1 first) and builds the tile work
+ * list that the grouped kernel consumes.  Replaces the torch prologue of
+ * triteia/python/ops/matmul/sbmm.py:94-123 (unique_consecutive + cumsum + 3 host syncs) with
+ * one launch and no host synchronisation; indices may be in ANY order.
+ *   indices   int32 [T]; id = indices[t] - index_offset selects the delta, ids outside
+ *             [0, num_deltas) (this includes -1) mean "no delta for this token"
+ *   perm      int32 [T]   out: token positions in sorted order
+ *   seg_delta/seg_start/seg_count int32 [min(T, num_deltas)] out: one entry per distinct
+ *             delta id >= 0 in increasing id order; start/count index the SORTED order
+ *   tile_delta/tile_start/tile_count int32 [trb_route_max_tiles(T, num_deltas, tile_tokens)]
+ *             out: segments cut into tiles of at most tile_tokens tokens
+ *   counters  int32 [4] out: {R, number of tiles, number of tokens with id -1,
+ *             number of raw indices < -1 or >= index_offset + num_deltas}
+ * Any of perm / seg_* / tile_* may be NULL to skip that output.  T <= 65536,
+ * num_deltas <= 8191. */
+int trb_route(const void* indices, int num_tokens, int num_deltas, int tile_tokens,
+              int index_offset, void* perm, void* seg_delta, void* seg_start, void* seg_count, void* tile_delta,
+              void* tile_start, void* tile_count, void* counters, int dev, void* stream);
+int trb_route_max_tiles(int num_tokens, int num_deltas, int tile_tokens);
+
+/* Fused indexed delta matmul: y[t] (+)= x[t] @ dequant(delta[indices[t] - index_offset]) for
+ * indices[t] - index_offset in [0, num_deltas); other tokens count as "index -1".
+ * Router + row gather + grouped kernel on `stream`, no host synchronisation; indices in any
+ * order.  accumulate != 0: y[t] += ...  (rows with index -1 untouched); accumulate == 0:
+ * rows with index >= 0 are overwritten, rows with index -1 are set to zero.
+ * Stands for the body of sbmm_4bit_2_4_native (triteia/python/ops/matmul/sbmm.py:89-142)
+ * after its base GEMM.  `scratch` must hold trb_sbmm_indexed_scratch_bytes(T, K, D) bytes
+ * (mirrors sgmv_tmp_size, csrc/ops/sgmv.cuh:48-52). */
+size_t trb_sbmm_indexed_scratch_bytes(int num_tokens, int prob_k, int num_deltas);
+int trb_sbmm_indexed(const void* x, const void* qweights, const void* metas, const void* scales,
+                     const void* indices, void* y, int num_tokens, int prob_m, int prob_k,
+                     int num_deltas, int index_offset, int groupsize, int accumulate,
+                     void* scratch, size_t scratch_bytes, int dev, void* stream);
+
+/* Dense fp16 weight [K, N] from a packed delta (W = fp16(level) * fp16(scale), rounded once).
+ * The on-GPU statement of the format; bit-exact against the CPU decoder.  No counterpart
+ * kernel in the reference (its decoder is torch code,
+ * triteia/python/ops/utils/sparsity.py:297-394). */
+int trb_unpack_2_4(const void* B, const void* meta, const void* s, void* w_out, int prob_m,
+                   int prob_k, int groupsize, int dev, void* stream);
+
+/* BGMV: Y[b, :] += scale * W[indices[b], layer_idx] @ X[b, :], W [M, L, h_out, h_in]
+ * contiguous, indices int64 [B].  Replaces bgmv_kernel<feat_in, feat_out, T>
+ * (csrc/ops/bgmv_config.h:3-7, csrc/ops/bgmv_impl.cuh:186-207); any h_in, h_out that are
+ * multiples of 8 and < 65536 are accepted, and the launch goes to `stream` (the reference
+ * always uses the legacy default stream, bgmv_impl.cuh:198-205). */
+int trb_bgmv(void* Y, const void* X, const void* W, const void* indices, int batch, int h_in,
+             int h_out, int num_layers, int layer_idx, float scale, int dtype, int dev,
+             void* stream);
+
+/* Fused LoRA for decode: y[b] += scale * (x[b] @ A[idx]) @ B[idx] in ONE launch, the rank-r
+ * intermediate kept on chip.  wa_t [M, L, r, h1], wb_t [M, L, h2, r] (the layouts
+ * add_lora_bgmv takes, triteia/python/capi/punica.py:34-68); indices int64 [B], a negative
+ * index skips the row.  r <= 64. */
+int trb_lora_bgmv_fused(void* y, const void* x, const void* wa_t, const void* wb_t,
+                        const void* indices, int batch, int h1, int h2, int rank, int num_layers,
+                        int layer_idx, float scale, int dtype, int dev, void* stream);
+
+/* Indexed LoRA on the layouts the Python ops take: y[b] += scale * (x[b] @ A[id]) @ B[id] with
+ * A [M, h1, r], B [M, r, h2], id = indices[b] (int32, or int64 when index_is_64bit); ids outside
+ * [0, num_adapters) skip the row, so one index vector can address adapters and deltas.  Stands
+ * for lora_bgmv / the LoRA branch of ldmm (triteia/python/ops/matmul/lora.py:22-48,
+ * triteia/python/ops/matmul/ldmm.py:86-107) without their per-call transpose of every adapter
+ * and without gather / scatter of the token rows. */
+int trb_lora_indexed(void* y, const void* x, const void* wa, const void* wb, const void* indices,
+                     int index_is_64bit, int batch, int h1, int h2, int rank, int num_adapters,
+                     float scale, int dtype, int dev, void* stream);
+
+/* SGMV: y[s[i]:s[i+1]] += x[s[i]:s[i+1]] @ w[i][layer_idx], w[i] -> [L, d_in, d_out] row-major,
+ * w: device array of num_problems device pointers, s int32 [num_problems + 1].
+ * Replaces sgmv<T> (csrc/ops/sgmv.h:6-9, csrc/ops/sgmv.cuh:61-174).  `tmp` is accepted for call
+ * compatibility (trb_sgmv_tmp_size bytes, as csrc/ops/sgmv.cuh:48-52) and not touched. */
+size_t trb_sgmv_tmp_size(int num_problems);
+int trb_sgmv(void* y, const void* x, const void* w, const void* s, void* tmp, int num_problems,
+             int d_in, int d_out, int layer_idx, int dtype, int dev, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRITEIA_B200_H_ */

@@ -1,0 +1,432 @@
+"""GPU parity: every operator of the path, called through the C ABI (ctypes shims of
+triteia_b200), against the CPU oracle on the same seeded inputs.
+
+Bars: bit-exact for routing, tile work lists and weight / metadata unpacking; for fp16 outputs
+max relative error per output row <= 1e-2 against the fp32 dequantise-then-matmul oracle
+(max_n |y - ref| / max_n |ref|), plus the reference's own metric mean|y - ref| / mean|ref|
+< 0.002 where its tests use it (tests/ops/test_matmul.py:18-22, tests/ops/test_sbmm.py:47-61).
+"""
+import zlib
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import delta_format as fmt
+from oracle import ops as oracle
+
+pytestmark = pytest.mark.gpu
+
+ROW_TOL = 1e-2
+MEAN_TOL = 2e-3
+
+
+def _ops():
+    import triteia_b200.ops as ops
+    return ops
+
+
+def _lib():
+    from triteia_b200 import _lib
+    return _lib
+
+
+def check(y, ref, mean_tol=MEAN_TOL):
+    y = y.float().cpu().numpy()
+    assert np.isfinite(y).all()
+    err = oracle.row_rel_err(y, ref)
+    assert err.max() <= ROW_TOL, f"row rel err {err.max():.4g} (row {err.argmax()})"
+    if mean_tol is not None and np.abs(ref).mean() > 0:
+        assert oracle.mean_rel_err(y, ref) < mean_tol
+
+
+def packed(n_out, k_in, groupsize, seed, num=None, dev="cuda"):
+    ops = _ops()
+    qs, metas, ss = ops.random_packed_deltas(num or 1, k_in, n_out, groupsize=groupsize, device=dev, seed=seed,
+                                              scale_lo=0.005, scale_hi=0.02)
+    if num is None:
+        return qs[0], metas[0], ss[0]
+    return qs, metas, ss
+
+
+# ------------------------------------------------------------------ unpack (bit-exact)
+@pytest.mark.parametrize("name", ["pack_a", "pack_b", "pack_c"])
+def test_unpack_golden_bit_exact(cuda, golden, name):
+    L = _lib()
+    q = torch.from_numpy(golden[f"{name}_q"]).to(cuda)
+    meta = torch.from_numpy(golden[f"{name}_meta"]).to(cuda)
+    s = torch.from_numpy(golden[f"{name}_s"]).to(cuda)
+    k, n = q.shape[0] * 32, q.shape[1] // 2
+    w = torch.empty(k, n, dtype=torch.float16, device=cuda)
+    L.check(L.lib.trb_unpack_2_4(L.ptr(q), L.ptr(meta), L.ptr(s), L.ptr(w), n, k, -1, 0, L.stream_of(w)), "unpack")
+    ref = fmt.dequantize(golden[f"{name}_q"], golden[f"{name}_meta"], golden[f"{name}_s"])
+    assert np.array_equal(w.cpu().numpy().view(np.uint16), ref.view(np.uint16))
+    assert np.array_equal(w.cpu().numpy(), golden[f"{name}_uncompress"])
+
+
+@pytest.mark.parametrize("groupsize", [-1, 128])
+def test_unpack_random_bit_exact(cuda, groupsize):
+    L = _lib()
+    q, meta, s = packed(512, 384, groupsize, seed=5)
+    w = torch.empty(384, 512, dtype=torch.float16, device=cuda)
+    L.check(L.lib.trb_unpack_2_4(L.ptr(q), L.ptr(meta), L.ptr(s), L.ptr(w), 512, 384, groupsize, 0, L.stream_of(w)),
+            "unpack")
+    ref = fmt.dequantize(q.cpu().numpy(), meta.cpu().numpy(), s.cpu().numpy())
+    assert np.array_equal(w.cpu().numpy().view(np.uint16), ref.view(np.uint16))
+
+
+# ------------------------------------------------------------------ single matmul
+@pytest.mark.parametrize("groupsize", [-1, 128])
+@pytest.mark.parametrize("tokens", [1, 3, 8, 9, 16, 17, 31, 33, 64, 65, 130])
+def test_matmul_small(cuda, tokens, groupsize):
+    ops = _ops()
+    q, meta, s = packed(256, 384, groupsize, seed=tokens)
+    x = torch.randn(tokens, 384, dtype=torch.float16, device=cuda, generator=torch.Generator(cuda).manual_seed(tokens))
+    y = ops.matmul_4bit_2_4(q, x, meta, s)
+    assert y.shape == (tokens, 256) and y.dtype == torch.float16
+    check(y, oracle.matmul_2_4(q.cpu().numpy(), x.cpu().numpy(), meta.cpu().numpy(), s.cpu().numpy()))
+
+
+@pytest.mark.parametrize("name", ["pack_a", "pack_b", "pack_c"])
+def test_matmul_reference_packed_tensors(cuda, golden, name):
+    """Tensors produced by the reference's packer; oracle = fp32 matmul on its fp16 `uncompress`."""
+    ops = _ops()
+    q = torch.from_numpy(golden[f"{name}_q"]).to(cuda)
+    meta = torch.from_numpy(golden[f"{name}_meta"]).to(cuda)
+    s = torch.from_numpy(golden[f"{name}_s"]).to(cuda)
+    k = q.shape[0] * 32
+    x = torch.randn(16, k, dtype=torch.float16, device=cuda, generator=torch.Generator(cuda).manual_seed(1))
+    y = ops.matmul_4bit_2_4(q, x, meta, s)
+    ref = x.float().cpu().numpy() @ golden[f"{name}_uncompress"].astype(np.float32)
+    check(y, ref)
+
+
+def test_matmul_plumbing_config(cuda):
+    """16 x 4096 x 4096, per-channel scales U(0.001, 0.01): the CPU-runnable benchmark config."""
+    ops = _ops()
+    qs, metas, ss = ops.random_packed_deltas(1, 4096, 4096, device=cuda, seed=0)
+    x = torch.randn(16, 4096, dtype=torch.float16, device=cuda, generator=torch.Generator(cuda).manual_seed(0))
+    y = ops.matmul_4bit_2_4(qs[0], x, metas[0], ss[0])
+    y2 = ops.matmul_4bit_2_4(qs[0], x, metas[0], ss[0])
+    assert torch.equal(y, y2)  # deterministic reduction order
+    check(y, oracle.matmul_2_4(qs[0].cpu().numpy(), x.cpu().numpy(), metas[0].cpu().numpy(), ss[0].cpu().numpy()))
+
+
+def test_matmul_leading_dims_and_module(cuda):
+    ops = _ops()
+    from triteia_b200.nn import sparse_low_precision_linear
+
+    torch.manual_seed(3)
+    unc, q, s, meta = ops.gen_sparse_quant4_NT(256, 256, device=cuda)
+    x = torch.randn(2, 5, 256, dtype=torch.float16, device=cuda)
+    y = ops.matmul_4bit_2_4(q, x, meta, s)
+    assert y.shape == (2, 5, 256)
+    ref = x.float().cpu().numpy().reshape(10, 256) @ unc.float().cpu().numpy()
+    check(y.reshape(10, 256), ref)
+    layer = sparse_low_precision_linear(256, 256).to(cuda)
+    layer.pack(unc, s)
+    assert torch.equal(layer.qweight, q) and torch.equal(layer.meta, meta)
+    check(layer(x).reshape(10, 256), ref)
+
+
+def test_matmul_errors(cuda):
+    ops = _ops()
+    from triteia_b200.capi import mul_2_4
+
+    q, meta, s = packed(256, 128, -1, seed=1)
+    x = torch.randn(4, 128, dtype=torch.float16, device=cuda)
+    C = torch.empty(4, 256, dtype=torch.float16, device=cuda)
+    with pytest.raises(RuntimeError, match="workspace"):
+        mul_2_4(x, q, meta, C, s, torch.zeros(1, dtype=torch.int32, device=cuda))
+    with pytest.raises(RuntimeError, match="contiguous"):
+        mul_2_4(x.t().contiguous().t(), q, meta, C, s, torch.zeros(64, dtype=torch.int32, device=cuda))
+    # K not a multiple of 128: problem-shape error with the reference's message
+    with pytest.raises(RuntimeError, match="not compatible"):
+        mul_2_4(x[:, :64].contiguous(), q[:2], meta[:, :4].contiguous(), C, s,
+                torch.zeros(64, dtype=torch.int32, device=cuda))
+    # zero tokens: nothing to do
+    y0 = ops.matmul_4bit_2_4(q, x[:0], meta, s)
+    assert y0.shape == (0, 256)
+
+
+# ------------------------------------------------------------------ router (bit-exact)
+def run_route(idx_np, num_deltas, tile, offset=0):
+    L = _lib()
+    dev = torch.device("cuda:0")
+    T = len(idx_np)
+    idx = torch.from_numpy(np.asarray(idx_np, dtype=np.int32)).to(dev)
+    max_tiles = L.lib.trb_route_max_tiles(T, num_deltas, tile)
+    nseg = max(1, min(T, num_deltas))
+    perm = torch.full((max(T, 1),), -7, dtype=torch.int32, device=dev)
+    seg = [torch.full((nseg,), -7, dtype=torch.int32, device=dev) for _ in range(3)]
+    til = [torch.full((max(max_tiles, 1),), -7, dtype=torch.int32, device=dev) for _ in range(3)]
+    cnt = torch.full((4,), -7, dtype=torch.int32, device=dev)
+    L.check(L.lib.trb_route(L.ptr(idx), T, num_deltas, tile, offset, L.ptr(perm), *[L.ptr(t) for t in seg],
+                            *[L.ptr(t) for t in til], L.ptr(cnt), 0, L.stream_of(cnt)), "route")
+    c = cnt.cpu().numpy()
+    R, NT = int(c[0]), int(c[1])
+    return (perm.cpu().numpy()[:T], [t.cpu().numpy()[:R] for t in seg], [t.cpu().numpy()[:NT] for t in til], c)
+
+
+def oracle_tiles(u, st, c, tile):
+    td, ts, tc = [], [], []
+    for d, a, n in zip(u, st, c):
+        for off in range(0, n, tile):
+            td.append(d); ts.append(a + off); tc.append(min(tile, n - off))
+    return np.array(td, np.int32), np.array(ts, np.int32), np.array(tc, np.int32)
+
+
+ROUTE_CASES = {
+    "sorted": lambda r: np.sort(r.integers(-1, 64, 128)),
+    "shuffled": lambda r: r.integers(-1, 64, 128),
+    "all_base": lambda r: np.full(37, -1),
+    "one_delta": lambda r: np.full(50, 3),
+    "single_token": lambda r: np.array([5]),
+    "empty": lambda r: np.zeros(0, dtype=np.int64),
+    "distinct": lambda r: r.permutation(64),
+    "ragged_big": lambda r: r.integers(-1, 1000, 5000),
+    "many_tokens": lambda r: r.integers(-1, 32, 8192),
+    "zipf": lambda r: np.minimum(r.zipf(1.5, 512) - 1, 127),
+}
+
+
+@pytest.mark.parametrize("case", list(ROUTE_CASES))
+@pytest.mark.parametrize("tile", [8, 64])
+def test_route_bit_exact(cuda, case, tile):
+    rng = np.random.default_rng(zlib.crc32(case.encode()) % 1000)
+    idx = ROUTE_CASES[case](rng).astype(np.int32)
+    D = 1024 if case == "ragged_big" else 128
+    perm, seg, til, cnt = run_route(idx, D, tile)
+    operm, u, st, c = oracle.route_any(idx)
+    assert np.array_equal(perm, operm)
+    assert np.array_equal(seg[0], u) and np.array_equal(seg[1], st) and np.array_equal(seg[2], c)
+    td, ts, tc = oracle_tiles(u, st, c, tile)
+    assert np.array_equal(til[0], td) and np.array_equal(til[1], ts) and np.array_equal(til[2], tc)
+    assert cnt[2] == (idx == -1).sum() and cnt[3] == 0
+
+
+def test_route_offset_and_out_of_range(cuda):
+    idx = np.array([-1, 0, 9, 4, 5, 5, 12, 4, 3, -5], dtype=np.int32)   # deltas are ids 4..7 (offset 4, D = 4)
+    perm, seg, til, cnt = run_route(idx, 4, 8, offset=4)
+    mapped = np.where((idx - 4 >= 0) & (idx - 4 < 4), idx - 4, -1)
+    operm, u, st, c = oracle.route_any(mapped)
+    assert np.array_equal(perm, operm) and np.array_equal(seg[0], u) and np.array_equal(seg[2], c)
+    assert cnt[3] == 3  # 9, 12 and -5 are outside [-1, offset + D)
+
+
+# ------------------------------------------------------------------ sbmm
+def sbmm_inputs(T, D, K, N, groupsize, seed, base=False, sort=True, frac_base=0.1):
+    dev = torch.device("cuda:0")
+    rng = np.random.default_rng(seed)
+    qs, metas, ss = packed(N, K, groupsize, seed=seed, num=D)
+    x = torch.randn(T, K, dtype=torch.float16, device=dev, generator=torch.Generator(dev).manual_seed(seed))
+    idx = rng.integers(0, D, T)
+    idx[rng.random(T) < frac_base] = -1
+    if sort:
+        idx = np.sort(idx)
+    bw = None
+    if base:
+        bw = (torch.randn(N, K, device=dev, generator=torch.Generator(dev).manual_seed(seed + 1)) * 0.02).half()
+    return qs, metas, ss, x, torch.from_numpy(idx.astype(np.int32)).to(dev), bw
+
+
+def sbmm_ref(qs, metas, ss, x, idx, bw):
+    return oracle.sbmm(qs.cpu().numpy(), x.cpu().numpy(), metas.cpu().numpy(), ss.cpu().numpy(), idx.cpu().numpy(),
+                       None if bw is None else bw.cpu().numpy())
+
+
+@pytest.mark.parametrize("groupsize", [-1, 128])
+@pytest.mark.parametrize("sort", [True, False])
+@pytest.mark.parametrize("base", [False, True])
+def test_sbmm_native(cuda, groupsize, sort, base):
+    ops = _ops()
+    qs, metas, ss, x, idx, bw = sbmm_inputs(40, 6, 256, 512, groupsize, seed=7, base=base, sort=sort)
+    y = ops.sbmm_4bit_2_4_native(qs, x, metas, ss, idx, base_weight=bw)
+    ref = sbmm_ref(qs, metas, ss, x, idx, bw)
+    check(y, ref, mean_tol=None if base else MEAN_TOL)
+    if not base:
+        assert torch.all(y[idx == -1] == 0)
+    y2 = ops.sbmm_4bit_2_4_native(qs, x, metas, ss, idx, base_weight=bw)
+    assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("variant", ["forloop", "multilaunch", "segments"])
+def test_sbmm_reference_call_sequences(cuda, variant):
+    ops = _ops()
+    qs, metas, ss, x, idx, bw = sbmm_inputs(30, 5, 256, 256, -1, seed=9)
+    fn = {"forloop": ops.sbmm_4bit_2_4_forloop, "multilaunch": ops.sbmm_4bit_2_4_multilaunch,
+          "segments": ops.sbmm_4bit_2_4_segments}[variant]
+    check(fn(qs, x, metas, ss, idx), sbmm_ref(qs, metas, ss, x, idx, None))
+
+
+def test_sbmm_reference_test_shape_uniform(cuda):
+    """("uniform", 10 requests, 5 models, 256 x 512), sorted — tests/ops/test_sbmm.py:15-31."""
+    ops = _ops()
+    qs, metas, ss, x, idx, _ = sbmm_inputs(10, 5, 256, 512, -1, seed=11)
+    check(ops.sbmm_4bit_2_4_native(qs, x, metas, ss, idx), sbmm_ref(qs, metas, ss, x, idx, None))
+
+
+@pytest.mark.parametrize("case", ["all_base", "one_delta", "one_token", "hot_delta", "every_delta_once"])
+def test_sbmm_edge_cases(cuda, case):
+    ops = _ops()
+    qs, metas, ss, x, idx, _ = sbmm_inputs(96, 8, 128, 256, -1, seed=13, sort=False)
+    if case == "all_base":
+        idx[:] = -1
+    elif case == "one_delta":
+        idx[:] = 5
+    elif case == "one_token":
+        x, idx = x[:1].contiguous(), idx[:1]
+    elif case == "hot_delta":
+        idx[:80] = 2          # 80 tokens of one delta: several token tiles
+    elif case == "every_delta_once":
+        x, idx = x[:8].contiguous(), torch.arange(8, dtype=torch.int32, device=cuda)
+    y = ops.sbmm_4bit_2_4_native(qs, x, metas, ss, idx)
+    check(y, sbmm_ref(qs, metas, ss, x, idx, None), mean_tol=None)
+
+
+def test_sbmm_decode_config_shape(cuda):
+    """BASELINE sbmm config at reduced delta count: 128 tokens, 4096 x 4096, group 128, 10% base."""
+    ops = _ops()
+    qs, metas, ss, x, idx, _ = sbmm_inputs(128, 8, 4096, 4096, 128, seed=17, sort=False)
+    y = ops.sbmm_4bit_2_4_native(qs, x, metas, ss, idx)
+    check(y, sbmm_ref(qs, metas, ss, x, idx, None))
+
+
+def test_sbmm_linearity_full_size(cuda):
+    """Size-independent properties at the full 64-delta configuration: f(2x) == 2 f(x) bit for bit
+    (scaling by 2 is exact in fp16 and fp32 outside the fp16 subnormal range of the output), and
+    permuting the tokens permutes the rows."""
+    ops = _ops()
+    qs, metas, ss, x, idx, _ = sbmm_inputs(128, 64, 4096, 4096, 128, seed=19, sort=False)
+    y = ops.sbmm_4bit_2_4_native(qs, x, metas, ss, idx)
+    y2 = ops.sbmm_4bit_2_4_native(qs, (x * 2).contiguous(), metas, ss, idx)
+    normal = y.abs() >= 1e-3          # fp16 results below 2**-14 round on a fixed grid, not a relative one
+    assert torch.equal(y2[normal], (y * 2)[normal])
+    assert torch.allclose(y2.float(), 2 * y.float(), rtol=0, atol=2e-7)
+    p = torch.randperm(128, device=cuda, generator=torch.Generator(cuda).manual_seed(1))
+    yp = ops.sbmm_4bit_2_4_native(qs, x[p].contiguous(), metas, ss, idx[p].contiguous())
+    assert torch.equal(yp, y[p])
+
+
+# ------------------------------------------------------------------ bmm
+@pytest.mark.parametrize("b", [1, 4, 16])
+def test_bmm(cuda, b):
+    ops = _ops()
+    qs, metas, ss = packed(256, 512, -1, seed=b, num=b)
+    x = torch.randn(b, 1, 512, dtype=torch.float16, device=cuda, generator=torch.Generator(cuda).manual_seed(b))
+    y = ops.bmm_4bit_2_4(qs, x, metas, ss)
+    assert y.shape == (b, 1, 256)
+    ref = np.stack([oracle.matmul_2_4(qs[i].cpu().numpy(), x[i].cpu().numpy(), metas[i].cpu().numpy(),
+                                      ss[i].cpu().numpy()) for i in range(b)])
+    check(y.reshape(b, 256), ref.reshape(b, 256), mean_tol=1e-3)
+    check(ops.bmm_4bit_2_4_forloop(qs, x, metas, ss).reshape(b, 256), ref.reshape(b, 256), mean_tol=1e-3)
+
+
+# ------------------------------------------------------------------ LoRA
+def lora_inputs(T, M, H1, H2, r, seed, dtype=torch.float16):
+    dev = torch.device("cuda:0")
+    g = torch.Generator(dev).manual_seed(seed)
+    A = (torch.randn(M, H1, r, device=dev, generator=g) / H1 ** 0.5).to(dtype)
+    B = (torch.randn(M, r, H2, device=dev, generator=g) / r ** 0.5).to(dtype)
+    x = torch.randn(T, H1, device=dev, generator=g).to(dtype)
+    idx = np.sort(np.random.default_rng(seed).integers(-1, M, T)).astype(np.int32)
+    return A, B, x, torch.from_numpy(idx).to(dev)
+
+
+def lora_ref(A, B, x, idx, scale=1.0):
+    return oracle.lora(A.float().cpu().numpy(), B.float().cpu().numpy(), x.float().cpu().numpy(), idx.cpu().numpy(),
+                       scale=scale)
+
+
+@pytest.mark.parametrize("rank", [8, 16, 32, 64])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_lora_bgmv(cuda, rank, dtype):
+    ops = _ops()
+    A, B, x, idx = lora_inputs(33, 5, 768, 768, rank, seed=rank, dtype=dtype)
+    y = ops.lora_bgmv(A, B, x, idx, scale=0.5)
+    ref = lora_ref(A, B, x, idx, 0.5)
+    tol = 1e-2 if dtype == torch.float16 else 3e-2
+    assert oracle.row_rel_err(y.float().cpu().numpy(), ref)[idx.cpu().numpy() >= 0].max() <= tol
+    assert torch.all(y[idx == -1] == 0)
+
+
+def test_lora_bgmv_capi_transposed_layouts(cuda):
+    """The two-launch BGMV of the reference API (shrink into fp16 tmp, then expand)."""
+    from triteia_b200.capi import add_lora_bgmv
+    from triteia_b200 import _lib as L
+
+    A, B, x, idx = lora_inputs(20, 4, 4096, 1024, 16, seed=2)
+    keep = idx >= 0
+    xk, ik = x[keep].contiguous(), idx[keep].long()
+    wa_t = A.transpose(1, 2).contiguous().unsqueeze(1)
+    wb_t = B.transpose(1, 2).contiguous().unsqueeze(1)
+    y = torch.zeros(xk.shape[0], 1024, dtype=torch.float16, device=cuda)
+    add_lora_bgmv(y, xk, wa_t, wb_t, ik, 0, 1.0)
+    ref = lora_ref(A, B, xk, ik)
+    check(y, ref, mean_tol=5e-3)
+    # fused single-launch variant on the same layouts
+    y2 = torch.zeros_like(y)
+    L.check(L.lib.trb_lora_bgmv_fused(L.ptr(y2), L.ptr(xk), L.ptr(wa_t), L.ptr(wb_t), L.ptr(ik), xk.shape[0], 4096,
+                                      1024, 16, 1, 0, 1.0, 0, 0, L.stream_of(y2)), "fused")
+    check(y2, ref, mean_tol=5e-3)
+
+
+@pytest.mark.parametrize("shape", [(768, 768), (256, 256), (4096, 1536)])
+def test_lora_sgmv(cuda, shape):
+    ops = _ops()
+    A, B, x, idx = lora_inputs(150, 6, shape[0], shape[1], 64, seed=4)
+    y = ops.lora_sgmv(A, B, x, idx)
+    check(y, lora_ref(A, B, x, idx), mean_tol=5e-3)
+
+
+def test_lora_golden(cuda, golden):
+    ops = _ops()
+    A, B = torch.from_numpy(golden["lora_A"]).to(cuda), torch.from_numpy(golden["lora_B"]).to(cuda)
+    x, idx = torch.from_numpy(golden["lora_x"]).to(cuda), torch.from_numpy(golden["lora_idx"]).to(cuda)
+    ref = oracle.lora(golden["lora_A"], golden["lora_B"], golden["lora_x"], golden["lora_idx"])
+    check(ops.lora_bgmv(A, B, x, idx), ref, mean_tol=5e-3)
+    check(ops.lora_sgmv(A, B, x, idx), ref, mean_tol=5e-3)
+
+
+# ------------------------------------------------------------------ ldmm
+@pytest.mark.parametrize("rank", [8, 16, 64])
+@pytest.mark.parametrize("base", [False, True])
+def test_ldmm(cuda, rank, base):
+    ops = _ops()
+    M, D, K, N, T = 5, 5, 768, 768, 60
+    qs, metas, ss = packed(N, K, -1, seed=rank, num=D)
+    A, B, x, _ = lora_inputs(T, M, K, N, rank, seed=rank)
+    idx = torch.from_numpy(np.random.default_rng(rank).integers(-1, M + D, T).astype(np.int32)).to(cuda)
+    bw = (torch.randn(N, K, device=cuda) * 0.02).half() if base else None
+    y = ops.ldmm(idx, x, A, B, qs, metas, ss, base_weight=bw)
+    ref = oracle.ldmm(idx.cpu().numpy(), x.cpu().numpy(), A.cpu().numpy(), B.cpu().numpy(), qs.cpu().numpy(),
+                      metas.cpu().numpy(), ss.cpu().numpy(), None if bw is None else bw.cpu().numpy())
+    check(y, ref, mean_tol=None)
+    yb = ops.baseline_ldmm(idx, x, A, B, qs, metas, ss, base_weight=bw)
+    check(yb, ref, mean_tol=None)
+    assert torch.allclose(y.float(), yb.float(), rtol=5e-3, atol=5e-3)  # tests/ops/test_ldmm.py:73-77
+
+
+def test_ldmm_golden_dispatch(cuda, golden):
+    ops = _ops()
+    t = lambda k: torch.from_numpy(golden[k]).to(cuda)
+    y = ops.ldmm(t("ldmm_idx"), t("ldmm_x"), t("lora_A"), t("lora_B"), t("sbmm_q"), t("sbmm_meta"), t("sbmm_s"))
+    ref = oracle.ldmm(golden["ldmm_idx"], golden["ldmm_x"], golden["lora_A"], golden["lora_B"], golden["sbmm_q"],
+                      golden["sbmm_meta"], golden["sbmm_s"])
+    check(y, ref, mean_tol=None)
+    assert oracle.row_rel_err(y.float().cpu().numpy(), golden["ldmm_y"].astype(np.float32)).max() < 2e-2
+
+
+def test_ldmm_float32_input_dtype(cuda):
+    ops = _ops()
+    qs, metas, ss = packed(256, 256, -1, seed=1, num=2)
+    A, B, x, _ = lora_inputs(9, 2, 256, 256, 16, seed=1)
+    idx = torch.tensor([0, 1, 2, 3, -1, 3, 0, 2, 1], dtype=torch.int32, device=cuda)
+    y = ops.ldmm(idx, x.float(), A, B, qs, metas, ss)
+    assert y.dtype == torch.float32
+
+
+def test_no_device_side_timeouts(cuda):
+    from triteia_b200 import _lib as L
+
+    assert L.device_status(0) == 0

@@ -1,0 +1,77 @@
+"""CPU, world_size 2 over gloo: the delta-sharding / token dispatch logic of triteia_b200.sharded
+(ownership rule, split sizes, permutations, combine) against an unsharded computation."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, case, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from triteia_b200 import sharded
+        from triteia_b200.ops.matmul.sbmm import sbmm_16bit_forloop
+
+        D, K, N, T = 6, 32, 16, 20
+        g = torch.Generator().manual_seed(0)
+        weights = torch.randn(D, K, N, generator=g)                       # every rank builds all, keeps its shard
+        mine = sharded.shard_ids(D, rank, world)
+        w_local = weights[mine]
+        gr = torch.Generator().manual_seed(100 + rank)
+        x = torch.randn(T, K, generator=gr)
+        if case == "mixed":
+            idx = torch.randint(-1, D, (T,), generator=gr, dtype=torch.int32)
+        elif case == "all_base":
+            idx = torch.full((T,), -1, dtype=torch.int32)
+        elif case == "one_owner":
+            idx = torch.full((T,), 1, dtype=torch.int32)                   # everything goes to rank 1
+        else:
+            idx = torch.randint(0, D, (T,), generator=gr, dtype=torch.int32)
+
+        def local_compute(rows, local_ids):
+            return sbmm_16bit_forloop(w_local, rows, local_ids)
+
+        y = sharded.sbmm_sharded(x, idx, local_compute, N)
+        ref = sbmm_16bit_forloop(weights, x, idx)
+        ok = torch.allclose(y, ref, rtol=1e-5, atol=1e-5)
+        plan = sharded.DispatchPlan(idx, world)
+        ok = ok and plan.n_send == int((idx >= 0).sum())
+        torch.save({"ok": bool(ok), "max_err": float((y - ref).abs().max())}, os.path.join(out_dir, f"r{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("case", ["mixed", "all_base", "one_owner", "no_base"])
+def test_sharded_dispatch_world2(tmp_path, case):
+    world = 2
+    mp.start_processes(_worker, args=(world, _free_port(), case, str(tmp_path)), nprocs=world, join=True,
+                       start_method="spawn")
+    for r in range(world):
+        res = torch.load(os.path.join(str(tmp_path), f"r{r}.pt"))
+        assert res["ok"], res
+
+
+def test_ownership_rule():
+    from triteia_b200 import sharded
+
+    ids = torch.arange(10)
+    assert sharded.owner_of(ids, 4).tolist() == [0, 1, 2, 3, 0, 1, 2, 3, 0, 1]
+    assert sharded.local_id_of(ids, 4).tolist() == [0, 0, 0, 0, 1, 1, 1, 1, 2, 2]
+    assert sharded.shard_ids(10, 1, 4) == [1, 5, 9]
+    for r in range(4):
+        for local, d in enumerate(sharded.shard_ids(10, r, 4)):
+            assert int(sharded.owner_of(torch.tensor(d), 4)) == r and int(sharded.local_id_of(torch.tensor(d), 4)) == local

@@ -1,0 +1,399 @@
+// Grouped 2:4-sparse int4 delta GEMM for decode-sized token tiles (HBM-bound regime).
+//
+// One persistent launch serves every (token segment, 64*SW-column stripe) work item of a batch:
+// a producer warp streams packed weights, 2:4 metadata, scales and the activation tile into a
+// ring of shared-memory stages with TMA (cp.async.bulk.tensor + mbarrier transaction counts),
+// eight consumer warps turn nibbles into fp16 in registers and issue 2:4-sparse tensor-core
+// MMAs with the weights as the sparse operand (output features on the MMA M dimension, tokens
+// on N).  Every delta is read from HBM once per token tile; no split-K across CTAs, no locks.
+//
+// The work done per (32-K slab, 64-column block) follows the packed format's own fragment
+// order (reference: triteia/python/ops/utils/sparsity.py:35-61 for the nibble order,
+// :134-161 for the metadata order; the consuming kernel in the reference is
+// triteia/csrc/ops/marlin.cuh:337-387): lane i owns words 4i..4i+3 of the block's 128 weight
+// words and metadata words i and 32+i of its 64 metadata words.
+#pragma once
+
+#include "common.cuh"
+
+namespace trb {
+
+constexpr int kMaxSegments = 2048;
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kGemmThreads = kConsumerThreads + 32;
+
+enum SegMode { kSegList = 0, kSegSingle = 1, kSegIdentity = 2 };
+
+struct GemmArgs {
+  const int* seg_delta;   // [n_seg] delta id per segment (kSegList)
+  const int* seg_start;   // [n_seg] first row of the segment in x / y
+  const int* seg_count;   // [n_seg] rows in the segment
+  const int* n_seg_ptr;   // device scalar with the segment count, or nullptr -> n_seg
+  int n_seg;
+  int mode;
+  int rows;               // rows of x and y
+  int N, K;
+  int num_deltas;
+  int grouped;            // 0: scales [D,1,N] applied in the epilogue; 1: [D,K/128,N]
+  const __half* scales;
+  __half* y;
+  const int* row_map;     // nullptr, or output row of each x row (scatter through the router's perm)
+  int accumulate;         // y += result instead of y = result
+};
+
+template <int NB_, int SW_, int KQ_, int KS_, int STAGES_>
+struct GemmCfg {
+  static constexpr int NB = NB_;          // token blocks of 8 per tile
+  static constexpr int SW = SW_;          // 64-column blocks per stripe
+  static constexpr int KQ = KQ_;          // warps sharing one column block (split over slabs)
+  static constexpr int KS = KS_;          // 32-K slabs per pipeline stage
+  static constexpr int STAGES = STAGES_;
+  static_assert(SW * KQ == kConsumerWarps, "eight consumer warps");
+  static_assert(KS % 4 == 0 && KS % KQ == 0 && KS % 2 == 0, "stage must hold whole scale groups");
+  static_assert((KS / KQ) <= 4 && 4 % (KS / KQ) == 0, "a warp's slabs of a stage share one scale group");
+  static constexpr int TT = NB * 8;                 // tokens per tile
+  static constexpr int QB = SW >= 2 ? 2 : 1;        // column blocks per weight TMA box
+  static constexpr int NQBOX = SW / QB;
+  static constexpr int NXBOX = KS / 2;              // 64-half boxes of activations per stage
+  static constexpr int X_BOX_BYTES = TT * 128;
+  static constexpr int X_BYTES = NXBOX * X_BOX_BYTES;
+  static constexpr int Q_BYTES = KS * SW * 512;
+  static constexpr int M_BYTES = KS * SW * 256;
+  static constexpr int S_BYTES = (KS / 4) * SW * 128;
+  static constexpr int X_OFF = 0;
+  static constexpr int Q_OFF = (X_BYTES + 1023) / 1024 * 1024;
+  static constexpr int M_OFF = Q_OFF + Q_BYTES;
+  static constexpr int S_OFF = M_OFF + M_BYTES;
+  static constexpr int STAGE_BYTES = (S_OFF + S_BYTES + 1023) / 1024 * 1024;
+  static constexpr int RED_FLOATS = (KQ - 1) * 16 * NB * SW * 32;
+  static constexpr int RED_OFF = STAGES * STAGE_BYTES;
+  static constexpr int PREFIX_OFF = RED_OFF + RED_FLOATS * 4;
+  static constexpr int BAR_OFF = PREFIX_OFF + (kMaxSegments + 2) * 4;
+  static constexpr int SMEM_BYTES = BAR_OFF + 2 * STAGES * 8 + 16;
+  static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;  // slack to align the base to 1 KiB
+};
+
+struct WorkItem {
+  int delta, row0, valid, col0;
+  bool ok;
+};
+
+// Tile t of the batch -> (segment, tile inside the segment); item = tile * n_stripes + stripe.
+template <class Cfg>
+__device__ __forceinline__ WorkItem decode_item(const GemmArgs& a, const int* prefix, int n_seg,
+                                                int n_stripes, int item) {
+  WorkItem w;
+  const int tile = item / n_stripes;
+  const int stripe = item - tile * n_stripes;
+  int seg, tin;
+  if (a.mode == kSegSingle) {
+    seg = 0;
+    tin = tile;
+  } else if (a.mode == kSegIdentity) {
+    seg = tile;
+    tin = 0;
+  } else {
+    int lo = 0, hi = n_seg;  // largest seg with prefix[seg] <= tile
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (prefix[mid] <= tile) lo = mid; else hi = mid;
+    }
+    seg = lo;
+    tin = tile - prefix[seg];
+  }
+  int delta, start, count;
+  if (a.mode == kSegSingle) {
+    delta = 0; start = 0; count = a.rows;
+  } else if (a.mode == kSegIdentity) {
+    delta = seg; start = seg; count = 1;
+  } else {
+    delta = a.seg_delta[seg]; start = a.seg_start[seg]; count = a.seg_count[seg];
+  }
+  w.delta = delta;
+  w.row0 = start + tin * Cfg::TT;
+  w.valid = min(Cfg::TT, count - tin * Cfg::TT);
+  w.col0 = stripe * Cfg::SW * 64;
+  // Never trust a list entry with the address arithmetic: bad entries are skipped.
+  w.ok = delta >= 0 && delta < a.num_deltas && start >= 0 && count >= 0 &&
+         start + count <= a.rows && w.valid > 0;
+  return w;
+}
+
+template <class Cfg>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_q,
+                  const __grid_constant__ CUtensorMap tm_m, const __grid_constant__ CUtensorMap tm_s,
+                  const GemmArgs a) {
+  constexpr int NB = Cfg::NB, SW = Cfg::SW, KQ = Cfg::KQ, KS = Cfg::KS, STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* red = reinterpret_cast<float*>(smem + Cfg::RED_OFF);
+  int* prefix = reinterpret_cast<int*>(smem + Cfg::PREFIX_OFF);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::BAR_OFF);
+  uint64_t* empty_bar = full_bar + STAGES;
+  volatile int* dead = reinterpret_cast<volatile int*>(empty_bar + STAGES);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  int n_seg = a.n_seg_ptr ? *a.n_seg_ptr : a.n_seg;
+  n_seg = max(0, min(n_seg, kMaxSegments));
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], kConsumerWarps);
+    }
+    *dead = 0;
+    fence_mbar_init();
+  }
+  // Tiles-per-segment prefix sums (list mode).  Warp 0 scans 32 segments per step.
+  int total_tiles;
+  if (a.mode == kSegList) {
+    if (warp == 0) {
+      int running = 0;
+      for (int base = 0; base < n_seg; base += 32) {
+        const int s = base + lane;
+        int c = 0;
+        if (s < n_seg) {
+          const int cnt = a.seg_count[s];
+          c = cnt > 0 ? (cnt + Cfg::TT - 1) / Cfg::TT : 0;
+        }
+        int inc = c;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int v = __shfl_up_sync(0xffffffffu, inc, o);
+          if (lane >= o) inc += v;
+        }
+        if (s < n_seg) prefix[s] = running + inc - c;
+        running += __shfl_sync(0xffffffffu, inc, 31);
+      }
+      if (lane == 0) prefix[n_seg] = running;
+    }
+    __syncthreads();
+    total_tiles = prefix[n_seg];
+  } else {
+    __syncthreads();
+    total_tiles = a.mode == kSegSingle ? (a.rows + Cfg::TT - 1) / Cfg::TT : a.rows;
+  }
+
+  const int n_stripes = (a.N + SW * 64 - 1) / (SW * 64);
+  const int n_items = total_tiles * n_stripes;
+  const int slabs = a.K / 32;
+  const int k_stages = (slabs + KS - 1) / KS;
+  const int groups = a.grouped ? a.K / 128 : 1;
+
+  if (warp == kConsumerWarps) {
+    // ------------------------------ producer ------------------------------
+    if (lane == 0) {
+      prefetch_tmap(&tm_x);
+      prefetch_tmap(&tm_q);
+      prefetch_tmap(&tm_m);
+      if (a.grouped) prefetch_tmap(&tm_s);
+      const uint64_t pol_w = policy_evict_first();
+      const uint64_t pol_x = policy_evict_last();
+      const uint32_t stage_tx = Cfg::X_BYTES + Cfg::Q_BYTES + Cfg::M_BYTES + (a.grouped ? Cfg::S_BYTES : 0);
+      int st = 0;
+      uint32_t phase = 0;
+      for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+        const WorkItem w = decode_item<Cfg>(a, prefix, n_seg, n_stripes, item);
+        if (!w.ok) continue;
+        for (int ks = 0; ks < k_stages; ++ks) {
+          mbar_wait(&empty_bar[st], phase ^ 1, dead);
+          uint8_t* sbase = smem + st * Cfg::STAGE_BYTES;
+          mbar_arrive_expect_tx(&full_bar[st], stage_tx);
+#pragma unroll
+          for (int b = 0; b < Cfg::NXBOX; ++b)
+            tma_load_2d_hint(sbase + Cfg::X_OFF + b * Cfg::X_BOX_BYTES, &tm_x, ks * KS * 32 + b * 64, w.row0,
+                             &full_bar[st], pol_x);
+          const int wrow = w.delta * slabs + ks * KS;
+#pragma unroll
+          for (int b = 0; b < Cfg::NQBOX; ++b) {
+            tma_load_2d_hint(sbase + Cfg::Q_OFF + b * (KS * Cfg::QB * 512), &tm_q,
+                             (w.col0 / 64 + b * Cfg::QB) * 128, wrow, &full_bar[st], pol_w);
+            tma_load_2d_hint(sbase + Cfg::M_OFF + b * (KS * Cfg::QB * 256), &tm_m,
+                             (w.col0 / 64 + b * Cfg::QB) * 64, wrow, &full_bar[st], pol_w);
+          }
+          if (a.grouped)
+            tma_load_2d_hint(sbase + Cfg::S_OFF, &tm_s, w.col0, w.delta * groups + ks * (KS / 4), &full_bar[st],
+                             pol_w);
+          if (++st == STAGES) { st = 0; phase ^= 1; }
+        }
+      }
+    }
+    return;
+  }
+
+  // ------------------------------ consumers ------------------------------
+  const int cb = warp / KQ;   // column block of the stripe
+  const int kq = warp % KQ;   // which share of each stage's slabs
+  const int g8 = lane >> 2;   // quad index: MMA row group / token inside a block of 8
+  const int m4 = lane & 3;
+  constexpr int SPW = KS / KQ;  // slabs per warp per stage
+
+  int st = 0;
+  uint32_t phase = 0;
+  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const WorkItem w = decode_item<Cfg>(a, prefix, n_seg, n_stripes, item);
+    if (!w.ok) continue;
+    const int nbv = (w.valid + 7) >> 3;
+    const bool col_ok = w.col0 + cb * 64 < a.N;
+
+    float acc[4][NB][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[j][nb][c] = 0.f;
+
+    for (int ks = 0; ks < k_stages; ++ks) {
+      mbar_wait(&full_bar[st], phase, dead);
+      const uint8_t* sbase = smem + st * Cfg::STAGE_BYTES;
+      const uint32_t x_s = smem_u32(sbase + Cfg::X_OFF);
+      uint4 sc = make_uint4(0, 0, 0, 0);
+      if (a.grouped) {
+        const int grp = (kq * SPW) / 4;
+        sc = *reinterpret_cast<const uint4*>(sbase + Cfg::S_OFF + grp * (SW * 128) + cb * 128 + g8 * 16);
+      }
+#pragma unroll
+      for (int i = 0; i < SPW; ++i) {
+        const int slab = kq * SPW + i;
+        if (ks * KS + slab < slabs && col_ok) {
+          const int box = cb / Cfg::QB, within = cb % Cfg::QB;
+          const uint4 q4 = *reinterpret_cast<const uint4*>(sbase + Cfg::Q_OFF + box * (KS * Cfg::QB * 512) +
+                                                           slab * (Cfg::QB * 512) + within * 512 + lane * 16);
+          const uint8_t* mp = sbase + Cfg::M_OFF + box * (KS * Cfg::QB * 256) + slab * (Cfg::QB * 256) + within * 256;
+          const uint32_t e0 = *reinterpret_cast<const uint32_t*>(mp + lane * 4);
+          const uint32_t e1 = *reinterpret_cast<const uint32_t*>(mp + 128 + lane * 4);
+          // Activation fragments: matrix c of the ldmatrix is 16-byte K chunk c of the slab.
+          uint32_t bf[NB][4];
+          {
+            const int chunk = slab * 4 + (lane >> 3);          // 16-byte chunk inside the stage
+            const int bx = chunk >> 3, cw = chunk & 7, r8 = lane & 7;
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+              if (nb < nbv) {
+                const int row = nb * 8 + r8;
+                ldmatrix_x4(bf[nb], x_s + bx * Cfg::X_BOX_BYTES + row * 128 + ((cw ^ r8) << 4));
+              }
+            }
+          }
+          const uint32_t qs[4] = {q4.x, q4.y, q4.z, q4.w};
+          const uint32_t scs[4] = {sc.x, sc.y, sc.z, sc.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint32_t lo0, hi0, lo1, hi1;
+            int4x4_to_half2x2(qs[j], lo0, hi0);
+            int4x4_to_half2x2(qs[j] >> 8, lo1, hi1);
+            if (a.grouped) {
+              const uint32_t s0 = __byte_perm(scs[j], 0, 0x1010);  // scale of column j, both halves
+              const uint32_t s1 = __byte_perm(scs[j], 0, 0x3232);  // scale of column j + 4
+              lo0 = hmul2_u32(lo0, s0); hi0 = hmul2_u32(hi0, s0);
+              lo1 = hmul2_u32(lo1, s1); hi1 = hmul2_u32(hi1, s1);
+            }
+            const uint32_t e = (j < 2) ? e0 : e1;
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+              if (nb < nbv) {
+                if (j & 1) mma_sp_m16n8k32<1>(acc[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
+                else       mma_sp_m16n8k32<0>(acc[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
+              }
+            }
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[st]);
+      if (++st == STAGES) { st = 0; phase ^= 1; }
+    }
+
+    // Partner warps (same column block) own identical fragments: reduce element-wise in a fixed order.
+    if constexpr (KQ > 1) {
+      if (kq > 0) {
+        float* dst = red + (kq - 1) * (16 * NB * SW * 32) + cb * 32 + lane;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+          for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) dst[((j * NB + nb) * 4 + c) * (SW * 32)] = acc[j][nb][c];
+      }
+      named_bar_sync(1, kConsumerThreads);
+      if (kq == 0) {
+#pragma unroll
+        for (int p = 0; p < KQ - 1; ++p) {
+          const float* src = red + p * (16 * NB * SW * 32) + cb * 32 + lane;
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+              for (int c = 0; c < 4; ++c) acc[j][nb][c] += src[((j * NB + nb) * 4 + c) * (SW * 32)];
+        }
+      }
+    }
+
+    if (kq == 0 && col_ok) {
+      // This thread owns columns col..col+7 (col + j from c = 0,1 and col + 4 + j from c = 2,3)
+      // for tokens nb*8 + 2*m4 and + 1.
+      const int col = w.col0 + cb * 64 + g8 * 8;
+      float sf[8];
+      if (!a.grouped) {
+        const uint4 sv = *reinterpret_cast<const uint4*>(a.scales + (size_t)w.delta * a.N + col);
+        const __half2* sh = reinterpret_cast<const __half2*>(&sv);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __half22float2(sh[i]);
+          sf[2 * i] = f.x;
+          sf[2 * i + 1] = f.y;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sf[i] = 1.f;
+      }
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) {
+        if (nb < nbv) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int t = nb * 8 + 2 * m4 + h;
+            if (t < w.valid) {
+              const int xr = w.row0 + t;
+              const int orow = a.row_map ? a.row_map[xr] : xr;
+              if (orow >= 0 && orow < a.rows) {
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  v[j] = acc[j][nb][h] * sf[j];
+                  v[4 + j] = acc[j][nb][2 + h] * sf[4 + j];
+                }
+                uint4* dst = reinterpret_cast<uint4*>(a.y + (size_t)orow * a.N + col);
+                if (a.accumulate) {
+                  const uint4 old = *dst;
+                  const __half2* oh = reinterpret_cast<const __half2*>(&old);
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    const float2 f = __half22float2(oh[i]);
+                    v[2 * i] += f.x;
+                    v[2 * i + 1] += f.y;
+                  }
+                }
+                uint4 out;
+                __half2* ob = reinterpret_cast<__half2*>(&out);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) ob[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+                *dst = out;
+              }
+            }
+          }
+        }
+      }
+    }
+    if constexpr (KQ > 1) named_bar_sync(1, kConsumerThreads);  // red[] may be rewritten after this
+  }
+}
+
+}  // namespace trb

@@ -1,0 +1,303 @@
+// Host side of the grouped 2:4-sparse delta GEMM: tensor-map construction, configuration choice
+// and the C entry points that stand in for the reference's launchers
+// (marlin_cuda_2_4, csrc/ops/marlin_nm.cu:42-119; triteia_cuda_sbmm_2_4,
+// csrc/ops/triteia_nm_sbmm.cu:809-847; triteia_cuda_bmm_2_4, csrc/ops/triteia_nm_bmm.cu:760-834).
+#include "delta_gemm.cuh"
+
+#include <cudaTypedefs.h>
+#include <mutex>
+
+namespace trb {
+
+static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  });
+  return fn;
+}
+
+// 2-D row-major tensor [rows, cols] of `esize`-byte elements, box [box_rows, box_cols].
+static bool make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int esize, const void* base, uint64_t rows,
+                        uint64_t cols, uint32_t box_rows, uint32_t box_cols, CUtensorMapSwizzle swz) {
+  auto fn = get_encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * (uint64_t)esize};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static int sm_count(int dev) {
+  static int cached[64] = {};
+  if (dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+    cached[dev] = v;
+  }
+  return cached[dev];
+}
+
+struct GemmCall {
+  const void* x;
+  const void* q;
+  const void* meta;
+  const void* s;
+  int num_deltas, groupsize, dev, sms;
+  cudaStream_t stream;
+};
+
+template <class Cfg>
+static int launch_cfg(const GemmCall& c, const GemmArgs& a) {
+  const int slabs = a.K / 32;
+  const int groups = a.grouped ? a.K / 128 : 1;
+  CUtensorMap tx, tq, tm, ts;
+  if (!make_map_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, c.x, (uint64_t)a.rows, (uint64_t)a.K, Cfg::TT, 64,
+                   CU_TENSOR_MAP_SWIZZLE_128B))
+    return TRB_ERR_CUDA;
+  if (!make_map_2d(&tq, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, c.q, (uint64_t)c.num_deltas * slabs, 2ull * a.N, Cfg::KS,
+                   Cfg::QB * 128, CU_TENSOR_MAP_SWIZZLE_NONE))
+    return TRB_ERR_CUDA;
+  if (!make_map_2d(&tm, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, c.meta, (uint64_t)c.num_deltas * slabs, (uint64_t)a.N,
+                   Cfg::KS, Cfg::QB * 64, CU_TENSOR_MAP_SWIZZLE_NONE))
+    return TRB_ERR_CUDA;
+  if (a.grouped) {
+    if (!make_map_2d(&ts, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, c.s, (uint64_t)c.num_deltas * groups, (uint64_t)a.N,
+                     Cfg::KS / 4, Cfg::SW * 64, CU_TENSOR_MAP_SWIZZLE_NONE))
+      return TRB_ERR_CUDA;
+  } else {
+    ts = tm;  // never dereferenced
+  }
+  static bool attr_set[64] = {};
+  if (c.dev >= 0 && c.dev < 64 && !attr_set[c.dev]) {
+    if (cudaFuncSetAttribute(delta_gemm_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg::SMEM_ALLOC) != cudaSuccess)
+      return TRB_ERR_CUDA;
+    attr_set[c.dev] = true;
+  }
+  int grid = sm_count(c.dev);
+  if (c.sms > 0 && c.sms < grid) grid = c.sms;
+  // Upper bound on work items known on the host: never launch more CTAs than that.
+  const int n_stripes = (a.N + Cfg::SW * 64 - 1) / (Cfg::SW * 64);
+  long long max_tiles;
+  if (a.mode == kSegSingle) max_tiles = (a.rows + Cfg::TT - 1) / Cfg::TT;
+  else if (a.mode == kSegIdentity) max_tiles = a.rows;
+  else max_tiles = (long long)a.rows / Cfg::TT + (a.n_seg_ptr ? kMaxSegments : a.n_seg);
+  const long long max_items = max_tiles * n_stripes;
+  if (max_items < grid) grid = (int)(max_items > 0 ? max_items : 1);
+  delta_gemm_kernel<Cfg><<<grid, kGemmThreads, Cfg::SMEM_ALLOC, c.stream>>>(tx, tq, tm, ts, a);
+  return cudaGetLastError() == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
+}
+
+using CfgT8 = GemmCfg<1, 2, 4, 8, 10>;
+using CfgT16 = GemmCfg<2, 2, 4, 8, 8>;
+using CfgT32 = GemmCfg<4, 2, 4, 8, 5>;
+using CfgT64 = GemmCfg<8, 4, 2, 4, 5>;
+static_assert(CfgT8::SMEM_ALLOC <= 232448 && CfgT16::SMEM_ALLOC <= 232448 && CfgT32::SMEM_ALLOC <= 232448 &&
+                  CfgT64::SMEM_ALLOC <= 232448,
+              "shared memory budget of one sm_100 CTA");
+
+int gemm_tile_tokens(int tokens_per_segment) {
+  if (tokens_per_segment <= 8) return 8;
+  if (tokens_per_segment <= 16) return 16;
+  if (tokens_per_segment <= 32) return 32;
+  return 64;
+}
+
+static int check_common(const void* A, const void* B, const void* meta, void* C, const void* s, int N, int T, int K,
+                        int groupsize) {
+  if (N < 0 || T < 0 || K < 0) return TRB_ERR_BAD_ARG;
+  if (N == 0 || T == 0 || K == 0) return -1;  // nothing to do
+  if (!A || !B || !meta || !C || !s) return TRB_ERR_BAD_ARG;
+  if (N % 128 != 0 || K % 128 != 0) return TRB_ERR_PROB_SHAPE;
+  if (groupsize != -1 && groupsize != 128) return TRB_ERR_KERN_SHAPE;
+  const uintptr_t bits = (uintptr_t)A | (uintptr_t)B | (uintptr_t)meta | (uintptr_t)C | (uintptr_t)s;
+  if (bits & 15) return TRB_ERR_BAD_ARG;
+  return TRB_OK;
+}
+
+int gemm_dispatch(const GemmCall& c, const GemmArgs& a, int tile_tokens) {
+  cudaError_t e = cudaSetDevice(c.dev);
+  if (e != cudaSuccess) return TRB_ERR_CUDA;
+  switch (tile_tokens) {
+    case 8: return launch_cfg<CfgT8>(c, a);
+    case 16: return launch_cfg<CfgT16>(c, a);
+    case 32: return launch_cfg<CfgT32>(c, a);
+    case 64: return launch_cfg<CfgT64>(c, a);
+    default: return TRB_ERR_KERN_SHAPE;
+  }
+}
+
+}  // namespace trb
+
+using namespace trb;
+
+extern "C" int trb_mul_2_4(const void* A, const void* B, const void* meta, void* C, const void* s, int prob_m,
+                           int prob_n, int prob_k, void* workspace, int groupsize, int dev, void* stream,
+                           int thread_k, int thread_m, int sms, int max_par) {
+  (void)workspace; (void)thread_k; (void)thread_m; (void)max_par;
+  const int rc = check_common(A, B, meta, C, s, prob_m, prob_n, prob_k, groupsize);
+  if (rc == -1) return TRB_OK;
+  if (rc != TRB_OK) return rc;
+  GemmArgs a{};
+  a.mode = kSegSingle;
+  a.rows = prob_n; a.N = prob_m; a.K = prob_k; a.num_deltas = 1;
+  a.grouped = groupsize == 128;
+  a.scales = (const __half*)s;
+  a.y = (__half*)C;
+  GemmCall c{A, B, meta, s, 1, groupsize, dev, sms, (cudaStream_t)stream};
+  return gemm_dispatch(c, a, gemm_tile_tokens(prob_n));
+}
+
+extern "C" int trb_sbmm_2_4(const void* A, const void* B, const void* meta, void* C, const void* s,
+                            const void* indices, const void* starts, const void* counts, int prob_m, int prob_n,
+                            int prob_k, int prob_r, void* workspace, int groupsize, int dev, void* stream,
+                            int thread_k, int thread_m, int sms, int max_par) {
+  (void)workspace; (void)thread_k; (void)thread_m; (void)max_par;
+  if (prob_r == 0) return TRB_OK;
+  if (prob_r < 0 || !indices || !starts || !counts) return TRB_ERR_BAD_ARG;
+  const int rc = check_common(A, B, meta, C, s, prob_m, prob_n, prob_k, groupsize);
+  if (rc == -1) return TRB_OK;
+  if (rc != TRB_OK) return rc;
+  if (prob_r > kMaxSegments) return TRB_ERR_KERN_SHAPE;
+  GemmArgs a{};
+  a.mode = kSegList;
+  a.seg_delta = (const int*)indices; a.seg_start = (const int*)starts; a.seg_count = (const int*)counts;
+  a.n_seg = prob_r;
+  a.rows = prob_n; a.N = prob_m; a.K = prob_k;
+  a.num_deltas = 1 << 30;  // the stacked tensors' leading dimension is not part of this signature
+  a.grouped = groupsize == 128;
+  a.scales = (const __half*)s;
+  a.y = (__half*)C;
+  // The tensor maps need a row bound; the reference signature has no delta count, so the maps
+  // cover the largest index space a 32-bit row coordinate allows and the ids are trusted as the
+  // reference trusts them.
+  const int slabs = prob_k / 32;
+  int max_d = (int)(((1ull << 31) - 1) / (uint64_t)slabs);
+  GemmCall c{A, B, meta, s, max_d, groupsize, dev, sms, (cudaStream_t)stream};
+  a.num_deltas = max_d;
+  const int avg = (prob_n + prob_r - 1) / prob_r;
+  return gemm_dispatch(c, a, gemm_tile_tokens(avg));
+}
+
+extern "C" int trb_bmm_2_4(const void* A, const void* B, const void* meta, void* C, const void* s, int prob_m,
+                           int prob_n, int prob_k, void* workspace, int groupsize, int dev, void* stream,
+                           int thread_k, int thread_m, int sms, int max_par) {
+  (void)workspace; (void)thread_k; (void)thread_m; (void)max_par;
+  const int rc = check_common(A, B, meta, C, s, prob_m, prob_n, prob_k, groupsize);
+  if (rc == -1) return TRB_OK;
+  if (rc != TRB_OK) return rc;
+  GemmArgs a{};
+  a.mode = kSegIdentity;
+  a.rows = prob_n; a.N = prob_m; a.K = prob_k; a.num_deltas = prob_n;
+  a.grouped = groupsize == 128;
+  a.scales = (const __half*)s;
+  a.y = (__half*)C;
+  GemmCall c{A, B, meta, s, prob_n, groupsize, dev, sms, (cudaStream_t)stream};
+  return gemm_dispatch(c, a, 8);
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+extern "C" size_t trb_sbmm_indexed_scratch_bytes(int num_tokens, int prob_k, int num_deltas) {
+  if (num_tokens <= 0 || prob_k <= 0 || num_deltas <= 0) return 256;
+  const size_t tiles = (size_t)trb_route_max_tiles(num_tokens, num_deltas, 8);
+  size_t b = 256;                                          // counters
+  b += align_up((size_t)num_tokens * 4, 256);              // perm
+  b += 3 * align_up(tiles * 4, 256);                       // tile lists
+  b += align_up((size_t)num_tokens * prob_k * 2, 256);     // gathered activations
+  return b;
+}
+
+extern "C" int trb_sbmm_indexed(const void* x, const void* qweights, const void* metas, const void* scales,
+                                const void* indices, void* y, int num_tokens, int prob_m, int prob_k,
+                                int num_deltas, int index_offset, int groupsize, int accumulate, void* scratch,
+                                size_t scratch_bytes, int dev, void* stream_v) {
+  cudaStream_t stream = (cudaStream_t)stream_v;
+  if (num_deltas <= 0) return TRB_ERR_BAD_ARG;
+  const int rc = check_common(x, qweights, metas, y, scales, prob_m, num_tokens, prob_k, groupsize);
+  if (rc == -1) return TRB_OK;
+  if (rc != TRB_OK) return rc;
+  if (!indices || !scratch || ((uintptr_t)scratch & 255)) return TRB_ERR_BAD_ARG;
+  if (scratch_bytes < trb_sbmm_indexed_scratch_bytes(num_tokens, prob_k, num_deltas)) return TRB_ERR_SCRATCH;
+  if (cudaSetDevice(dev) != cudaSuccess) return TRB_ERR_CUDA;
+
+  const int segs = num_tokens < num_deltas ? num_tokens : num_deltas;
+  const int tt = gemm_tile_tokens((num_tokens + segs - 1) / segs);
+  const int max_tiles = trb_route_max_tiles(num_tokens, num_deltas, tt);
+  if (max_tiles > kMaxSegments) return TRB_ERR_KERN_SHAPE;
+  const size_t tiles8 = (size_t)trb_route_max_tiles(num_tokens, num_deltas, 8);
+
+  uint8_t* p = (uint8_t*)scratch;
+  int* counters = (int*)p; p += 256;
+  int* perm = (int*)p; p += align_up((size_t)num_tokens * 4, 256);
+  int* tile_delta = (int*)p; p += align_up(tiles8 * 4, 256);
+  int* tile_start = (int*)p; p += align_up(tiles8 * 4, 256);
+  int* tile_count = (int*)p; p += align_up(tiles8 * 4, 256);
+  void* x_sorted = p;
+
+  int r = route_launch((const int*)indices, num_tokens, num_deltas, tt, index_offset, perm, nullptr, nullptr, nullptr, tile_delta,
+                       tile_start, tile_count, counters, stream);
+  if (r != TRB_OK) return r;
+  r = gather_launch(x, perm, counters, x_sorted, y, num_tokens, prob_k, prob_m, accumulate ? 0 : 1, stream);
+  if (r != TRB_OK) return r;
+
+  GemmArgs a{};
+  a.mode = kSegList;
+  a.seg_delta = tile_delta; a.seg_start = tile_start; a.seg_count = tile_count;
+  a.n_seg_ptr = counters + 1;
+  a.n_seg = max_tiles;
+  a.rows = num_tokens; a.N = prob_m; a.K = prob_k; a.num_deltas = num_deltas;
+  a.grouped = groupsize == 128;
+  a.scales = (const __half*)scales;
+  a.y = (__half*)y;
+  a.row_map = perm;
+  a.accumulate = accumulate;
+  GemmCall c{x_sorted, qweights, metas, scales, num_deltas, groupsize, dev, -1, stream};
+  return gemm_dispatch(c, a, tt);
+}
+
+extern "C" int trb_route(const void* indices, int num_tokens, int num_deltas, int tile_tokens, int index_offset,
+                         void* perm,
+                         void* seg_delta, void* seg_start, void* seg_count, void* tile_delta, void* tile_start,
+                         void* tile_count, void* counters, int dev, void* stream) {
+  if (cudaSetDevice(dev) != cudaSuccess) return TRB_ERR_CUDA;
+  return route_launch((const int*)indices, num_tokens, num_deltas, tile_tokens, index_offset, (int*)perm, (int*)seg_delta,
+                      (int*)seg_start, (int*)seg_count, (int*)tile_delta, (int*)tile_start, (int*)tile_count,
+                      (int*)counters, (cudaStream_t)stream);
+}
+
+extern "C" int trb_device_status(int dev, int* status_out) {
+  if (!status_out) return TRB_ERR_BAD_ARG;
+  if (cudaSetDevice(dev) != cudaSuccess) return TRB_ERR_CUDA;
+  if (cudaDeviceSynchronize() != cudaSuccess) return TRB_ERR_CUDA;
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)) != cudaSuccess) return TRB_ERR_CUDA;
+  const int zero = 0;
+  if (cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)) != cudaSuccess) return TRB_ERR_CUDA;
+  *status_out = v;
+  return TRB_OK;
+}
+
+extern "C" int trb_version(void) { return 100; }
+
+extern "C" const char* trb_status_string(int status) {
+  switch (status) {
+    case TRB_OK: return "ok";
+    case TRB_ERR_PROB_SHAPE: return "problem shape not supported";
+    case TRB_ERR_KERN_SHAPE: return "no kernel implementation for this configuration";
+    case TRB_ERR_BAD_ARG: return "bad argument (null or misaligned pointer, negative size)";
+    case TRB_ERR_CUDA: return "CUDA call failed";
+    case TRB_ERR_TIMEOUT: return "a bounded device-side wait expired";
+    case TRB_ERR_SCRATCH: return "scratch buffer too small";
+    default: return "unknown status";
+  }
+}

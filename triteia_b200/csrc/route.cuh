@@ -1,0 +1,216 @@
+// Token router: stable grouping of tokens by delta id (-1 first) and the tile work list, in one
+// single-CTA launch with no host synchronisation.  Replaces the torch prologue of the reference
+// (triteia/python/ops/matmul/sbmm.py:94-123: unique_consecutive, where, cumsum, three host
+// syncs), and drops its requirement that the caller pre-sorts the indices.
+//
+// Counting sort made stable with warp-level primitives: the token range is cut into one
+// contiguous piece per warp; each warp histograms its piece (match_any groups equal ids inside
+// a 32-token step), a block-wide exclusive scan over (id-major, warp-minor) counts gives every
+// (id, warp) pair its first output slot, and a second pass ranks tokens inside each step with
+// match_any + popc.  All integer work; results are bit-exact against the CPU router.
+#include "common.cuh"
+
+namespace trb {
+
+constexpr int kRouteThreads = 1024;
+
+// Exclusive scan of data[0..len) in shared memory by the whole CTA; returns the total.
+__device__ int block_exclusive_scan(int* data, int len, int* warp_tot /* [33] */) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int per = (len + kRouteThreads - 1) / kRouteThreads;
+  const int lo = min(len, tid * per), hi = min(len, lo + per);
+  int sum = 0;
+  for (int i = lo; i < hi; ++i) sum += data[i];
+  int inc = sum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += v;
+  }
+  if (lane == 31) warp_tot[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    int w = warp_tot[lane];
+    int winc = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, winc, o);
+      if (lane >= o) winc += v;
+    }
+    warp_tot[lane] = winc - w;
+    if (lane == 31) warp_tot[32] = winc;
+  }
+  __syncthreads();
+  int run = warp_tot[warp] + inc - sum;
+  for (int i = lo; i < hi; ++i) {
+    const int v = data[i];
+    data[i] = run;
+    run += v;
+  }
+  const int total = warp_tot[32];
+  __syncthreads();
+  return total;
+}
+
+__global__ void __launch_bounds__(kRouteThreads, 1)
+route_kernel(const int* __restrict__ indices, int T, int D, int W, int TT, int id_offset, int* __restrict__ perm,
+             int* __restrict__ seg_delta, int* __restrict__ seg_start, int* __restrict__ seg_count,
+             int* __restrict__ tile_delta, int* __restrict__ tile_start, int* __restrict__ tile_count,
+             int* __restrict__ counters) {
+  extern __shared__ int sm[];
+  const int bins = D + 1;             // bin 0 = id -1 (and out-of-range ids)
+  int* hist = sm;                     // [bins][W]
+  int* bin_start = hist + bins * W;   // [bins + 1]
+  int* seg_flag = bin_start + bins + 1;   // [bins]
+  int* tile_cnt = seg_flag + bins;        // [bins]
+  __shared__ int warp_tot[33];
+  __shared__ int n_invalid;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int i = tid; i < bins * W; i += kRouteThreads) hist[i] = 0;
+  if (tid == 0) n_invalid = 0;
+  __syncthreads();
+
+  const int piece = ((T + W - 1) / W + 31) / 32 * 32;   // tokens per warp, multiple of 32
+  const int t_lo = warp * piece, t_hi = min(T, t_lo + piece);
+
+  if (warp < W) {
+    for (int base = t_lo; base < t_hi; base += 32) {
+      const int t = base + lane;
+      int bin = -1;
+      if (t < t_hi) {
+        const int raw = indices[t];
+        const int id = raw - id_offset;
+        if (raw < -1 || id >= D) atomicAdd(&n_invalid, 1);
+        bin = (id < 0 || id >= D) ? 0 : id + 1;
+      }
+      const unsigned active = __ballot_sync(0xffffffffu, bin >= 0);
+      if (bin >= 0) {
+        const unsigned same = __match_any_sync(active, bin);
+        if ((same & ((1u << lane) - 1)) == 0) hist[bin * W + warp] += __popc(same);
+      }
+    }
+  }
+  __syncthreads();
+  block_exclusive_scan(hist, bins * W, warp_tot);
+  for (int b = tid; b < bins; b += kRouteThreads) bin_start[b] = hist[b * W];
+  if (tid == 0) bin_start[bins] = T;
+  __syncthreads();
+
+  if (perm != nullptr && warp < W) {
+    for (int base = t_lo; base < t_hi; base += 32) {
+      const int t = base + lane;
+      int bin = -1;
+      if (t < t_hi) {
+        const int id = indices[t] - id_offset;
+        bin = (id < 0 || id >= D) ? 0 : id + 1;
+      }
+      const unsigned active = __ballot_sync(0xffffffffu, bin >= 0);
+      if (bin >= 0) {
+        const unsigned same = __match_any_sync(active, bin);
+        const int rank = __popc(same & ((1u << lane) - 1));
+        const int first = hist[bin * W + warp];
+        __syncwarp(active);
+        if (rank == 0) hist[bin * W + warp] = first + __popc(same);
+        perm[first + rank] = t;
+      }
+      __syncwarp();
+    }
+  }
+  __syncthreads();
+
+  // Segments (distinct ids >= 0 in increasing order) and their tiles.
+  for (int b = tid; b < bins; b += kRouteThreads) {
+    const int cnt = bin_start[b + 1] - bin_start[b];
+    const bool is_seg = b >= 1 && cnt > 0;
+    seg_flag[b] = is_seg ? 1 : 0;
+    tile_cnt[b] = is_seg ? (cnt + TT - 1) / TT : 0;
+  }
+  __syncthreads();
+  const int n_seg = block_exclusive_scan(seg_flag, bins, warp_tot);
+  const int n_tiles = block_exclusive_scan(tile_cnt, bins, warp_tot);
+  for (int b = tid + 1; b < bins; b += kRouteThreads) {
+    const int start = bin_start[b], cnt = bin_start[b + 1] - start;
+    if (cnt > 0) {
+      const int s = seg_flag[b];
+      if (seg_delta) seg_delta[s] = b - 1;
+      if (seg_start) seg_start[s] = start;
+      if (seg_count) seg_count[s] = cnt;
+      if (tile_delta && tile_start && tile_count) {
+        int tpos = tile_cnt[b];
+        for (int off = 0; off < cnt; off += TT, ++tpos) {
+          tile_delta[tpos] = b - 1;
+          tile_start[tpos] = start + off;
+          tile_count[tpos] = min(TT, cnt - off);
+        }
+      }
+    }
+  }
+  if (tid == 0 && counters) {
+    counters[0] = n_seg;
+    counters[1] = n_tiles;
+    counters[2] = bin_start[1];
+    counters[3] = n_invalid;
+  }
+}
+
+// x_sorted[p] = x[perm[p]] for every sorted position; optionally zero y rows whose id is -1.
+__global__ void gather_rows_kernel(const uint4* __restrict__ x, const int* __restrict__ perm,
+                                   const int* __restrict__ counters, uint4* __restrict__ x_sorted,
+                                   uint4* __restrict__ y, int T, int k_vec, int n_vec, int zero_base_rows) {
+  const int p = blockIdx.x;
+  if (p >= T) return;
+  const int src = perm[p];
+  if (src < 0 || src >= T) return;
+  const int n_neg = counters[2];
+  if (p >= n_neg) {
+    const uint4* s = x + (size_t)src * k_vec;
+    uint4* d = x_sorted + (size_t)p * k_vec;
+    for (int i = threadIdx.x; i < k_vec; i += blockDim.x) d[i] = s[i];
+  } else if (zero_base_rows) {
+    uint4* d = y + (size_t)src * n_vec;
+    for (int i = threadIdx.x; i < n_vec; i += blockDim.x) d[i] = make_uint4(0, 0, 0, 0);
+  }
+}
+
+}  // namespace trb
+
+using namespace trb;
+
+extern "C" int trb_route_max_tiles(int num_tokens, int num_deltas, int tile_tokens) {
+  if (num_tokens <= 0 || tile_tokens <= 0) return 0;
+  const int segs = num_tokens < num_deltas ? num_tokens : num_deltas;
+  return num_tokens / tile_tokens + segs;
+}
+
+namespace trb {
+int route_launch(const int* indices, int T, int D, int TT, int id_offset, int* perm, int* seg_delta, int* seg_start,
+                 int* seg_count, int* tile_delta, int* tile_start, int* tile_count, int* counters,
+                 cudaStream_t stream) {
+  if (T < 0 || T > 65536 || D < 1 || D > 8191 || TT < 1) return TRB_ERR_PROB_SHAPE;
+  if ((indices == nullptr && T > 0) || counters == nullptr) return TRB_ERR_BAD_ARG;
+  const int bins = D + 1;
+  int W = (50000 - 3 * bins - 1) / bins;   // shared-memory budget of ~195 KiB
+  W = W < 1 ? 1 : (W > 32 ? 32 : W);
+  const size_t smem = (size_t)(bins * W + 3 * bins + 1) * sizeof(int);
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+      return TRB_ERR_CUDA;
+    attr_set[dev] = true;
+  }
+  route_kernel<<<1, kRouteThreads, smem, stream>>>(indices, T, D, W, TT, id_offset, perm, seg_delta, seg_start, seg_count,
+                                                   tile_delta, tile_start, tile_count, counters);
+  return cudaGetLastError() == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
+}
+
+int gather_launch(const void* x, const int* perm, const int* counters, void* x_sorted, void* y, int T, int K,
+                  int N, int zero_base_rows, cudaStream_t stream) {
+  if (T == 0) return TRB_OK;
+  gather_rows_kernel<<<T, 128, 0, stream>>>((const uint4*)x, perm, counters, (uint4*)x_sorted, (uint4*)y, T,
+                                            K / 8, N / 8, zero_base_rows);
+  return cudaGetLastError() == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
+}
+}  // namespace trb

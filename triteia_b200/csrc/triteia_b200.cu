@@ -1,0 +1,10 @@
+// The library is built as ONE translation unit (no relocatable device code): every kernel and
+// every extern "C" entry point declared in include/triteia_b200.h is reached from here.
+#include <type_traits>
+
+#include "common.cuh"
+#include "route.cuh"
+#include "delta_gemm.cuh"
+#include "delta_gemm_host.cuh"
+#include "unpack.cuh"
+#include "lora.cuh"

@@ -1,0 +1,1 @@
+from .linear import sparse_low_precision_linear

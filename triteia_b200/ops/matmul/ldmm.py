@@ -1,0 +1,47 @@
+"""ldmm: per token, base GEMM plus either a LoRA adapter or a packed delta, chosen by one index
+vector — same signatures as triteia/python/ops/matmul/ldmm.py (`baseline_ldmm` :8, `ldmm` :51).
+
+Index space (ldmm.py:54-59 of the reference): [0, M) = LoRA adapter, [M, M + D) = delta,
+-1 = base only, with M = LwA.shape[0].
+"""
+import torch
+
+from .lora import lora_forloop, lora_indexed
+from .sbmm import sbmm_4bit_2_4_forloop, sbmm_indexed
+
+
+def _base(x_, base_weight, n_out):
+    if base_weight is not None:
+        return torch.matmul(x_, base_weight.t())
+    return torch.zeros(x_.shape[0], n_out, dtype=x_.dtype, device=x_.device)
+
+
+def baseline_ldmm(indices, x, LwA, LwB, DeltaW, metas, ss, base_weight=None, debug=False):
+    """Comparison path built from the per-id loops (gathers and scatters through masks)."""
+    x_ = x.to(torch.float16)
+    y = _base(x_, base_weight, LwB.shape[2])
+    M = LwA.shape[0]
+    mask_lora = (indices < M) & (indices != -1)
+    mask_sbmm = (indices >= M) & (indices != -1)
+    if bool(mask_lora.any()):
+        y[mask_lora] += lora_forloop(LwA.to(torch.float16), LwB.to(torch.float16), x_[mask_lora], indices[mask_lora])
+    if bool(mask_sbmm.any()):
+        y[mask_sbmm] += sbmm_4bit_2_4_forloop(DeltaW, x_[mask_sbmm], metas, ss, indices[mask_sbmm] - M)
+    return y.to(x.dtype)
+
+
+def ldmm(indices, x, LwA, LwB, DeltaW, metas, ss, base_weight=None, debug=False):
+    """Two launches after the base GEMM, no host synchronisation, no masks: the indexed LoRA
+    kernel skips ids outside [0, M) and the router of the delta kernel skips ids outside
+    [M, M + D), both reading the one index vector.  The delta tokens may be in any order."""
+    x_ = x.to(torch.float16)
+    if not x_.is_contiguous():
+        x_ = x_.contiguous()
+    y = _base(x_, base_weight, LwB.shape[2])
+    M = LwA.shape[0]
+    idx = indices if indices.dtype == torch.int32 else indices.to(torch.int32)
+    if M > 0:
+        lora_indexed(y, x_, LwA.to(torch.float16).contiguous(), LwB.to(torch.float16).contiguous(), idx)
+    if DeltaW is not None and DeltaW.shape[0] > 0:
+        sbmm_indexed(x_, DeltaW, metas, ss, idx, y=y, index_offset=M)
+    return y.to(x.dtype)
