@@ -1,0 +1,332 @@
+"""Benchmark of the indexed delta matmul path (sbmm) on synthetic Llama-shaped data.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload at N = 1 (`config.workload` = "sbmm-decode-64x4096x4096-g128"): 64 int4 2:4 deltas of
+4096 x 4096 with group-128 fp16 scales resident in HBM; one step = one batch of 128 fp16 tokens
+~N(0,1), one int32 delta index per token uniform over [0, 64) with 10% set to -1, pushed
+through `sbmm_4bit_2_4_native` (router + row gather + grouped kernel).  At N > 1 every rank holds
+its own 64-delta shard of a 64*N-delta set and 128 tokens whose indices range over the whole set;
+tokens are exchanged with all-to-all (weak scaling).
+
+Prints ONE JSON line: tokens/s with inputs resident on the device (`value`), the same through the
+public API from pinned host buffers (`e2e`), the roofline of the grouped kernel measured with CUDA
+events on the launching stream, the CPU baseline (the torch fp32 dequantise-then-matmul path on
+the host cores, bounded sample), and the clocks sampled during the timed region.
+`--impl reference` times only that CPU path and prints it in the same format.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+D_PER_GPU, K, N_OUT, TOKENS, GROUP = 64, 4096, 4096, 128, 128
+BYTES_PER_DELTA = K * N_OUT // 4 + K * N_OUT // 8 + (K // GROUP) * N_OUT * 2   # codes + metadata + scales
+METRIC, UNIT = "sbmm_tokens_per_s", "tokens/s"
+WORKLOAD = "sbmm-decode-64x4096x4096-g128"
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+def make_indices(seed, tokens, num_deltas):
+    rng = np.random.default_rng(seed)
+    idx = rng.integers(0, num_deltas, tokens)
+    idx[rng.choice(tokens, size=tokens // 10, replace=False)] = -1
+    return idx.astype(np.int32)
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms while running."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.rows, self.proc, self.idx = [], None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.idx}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.thread.join(timeout=2)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------- CPU baseline
+def cpu_baseline(num_sample_deltas=6, repeats=3, seed=0):
+    """The reference has no CPU kernel for this path; its torch check path is
+    `sbmm_16bit_forloop` on dequantised weights (triteia/python/ops/matmul/sbmm.py:7-23).  Timed
+    here in fp32 with all host threads on a bounded sample: `num_sample_deltas` deltas of the
+    workload with the tokens that select them; dequantisation is done once, untimed."""
+    from oracle import delta_format as fmt
+    from triteia_b200.ops.utils.generator import random_packed_deltas
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    cores = torch.get_num_threads()
+    qs, metas, ss = random_packed_deltas(num_sample_deltas, K, N_OUT, groupsize=GROUP, device="cpu", seed=seed)
+    weights = [torch.from_numpy(fmt.dequantize(qs[d].numpy(), metas[d].numpy(), ss[d].numpy()).astype(np.float32))
+               for d in range(num_sample_deltas)]
+    idx = make_indices(seed, TOKENS, D_PER_GPU)
+    x = torch.randn(TOKENS, K, generator=torch.Generator().manual_seed(seed)).half().float()
+    rows = [np.flatnonzero(idx == d) for d in range(num_sample_deltas)]
+    n_tok = int(sum(len(r) for r in rows))
+    y = torch.zeros(TOKENS, N_OUT)
+
+    def run():
+        for d, r in enumerate(rows):
+            if len(r):
+                y[r] += x[r] @ weights[d]
+
+    run()
+    t0 = time.perf_counter()
+    for _ in range(repeats):
+        run()
+    dt = (time.perf_counter() - t0) / repeats
+    return {"value": n_tok / dt, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{num_sample_deltas} of {D_PER_GPU} deltas with their {n_tok} tokens, fp32 torch matmul on "
+                      f"dequantised weights, mean of {repeats} passes ({dt * 1e3:.1f} ms each), dequantisation untimed",
+            "seconds_per_pass": dt, "tokens_in_sample": n_tok}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    vals = []
+    for _ in range(args.warmup):
+        cpu_baseline(num_sample_deltas=2, repeats=1)
+    base = None
+    for _ in range(max(1, args.steps)):
+        base = cpu_baseline(num_sample_deltas=4, repeats=2)
+        vals.append(base["value"])
+    v = statistics.mean(vals)
+    base["value"] = v
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": base["seconds_per_pass"] * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "note": "reference ships no CPU kernel; its torch check path "
+                       "(dequantised weights, per-delta matmul) on host cores, bounded sample per step"},
+            "cpu_baseline": base,
+            "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------- GPU arm
+def time_steps(fn, steps, flush):
+    """Per-step CUDA-event timing on the current stream, L2 flushed (untimed) before every step."""
+    times = []
+    for _ in range(steps):
+        flush()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        b.synchronize()
+        times.append(a.elapsed_time(b))
+    return times
+
+
+def run_gpu_arm(args):
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the GPU arm has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    import triteia_b200.ops as ops
+    from triteia_b200 import _lib, sharded
+    from triteia_b200.ops.matmul.sbmm import sbmm_indexed, _segments
+
+    total_deltas = D_PER_GPU * world
+    qs, metas, ss = ops.random_packed_deltas(D_PER_GPU, K, N_OUT, groupsize=GROUP, device=dev, seed=1000 + rank)
+    idx_np = make_indices(rank, TOKENS, total_deltas)
+    x_host = torch.randn(TOKENS, K, generator=torch.Generator().manual_seed(rank)).half().pin_memory()
+    idx_host = torch.from_numpy(idx_np).pin_memory()
+    y_host = torch.empty(TOKENS, N_OUT, dtype=torch.float16).pin_memory()
+    x_dev, idx_dev = x_host.to(dev), idx_host.to(dev)
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    flush = lambda: flush_buf.zero_()
+
+    if world == 1:
+        step_resident = lambda: ops.sbmm_4bit_2_4_native(qs, x_dev, metas, ss, idx_dev)
+        launches_per_step = 3   # router, row gather, grouped kernel
+    else:
+        local = sharded.make_local_sbmm(qs, metas, ss)
+        step_resident = lambda: sharded.sbmm_sharded(x_dev, idx_dev, local, N_OUT)
+        launches_per_step = 3
+
+    def step_e2e():
+        xd = x_host.to(dev, non_blocking=True)
+        idd = idx_host.to(dev, non_blocking=True)
+        if world == 1:
+            y = ops.sbmm_4bit_2_4_native(qs, xd, metas, ss, idd)
+        else:
+            y = sharded.sbmm_sharded(xd, idd, local, N_OUT)
+        y_host.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step_resident()
+        step_e2e()
+    barrier()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    t_wall0 = time.perf_counter()
+    barrier()
+    times = time_steps(step_resident, args.steps, flush)
+    barrier()
+    # end-to-end: host buffers in, host buffer out, wall clock per step around a stream sync
+    e2e_times = []
+    for _ in range(args.steps):
+        flush()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        step_e2e()
+        e2e_times.append((time.perf_counter() - t0) * 1e3)
+    barrier()
+
+    # dominant kernel alone (grouped kernel through the segment-list entry point), rank-local
+    order = torch.argsort(idx_dev.long() % world if world > 1 else idx_dev, stable=True)
+    if world == 1:
+        idx_sorted = idx_dev[order].contiguous()
+        x_sorted = x_dev[order].contiguous()
+        uniq, starts, counts = _segments(idx_sorted)
+        touched = int(uniq.numel())
+    else:
+        mine = (idx_dev >= 0) & (idx_dev % world == rank)
+        loc = torch.div(idx_dev[mine], world, rounding_mode="floor")
+        o2 = torch.argsort(loc, stable=True)
+        idx_sorted = loc[o2].int().contiguous()
+        x_sorted = x_dev[mine][o2].contiguous()
+        uniq, starts, counts = _segments(idx_sorted)
+        touched = int(uniq.numel())
+    y_k = torch.empty(x_sorted.shape[0], N_OUT, dtype=torch.float16, device=dev)
+    ws = torch.zeros(max(touched, 1), N_OUT // 8, dtype=torch.int32, device=dev)
+    from triteia_b200.capi import sbmm_2_4
+    kern = lambda: sbmm_2_4(x_sorted, qs, metas, y_k, ss, uniq, ws, starts, counts) if touched else None
+    for _ in range(3):
+        kern()
+    k_times = time_steps(kern, args.steps, flush)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    wall_s = time.perf_counter() - t_wall0
+
+    t_step = statistics.mean(times)
+    t_e2e = statistics.mean(e2e_times)
+    t_kern = statistics.mean(k_times)
+    if world > 1:
+        t = torch.tensor([t_step, t_e2e], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        t_step, t_e2e = t.tolist()
+    status = _lib.device_status(local_rank)
+
+    if rank == 0:
+        peak, peak_src = peaks()
+        alg_bytes = touched * BYTES_PER_DELTA + x_sorted.numel() * 2 + y_k.numel() * 2 + touched * 12
+        achieved = alg_bytes / (t_kern * 1e-3) / 1e9
+        tokens_total = TOKENS * world
+        line = {
+            "metric": METRIC, "value": tokens_total / (t_step * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": t_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "deltas_per_gpu": D_PER_GPU, "tokens_per_gpu": TOKENS, "k": K, "n": N_OUT,
+                       "groupsize": GROUP, "index_law": "uniform over all deltas, 10% -1, unsorted",
+                       "distinct_deltas_touched_rank0": touched,
+                       "l2": "flushed before every timed step (256 MiB memset, untimed); touched weights "
+                             f"{touched * BYTES_PER_DELTA / 1e6:.0f} MB > 126 MB L2",
+                       "parallelism": "single GPU" if world == 1 else f"deltas sharded by id over {world} GPUs, "
+                                                                       "NCCL all-to-all token dispatch/combine"},
+            "e2e": {"value": tokens_total / (t_e2e * 1e-3), "unit": UNIT, "ms_per_step": t_e2e,
+                    "h2d_bytes_per_step": int(x_host.numel() * 2 + idx_host.numel() * 4),
+                    "d2h_bytes_per_step": int(y_host.numel() * 2),
+                    "note": "sbmm_4bit_2_4_native from pinned host buffers; packed deltas stay resident (model state)"},
+            "gpu_launches": launches_per_step * args.steps,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": peak_src, "kernel": "delta_gemm_kernel", "kernel_ms": t_kern,
+                         "algorithmic_bytes": alg_bytes, "traffic": None},
+            "clocks": clocks, "device_status": status, "wall_s": wall_s,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline()
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

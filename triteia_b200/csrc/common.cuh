@@ -141,6 +141,22 @@ __device__ __forceinline__ void mma_sp_m16n8k32(float (&d)[4], uint32_t a0, uint
         "n"(SEL));
 }
 
+// Same with a zero accumulator input: D = A_sparse * B.
+template <int SEL>
+__device__ __forceinline__ void mma_sp_m16n8k32_zero(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                     uint32_t a3, const uint32_t (&b)[4], uint32_t e) {
+  asm volatile(
+      "mma.sp::ordered_metadata.sync.aligned.m16n8k32.row.col.f32.f16.f16.f32 "
+      "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9,%10,%11}, {%12,%12,%12,%12}, %13, %14;"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b[0]), "r"(b[1]), "r"(b[2]), "r"(b[3]), "f"(0.f), "r"(e),
+        "n"(SEL));
+}
+
+__device__ __forceinline__ void named_bar_arrive(int id, int threads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
 // Dense m16n8k16 fp16 MMA (LoRA kernels).
 __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
                                              uint32_t b1) {

@@ -51,7 +51,7 @@ struct GemmCfg {
   static constexpr int STAGES = STAGES_;
   static_assert(SW * KQ == kConsumerWarps, "eight consumer warps");
   static_assert(KS % 4 == 0 && KS % KQ == 0 && KS % 2 == 0, "stage must hold whole scale groups");
-  static_assert((KS / KQ) <= 4 && 4 % (KS / KQ) == 0, "a warp's slabs of a stage share one scale group");
+  static_assert((KS / KQ) <= 4 && 4 % (KS / KQ) == 0 && KS <= 16, "a warp's slabs of a stage share one scale group");
   static constexpr int TT = NB * 8;                 // tokens per tile
   static constexpr int QB = SW >= 2 ? 2 : 1;        // column blocks per weight TMA box
   static constexpr int NQBOX = SW / QB;
@@ -232,9 +232,16 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   const int g8 = lane >> 2;   // quad index: MMA row group / token inside a block of 8
   const int m4 = lane & 3;
   constexpr int SPW = KS / KQ;  // slabs per warp per stage
+  // With a whole scale group (4 slabs) per warp and stage, the group's integer levels are
+  // accumulated on their own and scaled once in fp32; otherwise every weight is scaled in fp16.
+  constexpr bool kPostScale = (SPW == 4);
+  const int box = cb / Cfg::QB, within = cb % Cfg::QB;
+  const uint32_t q_off = Cfg::Q_OFF + box * (KS * Cfg::QB * 512) + within * 512 + lane * 16;
+  const uint32_t m_off = Cfg::M_OFF + box * (KS * Cfg::QB * 256) + within * 256 + lane * 4;
 
   int st = 0;
   uint32_t phase = 0;
+  bool first_item = true;
   for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
     const WorkItem w = decode_item<Cfg>(a, prefix, n_seg, n_stripes, item);
     if (!w.ok) continue;
@@ -253,21 +260,22 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       mbar_wait(&full_bar[st], phase, dead);
       const uint8_t* sbase = smem + st * Cfg::STAGE_BYTES;
       const uint32_t x_s = smem_u32(sbase + Cfg::X_OFF);
+      const bool grouped = a.grouped != 0;
       uint4 sc = make_uint4(0, 0, 0, 0);
-      if (a.grouped) {
+      if (grouped) {
         const int grp = (kq * SPW) / 4;
         sc = *reinterpret_cast<const uint4*>(sbase + Cfg::S_OFF + grp * (SW * 128) + cb * 128 + g8 * 16);
       }
+      const uint32_t scs[4] = {sc.x, sc.y, sc.z, sc.w};
+      const bool post = kPostScale && grouped;
+      float accg[4][NB][4];   // levels of the current scale group (post-scale mode)
 #pragma unroll
       for (int i = 0; i < SPW; ++i) {
         const int slab = kq * SPW + i;
         if (ks * KS + slab < slabs && col_ok) {
-          const int box = cb / Cfg::QB, within = cb % Cfg::QB;
-          const uint4 q4 = *reinterpret_cast<const uint4*>(sbase + Cfg::Q_OFF + box * (KS * Cfg::QB * 512) +
-                                                           slab * (Cfg::QB * 512) + within * 512 + lane * 16);
-          const uint8_t* mp = sbase + Cfg::M_OFF + box * (KS * Cfg::QB * 256) + slab * (Cfg::QB * 256) + within * 256;
-          const uint32_t e0 = *reinterpret_cast<const uint32_t*>(mp + lane * 4);
-          const uint32_t e1 = *reinterpret_cast<const uint32_t*>(mp + 128 + lane * 4);
+          const uint4 q4 = *reinterpret_cast<const uint4*>(sbase + q_off + slab * (Cfg::QB * 512));
+          const uint32_t e0 = *reinterpret_cast<const uint32_t*>(sbase + m_off + slab * (Cfg::QB * 256));
+          const uint32_t e1 = *reinterpret_cast<const uint32_t*>(sbase + m_off + slab * (Cfg::QB * 256) + 128);
           // Activation fragments: matrix c of the ldmatrix is 16-byte K chunk c of the slab.
           uint32_t bf[NB][4];
           {
@@ -282,13 +290,12 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             }
           }
           const uint32_t qs[4] = {q4.x, q4.y, q4.z, q4.w};
-          const uint32_t scs[4] = {sc.x, sc.y, sc.z, sc.w};
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             uint32_t lo0, hi0, lo1, hi1;
             int4x4_to_half2x2(qs[j], lo0, hi0);
             int4x4_to_half2x2(qs[j] >> 8, lo1, hi1);
-            if (a.grouped) {
+            if (grouped && !kPostScale) {
               const uint32_t s0 = __byte_perm(scs[j], 0, 0x1010);  // scale of column j, both halves
               const uint32_t s1 = __byte_perm(scs[j], 0, 0x3232);  // scale of column j + 4
               lo0 = hmul2_u32(lo0, s0); hi0 = hmul2_u32(hi0, s0);
@@ -298,9 +305,35 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb) {
               if (nb < nbv) {
-                if (j & 1) mma_sp_m16n8k32<1>(acc[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
-                else       mma_sp_m16n8k32<0>(acc[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
+                if (post) {
+                  if (i == 0) {
+                    if (j & 1) mma_sp_m16n8k32_zero<1>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
+                    else       mma_sp_m16n8k32_zero<0>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
+                  } else {
+                    if (j & 1) mma_sp_m16n8k32<1>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
+                    else       mma_sp_m16n8k32<0>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
+                  }
+                } else {
+                  if (j & 1) mma_sp_m16n8k32<1>(acc[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
+                  else       mma_sp_m16n8k32<0>(acc[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
+                }
               }
+            }
+          }
+        }
+      }
+      if (post && ks * KS + kq * SPW < slabs && col_ok) {
+        // A scale group is whole or absent (K is a multiple of 128), so slab 0 of the group decides.
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&scs[j]));
+#pragma unroll
+          for (int nb = 0; nb < NB; ++nb) {
+            if (nb < nbv) {
+              acc[j][nb][0] = fmaf(accg[j][nb][0], sf.x, acc[j][nb][0]);
+              acc[j][nb][1] = fmaf(accg[j][nb][1], sf.x, acc[j][nb][1]);
+              acc[j][nb][2] = fmaf(accg[j][nb][2], sf.y, acc[j][nb][2]);
+              acc[j][nb][3] = fmaf(accg[j][nb][3], sf.y, acc[j][nb][3]);
             }
           }
         }
@@ -310,9 +343,12 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       if (++st == STAGES) { st = 0; phase ^= 1; }
     }
 
-    // Partner warps (same column block) own identical fragments: reduce element-wise in a fixed order.
+    // Partner warps (same column block) own identical fragments: reduce element-wise in a fixed
+    // order.  Barrier 1: partials written.  Barrier 2: partials consumed (the reading warps only
+    // arrive, the writing warps wait on it before their next write, so they run ahead meanwhile).
     if constexpr (KQ > 1) {
       if (kq > 0) {
+        if (!first_item) named_bar_sync(2, kConsumerThreads);
         float* dst = red + (kq - 1) * (16 * NB * SW * 32) + cb * 32 + lane;
 #pragma unroll
         for (int j = 0; j < 4; ++j)
@@ -333,7 +369,9 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 #pragma unroll
               for (int c = 0; c < 4; ++c) acc[j][nb][c] += src[((j * NB + nb) * 4 + c) * (SW * 32)];
         }
+        named_bar_arrive(2, kConsumerThreads);
       }
+      first_item = false;
     }
 
     if (kq == 0 && col_ok) {
@@ -392,7 +430,10 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         }
       }
     }
-    if constexpr (KQ > 1) named_bar_sync(1, kConsumerThreads);  // red[] may be rewritten after this
+  }
+  // Pair the last "consumed" arrival so that no barrier is left half way at exit.
+  if constexpr (KQ > 1) {
+    if (kq > 0 && !first_item) named_bar_sync(2, kConsumerThreads);
   }
 }
 

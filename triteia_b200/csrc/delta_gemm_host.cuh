@@ -97,8 +97,8 @@ static int launch_cfg(const GemmCall& c, const GemmArgs& a) {
   return cudaGetLastError() == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
 }
 
-using CfgT8 = GemmCfg<1, 2, 4, 8, 10>;
-using CfgT16 = GemmCfg<2, 2, 4, 8, 8>;
+using CfgT8 = GemmCfg<1, 2, 4, 16, 6>;
+using CfgT16 = GemmCfg<2, 2, 4, 16, 4>;
 using CfgT32 = GemmCfg<4, 2, 4, 8, 5>;
 using CfgT64 = GemmCfg<8, 4, 2, 4, 5>;
 static_assert(CfgT8::SMEM_ALLOC <= 232448 && CfgT16::SMEM_ALLOC <= 232448 && CfgT32::SMEM_ALLOC <= 232448 &&
