@@ -260,82 +260,99 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       mbar_wait(&full_bar[st], phase, dead);
       const uint8_t* sbase = smem + st * Cfg::STAGE_BYTES;
       const uint32_t x_s = smem_u32(sbase + Cfg::X_OFF);
-      const bool grouped = a.grouped != 0;
-      uint4 sc = make_uint4(0, 0, 0, 0);
-      if (grouped) {
-        const int grp = (kq * SPW) / 4;
-        sc = *reinterpret_cast<const uint4*>(sbase + Cfg::S_OFF + grp * (SW * 128) + cb * 128 + g8 * 16);
-      }
-      const uint32_t scs[4] = {sc.x, sc.y, sc.z, sc.w};
-      const bool post = kPostScale && grouped;
-      float accg[4][NB][4];   // levels of the current scale group (post-scale mode)
+
+      // One stage of this warp's slabs.  FULL: every slab of the stage exists (no per-slab test, so
+      // the four slabs form one straight-line block the compiler can interleave).  GROUPED selects
+      // the scale handling at compile time.
+      auto run_stage = [&](auto full_tag, auto grouped_tag) {
+        constexpr bool FULL = decltype(full_tag)::value;
+        constexpr bool GROUPED = decltype(grouped_tag)::value;
+        constexpr bool POST = kPostScale && GROUPED;
+        uint32_t scs[4] = {0, 0, 0, 0};
+        if constexpr (GROUPED) {
+          const int grp = (kq * SPW) / 4;
+          const uint4 sc = *reinterpret_cast<const uint4*>(sbase + Cfg::S_OFF + grp * (SW * 128) + cb * 128 + g8 * 16);
+          scs[0] = sc.x; scs[1] = sc.y; scs[2] = sc.z; scs[3] = sc.w;
+        }
+        float accg[4][NB][4];   // integer-level partial sums of the current scale group (POST)
 #pragma unroll
-      for (int i = 0; i < SPW; ++i) {
-        const int slab = kq * SPW + i;
-        if (ks * KS + slab < slabs && col_ok) {
-          const uint4 q4 = *reinterpret_cast<const uint4*>(sbase + q_off + slab * (Cfg::QB * 512));
-          const uint32_t e0 = *reinterpret_cast<const uint32_t*>(sbase + m_off + slab * (Cfg::QB * 256));
-          const uint32_t e1 = *reinterpret_cast<const uint32_t*>(sbase + m_off + slab * (Cfg::QB * 256) + 128);
-          // Activation fragments: matrix c of the ldmatrix is 16-byte K chunk c of the slab.
-          uint32_t bf[NB][4];
-          {
-            const int chunk = slab * 4 + (lane >> 3);          // 16-byte chunk inside the stage
-            const int bx = chunk >> 3, cw = chunk & 7, r8 = lane & 7;
+        for (int i = 0; i < SPW; ++i) {
+          const int slab = kq * SPW + i;
+          if (FULL || ks * KS + slab < slabs) {
+            const uint4 q4 = *reinterpret_cast<const uint4*>(sbase + q_off + slab * (Cfg::QB * 512));
+            const uint32_t e0 = *reinterpret_cast<const uint32_t*>(sbase + m_off + slab * (Cfg::QB * 256));
+            const uint32_t e1 = *reinterpret_cast<const uint32_t*>(sbase + m_off + slab * (Cfg::QB * 256) + 128);
+            // Activation fragments: matrix c of the ldmatrix is 16-byte K chunk c of the slab.
+            uint32_t bf[NB][4];
+            {
+              const int chunk = slab * 4 + (lane >> 3);          // 16-byte chunk inside the stage
+              const int bx = chunk >> 3, cw = chunk & 7, r8 = lane & 7;
 #pragma unroll
-            for (int nb = 0; nb < NB; ++nb) {
-              if (nb < nbv) {
-                const int row = nb * 8 + r8;
-                ldmatrix_x4(bf[nb], x_s + bx * Cfg::X_BOX_BYTES + row * 128 + ((cw ^ r8) << 4));
+              for (int nb = 0; nb < NB; ++nb) {
+                if (NB == 1 || nb < nbv) {
+                  const int row = nb * 8 + r8;
+                  ldmatrix_x4(bf[nb], x_s + bx * Cfg::X_BOX_BYTES + row * 128 + ((cw ^ r8) << 4));
+                }
               }
             }
-          }
-          const uint32_t qs[4] = {q4.x, q4.y, q4.z, q4.w};
+            const uint32_t qs[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint32_t lo0, hi0, lo1, hi1;
-            int4x4_to_half2x2(qs[j], lo0, hi0);
-            int4x4_to_half2x2(qs[j] >> 8, lo1, hi1);
-            if (grouped && !kPostScale) {
-              const uint32_t s0 = __byte_perm(scs[j], 0, 0x1010);  // scale of column j, both halves
-              const uint32_t s1 = __byte_perm(scs[j], 0, 0x3232);  // scale of column j + 4
-              lo0 = hmul2_u32(lo0, s0); hi0 = hmul2_u32(hi0, s0);
-              lo1 = hmul2_u32(lo1, s1); hi1 = hmul2_u32(hi1, s1);
-            }
-            const uint32_t e = (j < 2) ? e0 : e1;
+            for (int j = 0; j < 4; ++j) {
+              uint32_t lo0, hi0, lo1, hi1;
+              int4x4_to_half2x2(qs[j], lo0, hi0);
+              int4x4_to_half2x2(qs[j] >> 8, lo1, hi1);
+              if constexpr (GROUPED && !kPostScale) {
+                const uint32_t s0 = __byte_perm(scs[j], 0, 0x1010);  // scale of column j, both halves
+                const uint32_t s1 = __byte_perm(scs[j], 0, 0x3232);  // scale of column j + 4
+                lo0 = hmul2_u32(lo0, s0); hi0 = hmul2_u32(hi0, s0);
+                lo1 = hmul2_u32(lo1, s1); hi1 = hmul2_u32(hi1, s1);
+              }
+              const uint32_t e = (j < 2) ? e0 : e1;
 #pragma unroll
-            for (int nb = 0; nb < NB; ++nb) {
-              if (nb < nbv) {
-                if (post) {
-                  if (i == 0) {
-                    if (j & 1) mma_sp_m16n8k32_zero<1>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
-                    else       mma_sp_m16n8k32_zero<0>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
+              for (int nb = 0; nb < NB; ++nb) {
+                if (NB == 1 || nb < nbv) {
+                  if constexpr (POST) {
+                    if (i == 0) {
+                      if (j & 1) mma_sp_m16n8k32_zero<1>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
+                      else       mma_sp_m16n8k32_zero<0>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
+                    } else {
+                      if (j & 1) mma_sp_m16n8k32<1>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
+                      else       mma_sp_m16n8k32<0>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
+                    }
                   } else {
-                    if (j & 1) mma_sp_m16n8k32<1>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
-                    else       mma_sp_m16n8k32<0>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
+                    if (j & 1) mma_sp_m16n8k32<1>(acc[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
+                    else       mma_sp_m16n8k32<0>(acc[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
                   }
-                } else {
-                  if (j & 1) mma_sp_m16n8k32<1>(acc[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
-                  else       mma_sp_m16n8k32<0>(acc[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
                 }
               }
             }
           }
         }
-      }
-      if (post && ks * KS + kq * SPW < slabs && col_ok) {
-        // A scale group is whole or absent (K is a multiple of 128), so slab 0 of the group decides.
+        // A scale group is whole or absent (K is a multiple of 128): slab 0 of the warp decides.
+        if (POST && (FULL || ks * KS + kq * SPW < slabs)) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&scs[j]));
+          for (int j = 0; j < 4; ++j) {
+            const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&scs[j]));
 #pragma unroll
-          for (int nb = 0; nb < NB; ++nb) {
-            if (nb < nbv) {
-              acc[j][nb][0] = fmaf(accg[j][nb][0], sf.x, acc[j][nb][0]);
-              acc[j][nb][1] = fmaf(accg[j][nb][1], sf.x, acc[j][nb][1]);
-              acc[j][nb][2] = fmaf(accg[j][nb][2], sf.y, acc[j][nb][2]);
-              acc[j][nb][3] = fmaf(accg[j][nb][3], sf.y, acc[j][nb][3]);
+            for (int nb = 0; nb < NB; ++nb) {
+              if (NB == 1 || nb < nbv) {
+                acc[j][nb][0] = fmaf(accg[j][nb][0], sf.x, acc[j][nb][0]);
+                acc[j][nb][1] = fmaf(accg[j][nb][1], sf.x, acc[j][nb][1]);
+                acc[j][nb][2] = fmaf(accg[j][nb][2], sf.y, acc[j][nb][2]);
+                acc[j][nb][3] = fmaf(accg[j][nb][3], sf.y, acc[j][nb][3]);
+              }
             }
           }
+        }
+      };
+      if (col_ok) {
+        const bool full = (ks + 1) * KS <= slabs;
+        if (a.grouped) {
+          if (full) run_stage(std::true_type{}, std::true_type{});
+          else run_stage(std::false_type{}, std::true_type{});
+        } else {
+          if (full) run_stage(std::true_type{}, std::false_type{});
+          else run_stage(std::false_type{}, std::false_type{});
         }
       }
       __syncwarp();
