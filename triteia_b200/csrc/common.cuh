@@ -63,6 +63,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Shared-memory loads through a 32-bit shared address: constant offsets fold into the instruction.
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+
 // Bounded wait.  `dead` is a CTA-wide shared flag: once any wait of the CTA has expired every
 // later wait returns at once, so a broken pipeline drains in bounded time instead of hanging.
 // The launch's output is then garbage and g_device_status says so.

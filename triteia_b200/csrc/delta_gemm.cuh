@@ -18,10 +18,7 @@
 
 namespace trb {
 
-constexpr int kMaxSegments = 2048;
-constexpr int kConsumerWarps = 8;
-constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kGemmThreads = kConsumerThreads + 32;
+constexpr int kMaxSegments = 1024;
 
 enum SegMode { kSegList = 0, kSegSingle = 1, kSegIdentity = 2 };
 
@@ -49,9 +46,13 @@ struct GemmCfg {
   static constexpr int KQ = KQ_;          // warps sharing one column block (split over slabs)
   static constexpr int KS = KS_;          // 32-K slabs per pipeline stage
   static constexpr int STAGES = STAGES_;
-  static_assert(SW * KQ == kConsumerWarps, "eight consumer warps");
+  static constexpr int CW = SW * KQ;                // consumer warps
+  static constexpr int CTHREADS = CW * 32;
+  static constexpr int THREADS = CTHREADS + 32;     // + one producer warp
+  static_assert(CW == 8, "8 consumer warps");
+  static_assert(KQ == 1 || KQ == 2 || KQ == 4, "the K split must divide the four j's of a fragment");
   static_assert(KS % 4 == 0 && KS % KQ == 0 && KS % 2 == 0, "stage must hold whole scale groups");
-  static_assert((KS / KQ) <= 4 && 4 % (KS / KQ) == 0 && KS <= 16, "a warp's slabs of a stage share one scale group");
+  static_assert((KS / KQ) <= 4 && 4 % (KS / KQ) == 0 && KS <= 32, "a warp's slabs of a stage share one scale group");
   static constexpr int TT = NB * 8;                 // tokens per tile
   static constexpr int QB = SW >= 2 ? 2 : 1;        // column blocks per weight TMA box
   static constexpr int NQBOX = SW / QB;
@@ -66,7 +67,9 @@ struct GemmCfg {
   static constexpr int M_OFF = Q_OFF + Q_BYTES;
   static constexpr int S_OFF = M_OFF + M_BYTES;
   static constexpr int STAGE_BYTES = (S_OFF + S_BYTES + 1023) / 1024 * 1024;
-  static constexpr int RED_FLOATS = (KQ - 1) * 16 * NB * SW * 32;
+  static constexpr int RED_BUFS = KQ - 1;                     // partner-warp reduction buffers
+  static constexpr int RED_BUF_FLOATS = 16 * NB * SW * 32;
+  static constexpr int RED_FLOATS = RED_BUFS * RED_BUF_FLOATS;
   static constexpr int RED_OFF = STAGES * STAGE_BYTES;
   static constexpr int PREFIX_OFF = RED_OFF + RED_FLOATS * 4;
   static constexpr int BAR_OFF = PREFIX_OFF + (kMaxSegments + 2) * 4;
@@ -121,7 +124,7 @@ __device__ __forceinline__ WorkItem decode_item(const GemmArgs& a, const int* pr
 }
 
 template <class Cfg>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(Cfg::THREADS, 1)
 delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_q,
                   const __grid_constant__ CUtensorMap tm_m, const __grid_constant__ CUtensorMap tm_s,
                   const GemmArgs a) {
@@ -144,7 +147,7 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], kConsumerWarps);
+      mbar_init(&empty_bar[s], Cfg::CW);
     }
     *dead = 0;
     fence_mbar_init();
@@ -185,7 +188,7 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   const int k_stages = (slabs + KS - 1) / KS;
   const int groups = a.grouped ? a.K / 128 : 1;
 
-  if (warp == kConsumerWarps) {
+  if (warp == Cfg::CW) {
     // ------------------------------ producer ------------------------------
     if (lane == 0) {
       prefetch_tmap(&tm_x);
@@ -232,21 +235,68 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   const int g8 = lane >> 2;   // quad index: MMA row group / token inside a block of 8
   const int m4 = lane & 3;
   constexpr int SPW = KS / KQ;  // slabs per warp per stage
-  // With a whole scale group (4 slabs) per warp and stage, the group's integer levels are
-  // accumulated on their own and scaled once in fp32; otherwise every weight is scaled in fp16.
-  constexpr bool kPostScale = (SPW == 4);
+  // A warp's slabs of one stage lie inside one scale group, so their integer-level products are
+  // accumulated on their own and scaled once per stage in fp32 (small token tiles); large token
+  // tiles scale every weight in fp16 instead, which costs less than scaling many accumulators.
+  constexpr bool kPostScale = (NB <= 2);
+  constexpr bool kBulkLoad = (NB <= 2);
   const int box = cb / Cfg::QB, within = cb % Cfg::QB;
-  const uint32_t q_off = Cfg::Q_OFF + box * (KS * Cfg::QB * 512) + within * 512 + lane * 16;
-  const uint32_t m_off = Cfg::M_OFF + box * (KS * Cfg::QB * 256) + within * 256 + lane * 4;
+  // Per-lane byte offsets inside a stage, fixed for the whole kernel.
+  const uint32_t q_off = Cfg::Q_OFF + box * (KS * Cfg::QB * 512) + within * 512 + lane * 16 + kq * SPW * (Cfg::QB * 512);
+  const uint32_t m_off = Cfg::M_OFF + box * (KS * Cfg::QB * 256) + within * 256 + lane * 4 + kq * SPW * (Cfg::QB * 256);
+  const uint32_t s_off = Cfg::S_OFF + ((kq * SPW) / 4) * (SW * 128) + cb * 128 + g8 * 16;
+  // ldmatrix row address of slab i of this warp: 16-byte chunk 4*slab + lane/8 of the stage's K
+  // range lives in activation box chunk/8 at swizzled chunk position (chunk%8) ^ (row%8).
+  uint32_t x_off[SPW];
+#pragma unroll
+  for (int i = 0; i < SPW; ++i) {
+    const int chunk = (kq * SPW + i) * 4 + (lane >> 3);
+    x_off[i] = Cfg::X_OFF + (chunk >> 3) * Cfg::X_BOX_BYTES + (lane & 7) * 128 + ((((chunk & 7) ^ (lane & 7))) << 4);
+  }
+  const uint32_t smem_base = smem_u32(smem);
 
   int st = 0;
   uint32_t phase = 0;
   bool first_item = true;
+  constexpr int JW = 4 / KQ;   // accumulator column pairs (j) that each partner warp finishes
+  WorkItem w_next{};
+  if ((int)blockIdx.x < n_items) w_next = decode_item<Cfg>(a, prefix, n_seg, n_stripes, blockIdx.x);
   for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-    const WorkItem w = decode_item<Cfg>(a, prefix, n_seg, n_stripes, item);
+    const WorkItem w = w_next;
+    // Descriptor of the next item: its global loads are in flight during this item's K loop.
+    if (item + (int)gridDim.x < n_items) w_next = decode_item<Cfg>(a, prefix, n_seg, n_stripes, item + gridDim.x);
     if (!w.ok) continue;
     const int nbv = (w.valid + 7) >> 3;
     const bool col_ok = w.col0 + cb * 64 < a.N;
+
+    // Epilogue operands fetched now, used after the K loop: output rows of this lane's tokens and
+    // (per-channel mode) the scales of the two columns of each j this warp finishes.
+    const int colb = w.col0 + cb * 64 + g8 * 8;
+    int orow[NB][2];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int t = nb * 8 + 2 * m4 + h;
+        int r = -1;
+        if (t < w.valid) {
+          r = w.row0 + t;
+          if (a.row_map) r = a.row_map[r];
+          if (r < 0 || r >= a.rows) r = -1;
+        }
+        orow[nb][h] = r;
+      }
+    float sfa[JW], sfb[JW];
+#pragma unroll
+    for (int jj = 0; jj < JW; ++jj) {
+      sfa[jj] = 1.f;
+      sfb[jj] = 1.f;
+      if (!a.grouped && col_ok) {
+        const __half* sp = a.scales + (size_t)w.delta * a.N + colb + kq * JW + jj;
+        sfa[jj] = __half2float(sp[0]);
+        sfb[jj] = __half2float(sp[4]);
+      }
+    }
 
     float acc[4][NB][4];
 #pragma unroll
@@ -258,8 +308,7 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 
     for (int ks = 0; ks < k_stages; ++ks) {
       mbar_wait(&full_bar[st], phase, dead);
-      const uint8_t* sbase = smem + st * Cfg::STAGE_BYTES;
-      const uint32_t x_s = smem_u32(sbase + Cfg::X_OFF);
+      const uint32_t sb = smem_base + st * Cfg::STAGE_BYTES;
 
       // One stage of this warp's slabs.  FULL: every slab of the stage exists (no per-slab test, so
       // the four slabs form one straight-line block the compiler can interleave).  GROUPED selects
@@ -270,63 +319,85 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         constexpr bool POST = kPostScale && GROUPED;
         uint32_t scs[4] = {0, 0, 0, 0};
         if constexpr (GROUPED) {
-          const int grp = (kq * SPW) / 4;
-          const uint4 sc = *reinterpret_cast<const uint4*>(sbase + Cfg::S_OFF + grp * (SW * 128) + cb * 128 + g8 * 16);
+          const uint4 sc = lds128(sb + s_off);
           scs[0] = sc.x; scs[1] = sc.y; scs[2] = sc.z; scs[3] = sc.w;
         }
-        float accg[4][NB][4];   // integer-level partial sums of the current scale group (POST)
+        float accg[4][NB][4];   // integer-level partial sums of this warp's slabs (POST)
+
+        // MMAs of one slab from registers: q4 = the lane's four weight words, e0/e1 = its two
+        // metadata words, bf = activation fragments per token block.
+        auto compute_slab = [&](int i, const uint4& q4, uint32_t e0, uint32_t e1, const uint32_t (&bf)[NB][4]) {
+          const uint32_t qs[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
-        for (int i = 0; i < SPW; ++i) {
-          const int slab = kq * SPW + i;
-          if (FULL || ks * KS + slab < slabs) {
-            const uint4 q4 = *reinterpret_cast<const uint4*>(sbase + q_off + slab * (Cfg::QB * 512));
-            const uint32_t e0 = *reinterpret_cast<const uint32_t*>(sbase + m_off + slab * (Cfg::QB * 256));
-            const uint32_t e1 = *reinterpret_cast<const uint32_t*>(sbase + m_off + slab * (Cfg::QB * 256) + 128);
-            // Activation fragments: matrix c of the ldmatrix is 16-byte K chunk c of the slab.
-            uint32_t bf[NB][4];
-            {
-              const int chunk = slab * 4 + (lane >> 3);          // 16-byte chunk inside the stage
-              const int bx = chunk >> 3, cw = chunk & 7, r8 = lane & 7;
-#pragma unroll
-              for (int nb = 0; nb < NB; ++nb) {
-                if (NB == 1 || nb < nbv) {
-                  const int row = nb * 8 + r8;
-                  ldmatrix_x4(bf[nb], x_s + bx * Cfg::X_BOX_BYTES + row * 128 + ((cw ^ r8) << 4));
-                }
-              }
+          for (int j = 0; j < 4; ++j) {
+            uint32_t lo0, hi0, lo1, hi1;
+            int4x4_to_half2x2(qs[j], lo0, hi0);
+            int4x4_to_half2x2(qs[j] >> 8, lo1, hi1);
+            if constexpr (GROUPED && !kPostScale) {
+              const uint32_t s0 = __byte_perm(scs[j], 0, 0x1010);  // scale of column j, both halves
+              const uint32_t s1 = __byte_perm(scs[j], 0, 0x3232);  // scale of column j + 4
+              lo0 = hmul2_u32(lo0, s0); hi0 = hmul2_u32(hi0, s0);
+              lo1 = hmul2_u32(lo1, s1); hi1 = hmul2_u32(hi1, s1);
             }
-            const uint32_t qs[4] = {q4.x, q4.y, q4.z, q4.w};
+            const uint32_t e = (j < 2) ? e0 : e1;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              uint32_t lo0, hi0, lo1, hi1;
-              int4x4_to_half2x2(qs[j], lo0, hi0);
-              int4x4_to_half2x2(qs[j] >> 8, lo1, hi1);
-              if constexpr (GROUPED && !kPostScale) {
-                const uint32_t s0 = __byte_perm(scs[j], 0, 0x1010);  // scale of column j, both halves
-                const uint32_t s1 = __byte_perm(scs[j], 0, 0x3232);  // scale of column j + 4
-                lo0 = hmul2_u32(lo0, s0); hi0 = hmul2_u32(hi0, s0);
-                lo1 = hmul2_u32(lo1, s1); hi1 = hmul2_u32(hi1, s1);
-              }
-              const uint32_t e = (j < 2) ? e0 : e1;
-#pragma unroll
-              for (int nb = 0; nb < NB; ++nb) {
-                if (NB == 1 || nb < nbv) {
-                  if constexpr (POST) {
-                    if (i == 0) {
-                      if (j & 1) mma_sp_m16n8k32_zero<1>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
-                      else       mma_sp_m16n8k32_zero<0>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
-                    } else {
-                      if (j & 1) mma_sp_m16n8k32<1>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
-                      else       mma_sp_m16n8k32<0>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
-                    }
+            for (int nb = 0; nb < NB; ++nb) {
+              if (NB == 1 || nb < nbv) {
+                if constexpr (POST) {
+                  if (i == 0) {
+                    if (j & 1) mma_sp_m16n8k32_zero<1>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
+                    else       mma_sp_m16n8k32_zero<0>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
                   } else {
-                    if (j & 1) mma_sp_m16n8k32<1>(acc[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
-                    else       mma_sp_m16n8k32<0>(acc[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
+                    if (j & 1) mma_sp_m16n8k32<1>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
+                    else       mma_sp_m16n8k32<0>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
                   }
+                } else {
+                  if (j & 1) mma_sp_m16n8k32<1>(acc[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
+                  else       mma_sp_m16n8k32<0>(acc[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
                 }
               }
             }
           }
+        };
+
+        if constexpr (kBulkLoad) {
+          // Small token tiles: pull the warp's whole share of the stage into registers, hand the
+          // stage back to the producer at once (the arrive is a release: the loads above are
+          // performed before it is observed), then do the math from registers.
+          uint4 q4[SPW];
+          uint32_t e0[SPW], e1[SPW], bf[SPW][NB][4];
+#pragma unroll
+          for (int i = 0; i < SPW; ++i) {
+            if (FULL || ks * KS + kq * SPW + i < slabs) {
+              q4[i] = lds128(sb + q_off + i * (Cfg::QB * 512));
+              e0[i] = lds32(sb + m_off + i * (Cfg::QB * 256));
+              e1[i] = lds32(sb + m_off + i * (Cfg::QB * 256) + 128);
+#pragma unroll
+              for (int nb = 0; nb < NB; ++nb)
+                if (NB == 1 || nb < nbv) ldmatrix_x4(bf[i][nb], sb + x_off[i] + nb * 1024);
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&empty_bar[st]);
+#pragma unroll
+          for (int i = 0; i < SPW; ++i)
+            if (FULL || ks * KS + kq * SPW + i < slabs) compute_slab(i, q4[i], e0[i], e1[i], bf[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < SPW; ++i) {
+            if (FULL || ks * KS + kq * SPW + i < slabs) {
+              const uint4 q4 = lds128(sb + q_off + i * (Cfg::QB * 512));
+              const uint32_t e0 = lds32(sb + m_off + i * (Cfg::QB * 256));
+              const uint32_t e1 = lds32(sb + m_off + i * (Cfg::QB * 256) + 128);
+              uint32_t bf[NB][4];
+#pragma unroll
+              for (int nb = 0; nb < NB; ++nb)
+                if (NB == 1 || nb < nbv) ldmatrix_x4(bf[nb], sb + x_off[i] + nb * 1024);
+              compute_slab(i, q4, e0, e1, bf);
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&empty_bar[st]);
         }
         // A scale group is whole or absent (K is a multiple of 128): slab 0 of the warp decides.
         if (POST && (FULL || ks * KS + kq * SPW < slabs)) {
@@ -354,103 +425,77 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
           if (full) run_stage(std::true_type{}, std::false_type{});
           else run_stage(std::false_type{}, std::false_type{});
         }
+      } else {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[st]);
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&empty_bar[st]);
       if (++st == STAGES) { st = 0; phase ^= 1; }
     }
 
-    // Partner warps (same column block) own identical fragments: reduce element-wise in a fixed
-    // order.  Barrier 1: partials written.  Barrier 2: partials consumed (the reading warps only
-    // arrive, the writing warps wait on it before their next write, so they run ahead meanwhile).
+    // Partner warps (same column block) own identical fragments.  Each of them finishes the j's
+    // [kq*JW, (kq+1)*JW): it hands its partial sums of the other j's to their owners through shared
+    // memory, adds the partners' partials to its own in a fixed order, and writes its columns.
+    // Barrier 2 (before the stores) keeps an item's partials until every reader of the previous
+    // item is done; barrier 1 separates stores from loads.
     if constexpr (KQ > 1) {
-      if (kq > 0) {
-        if (!first_item) named_bar_sync(2, kConsumerThreads);
-        float* dst = red + (kq - 1) * (16 * NB * SW * 32) + cb * 32 + lane;
+      constexpr int CT = Cfg::CTHREADS;
+      constexpr int LANES = SW * 32;
+      if (!first_item) named_bar_sync(2, CT);
+      first_item = false;
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+      for (int j = 0; j < 4; ++j) {
+        const int owner = j / JW;
+        if (owner != kq) {
+          const int slot = kq < owner ? kq : kq - 1;
+          float* dst = red + (((owner * (KQ - 1) + slot) * JW + (j % JW)) * NB * 4) * LANES + cb * 32 + lane;
 #pragma unroll
           for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
-            for (int c = 0; c < 4; ++c) dst[((j * NB + nb) * 4 + c) * (SW * 32)] = acc[j][nb][c];
+            for (int c = 0; c < 4; ++c) dst[(nb * 4 + c) * LANES] = acc[j][nb][c];
+        }
       }
-      named_bar_sync(1, kConsumerThreads);
-      if (kq == 0) {
+      named_bar_sync(1, CT);
 #pragma unroll
-        for (int p = 0; p < KQ - 1; ++p) {
-          const float* src = red + p * (16 * NB * SW * 32) + cb * 32 + lane;
+      for (int j = 0; j < 4; ++j) {
+        if (j / JW == kq) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
+          for (int slot = 0; slot < KQ - 1; ++slot) {
+            const float* src = red + (((kq * (KQ - 1) + slot) * JW + (j % JW)) * NB * 4) * LANES + cb * 32 + lane;
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
-              for (int c = 0; c < 4; ++c) acc[j][nb][c] += src[((j * NB + nb) * 4 + c) * (SW * 32)];
+              for (int c = 0; c < 4; ++c) acc[j][nb][c] += src[(nb * 4 + c) * LANES];
+          }
         }
-        named_bar_arrive(2, kConsumerThreads);
       }
-      first_item = false;
     }
 
-    if (kq == 0 && col_ok) {
-      // This thread owns columns col..col+7 (col + j from c = 0,1 and col + 4 + j from c = 2,3)
-      // for tokens nb*8 + 2*m4 and + 1.
-      const int col = w.col0 + cb * 64 + g8 * 8;
-      float sf[8];
-      if (!a.grouped) {
-        const uint4 sv = *reinterpret_cast<const uint4*>(a.scales + (size_t)w.delta * a.N + col);
-        const __half2* sh = reinterpret_cast<const __half2*>(&sv);
+    if (col_ok) {
+      // acc[j][nb][h] is (column colb + j, token nb*8 + 2*m4 + h); acc[j][nb][2 + h] is column colb + 4 + j.
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 f = __half22float2(sh[i]);
-          sf[2 * i] = f.x;
-          sf[2 * i + 1] = f.y;
-        }
-      } else {
+      for (int j = 0; j < 4; ++j) {
+        if (j / JW == kq) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) sf[i] = 1.f;
-      }
+          for (int nb = 0; nb < NB; ++nb) {
 #pragma unroll
-      for (int nb = 0; nb < NB; ++nb) {
-        if (nb < nbv) {
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int t = nb * 8 + 2 * m4 + h;
-            if (t < w.valid) {
-              const int xr = w.row0 + t;
-              const int orow = a.row_map ? a.row_map[xr] : xr;
-              if (orow >= 0 && orow < a.rows) {
-                float v[8];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  v[j] = acc[j][nb][h] * sf[j];
-                  v[4 + j] = acc[j][nb][2 + h] * sf[4 + j];
-                }
-                uint4* dst = reinterpret_cast<uint4*>(a.y + (size_t)orow * a.N + col);
+            for (int h = 0; h < 2; ++h) {
+              const int r = orow[nb][h];
+              if (r >= 0 && (NB == 1 || nb < nbv)) {
+                __half* yp = a.y + (size_t)r * a.N + colb + j;
+                float va = acc[j][nb][h] * sfa[j % JW];
+                float vb = acc[j][nb][2 + h] * sfb[j % JW];
                 if (a.accumulate) {
-                  const uint4 old = *dst;
-                  const __half2* oh = reinterpret_cast<const __half2*>(&old);
-#pragma unroll
-                  for (int i = 0; i < 4; ++i) {
-                    const float2 f = __half22float2(oh[i]);
-                    v[2 * i] += f.x;
-                    v[2 * i + 1] += f.y;
-                  }
+                  va += __half2float(yp[0]);
+                  vb += __half2float(yp[4]);
                 }
-                uint4 out;
-                __half2* ob = reinterpret_cast<__half2*>(&out);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) ob[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
-                *dst = out;
+                yp[0] = __float2half_rn(va);
+                yp[4] = __float2half_rn(vb);
               }
             }
           }
         }
       }
     }
-  }
-  // Pair the last "consumed" arrival so that no barrier is left half way at exit.
-  if constexpr (KQ > 1) {
-    if (kq > 0 && !first_item) named_bar_sync(2, kConsumerThreads);
   }
 }
 

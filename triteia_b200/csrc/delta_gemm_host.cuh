@@ -93,7 +93,7 @@ static int launch_cfg(const GemmCall& c, const GemmArgs& a) {
   else max_tiles = (long long)a.rows / Cfg::TT + (a.n_seg_ptr ? kMaxSegments : a.n_seg);
   const long long max_items = max_tiles * n_stripes;
   if (max_items < grid) grid = (int)(max_items > 0 ? max_items : 1);
-  delta_gemm_kernel<Cfg><<<grid, kGemmThreads, Cfg::SMEM_ALLOC, c.stream>>>(tx, tq, tm, ts, a);
+  delta_gemm_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_ALLOC, c.stream>>>(tx, tq, tm, ts, a);
   return cudaGetLastError() == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
 }
 
