@@ -108,6 +108,24 @@ int trb_sbmm_indexed(const void* x, const void* qweights, const void* metas, con
                      int num_deltas, int index_offset, int groupsize, int accumulate,
                      void* scratch, size_t scratch_bytes, int dev, void* stream);
 
+/* trb_sbmm_indexed without a scratch argument, for hosts that cannot allocate device memory for
+ * the library (a server whose arena owns all of HBM and offers foreign code no allocator, a plugin
+ * contract that bans cudaMalloc after start-up because it stalls the whole device).  The working
+ * memory is a fixed array inside the library image: trb_sbmm_indexed_static_capacity() bytes
+ * (4 MiB + 64 KiB), held by every GPU that uses the library until the process exits.  A request
+ * whose trb_sbmm_indexed_scratch_bytes() exceeds the capacity returns TRB_ERR_SCRATCH and launches
+ * nothing (fits e.g. 256 tokens x K 8192, or 512 tokens x K 4096).  Calls no allocator of any kind.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that
+ * device current); make that first call before any stream capture begins.  All calls on a device
+ * share the one array and it keeps the previous call's contents: nothing in it needs clearing
+ * between calls, but two calls that overlap on the GPU (different streams, no ordering) race.
+ * This entry point has no counterpart in the reference. */
+size_t trb_sbmm_indexed_static_capacity(void);
+int trb_sbmm_indexed_static(const void* x, const void* qweights, const void* metas,
+                            const void* scales, const void* indices, void* y, int num_tokens,
+                            int prob_m, int prob_k, int num_deltas, int index_offset, int groupsize,
+                            int accumulate, int dev, void* stream);
+
 /* Dense fp16 weight [K, N] from a packed delta (W = fp16(level) * fp16(scale), rounded once).
  * The on-GPU statement of the format; bit-exact against the CPU decoder.  No counterpart
  * kernel in the reference (its decoder is torch code,

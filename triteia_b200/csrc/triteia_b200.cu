@@ -8,3 +8,4 @@
 #include "delta_gemm_host.cuh"
 #include "unpack.cuh"
 #include "lora.cuh"
+#include "no_alloc.cuh"
