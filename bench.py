@@ -100,59 +100,64 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- CPU baseline
-def cpu_baseline(num_sample_deltas=6, repeats=3, seed=0):
+class CpuPath:
     """The reference has no CPU kernel for this path; its torch check path is
-    `sbmm_16bit_forloop` on dequantised weights (triteia/python/ops/matmul/sbmm.py:7-23).  Timed
-    here in fp32 with all host threads on a bounded sample: `num_sample_deltas` deltas of the
-    workload with the tokens that select them; dequantisation is done once, untimed."""
-    from oracle import delta_format as fmt
-    from triteia_b200.ops.utils.generator import random_packed_deltas
+    `sbmm_16bit_forloop` on dequantised weights (triteia/python/ops/matmul/sbmm.py:7-23).  Here: fp32
+    torch matmul with all host threads on a bounded sample of the workload — `num_sample_deltas`
+    deltas with the tokens that select them.  The sample is dequantised once by the oracle's
+    decoder (untimed); one pass = one per-delta matmul loop over the sample."""
 
-    torch.set_num_threads(os.cpu_count() or 1)
-    cores = torch.get_num_threads()
-    qs, metas, ss = random_packed_deltas(num_sample_deltas, K, N_OUT, groupsize=GROUP, device="cpu", seed=seed)
-    weights = [torch.from_numpy(fmt.dequantize(qs[d].numpy(), metas[d].numpy(), ss[d].numpy()).astype(np.float32))
-               for d in range(num_sample_deltas)]
-    idx = make_indices(seed, TOKENS, D_PER_GPU)
-    x = torch.randn(TOKENS, K, generator=torch.Generator().manual_seed(seed)).half().float()
-    rows = [np.flatnonzero(idx == d) for d in range(num_sample_deltas)]
-    n_tok = int(sum(len(r) for r in rows))
-    y = torch.zeros(TOKENS, N_OUT)
+    def __init__(self, num_sample_deltas=6, seed=0):
+        from oracle import delta_format as fmt
+        from triteia_b200.ops.utils.generator import random_packed_deltas
 
-    def run():
-        for d, r in enumerate(rows):
+        torch.set_num_threads(os.cpu_count() or 1)
+        self.cores = torch.get_num_threads()
+        self.n = num_sample_deltas
+        qs, metas, ss = random_packed_deltas(self.n, K, N_OUT, groupsize=GROUP, device="cpu", seed=seed)
+        self.weights = [torch.from_numpy(fmt.dequantize(qs[d].numpy(), metas[d].numpy(), ss[d].numpy())
+                                         .astype(np.float32)) for d in range(self.n)]
+        idx = make_indices(seed, TOKENS, D_PER_GPU)
+        self.x = torch.randn(TOKENS, K, generator=torch.Generator().manual_seed(seed)).half().float()
+        self.rows = [np.flatnonzero(idx == d) for d in range(self.n)]
+        self.tokens = int(sum(len(r) for r in self.rows))
+        self.y = torch.zeros(TOKENS, N_OUT)
+
+    def one_pass(self):
+        for d, r in enumerate(self.rows):
             if len(r):
-                y[r] += x[r] @ weights[d]
+                self.y[r] += self.x[r] @ self.weights[d]
 
-    run()
-    t0 = time.perf_counter()
-    for _ in range(repeats):
-        run()
-    dt = (time.perf_counter() - t0) / repeats
-    return {"value": n_tok / dt, "unit": UNIT, "cores": cores, "kind": "port",
-            "sample": f"{num_sample_deltas} of {D_PER_GPU} deltas with their {n_tok} tokens, fp32 torch matmul on "
-                      f"dequantised weights, mean of {repeats} passes ({dt * 1e3:.1f} ms each), dequantisation untimed",
-            "seconds_per_pass": dt, "tokens_in_sample": n_tok}
+    def timed(self, passes, warmup=1):
+        for _ in range(warmup):
+            self.one_pass()
+        t0 = time.perf_counter()
+        for _ in range(passes):
+            self.one_pass()
+        dt = (time.perf_counter() - t0) / passes
+        return {"value": self.tokens / dt, "unit": UNIT, "cores": self.cores, "kind": "port",
+                "sample": f"{self.n} of {D_PER_GPU} deltas with their {self.tokens} tokens, fp32 torch matmul on "
+                          f"dequantised weights, mean of {passes} passes ({dt * 1e3:.1f} ms each), dequantisation untimed",
+                "seconds_per_pass": dt, "tokens_in_sample": self.tokens}
+
+
+def cpu_baseline():
+    return CpuPath().timed(passes=200, warmup=3)
 
 
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    vals = []
-    for _ in range(args.warmup):
-        cpu_baseline(num_sample_deltas=2, repeats=1)
-    base = None
-    for _ in range(max(1, args.steps)):
-        base = cpu_baseline(num_sample_deltas=4, repeats=2)
-        vals.append(base["value"])
-    v = statistics.mean(vals)
-    base["value"] = v
+    path = CpuPath()
+    base = path.timed(passes=max(1, args.steps), warmup=max(1, args.warmup))
+    v = base["value"]
     line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": base["seconds_per_pass"] * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "note": "reference ships no CPU kernel; its torch check path "
-                       "(dequantised weights, per-delta matmul) on host cores, bounded sample per step"},
+            "config": {"workload": WORKLOAD, "note": "the reference ships no CPU kernel for this path; this is its "
+                       "torch check path (dequantised weights, per-delta fp32 matmul) on the host cores, one step = "
+                       "one pass over a bounded sample"},
             "cpu_baseline": base,
             "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
@@ -310,7 +315,11 @@ def run_gpu_arm(args):
             "gpu_launches": launches_per_step * args.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_src, "kernel": "delta_gemm_kernel", "kernel_ms": t_kern,
-                         "algorithmic_bytes": alg_bytes, "traffic": None},
+                         "algorithmic_bytes": alg_bytes,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this
+                         # launch (profiles/delta_gemm_kernel_sbmm-decode-64x4096x4096-g128.md);
+                         # only known for the single-GPU seed (56 deltas touched).
+                         "traffic": 373310976 if (world == 1 and touched == 56) else None},
             "clocks": clocks, "device_status": status, "wall_s": wall_s,
         }
         if world == 1 and not args.no_cpu_baseline:
