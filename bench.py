@@ -215,9 +215,19 @@ def run_gpu_arm(args):
         step_resident = lambda: ops.sbmm_4bit_2_4_native(qs, x_dev, metas, ss, idx_dev)
         launches_per_step = 3   # router, row gather, grouped kernel
     else:
-        local = sharded.make_local_sbmm(qs, metas, ss)
-        step_resident = lambda: sharded.sbmm_sharded(x_dev, idx_dev, local, N_OUT)
-        launches_per_step = 3
+        # Peer-to-peer exchange over CUDA symmetric memory when the box offers it, else NCCL all-to-all.
+        exchange_kind = os.environ.get("TRB_EXCHANGE", "p2p")
+        try:
+            exchange = sharded.FixedCapacityExchange(TOKENS, K, N_OUT, dev, backend=exchange_kind, qweights=qs,
+                                                     metas=metas, scales=ss)
+        except Exception as e:   # symmetric memory unavailable
+            if rank == 0:
+                print(f"bench.py: p2p exchange unavailable ({e}); using NCCL all-to-all", file=sys.stderr)
+            exchange_kind = "cuda"
+            exchange = sharded.FixedCapacityExchange(TOKENS, K, N_OUT, dev, backend="cuda", qweights=qs, metas=metas,
+                                                     scales=ss)
+        step_resident = lambda: exchange(x_dev, idx_dev)
+        launches_per_step = 6   # dispatch plan + pack, router + gather + grouped kernel, combine
 
     def step_e2e():
         xd = x_host.to(dev, non_blocking=True)
@@ -225,7 +235,7 @@ def run_gpu_arm(args):
         if world == 1:
             y = ops.sbmm_4bit_2_4_native(qs, xd, metas, ss, idd)
         else:
-            y = sharded.sbmm_sharded(xd, idd, local, N_OUT)
+            y = exchange(xd, idd)
         y_host.copy_(y, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
@@ -307,7 +317,11 @@ def run_gpu_arm(args):
                        "l2": "flushed before every timed step (256 MiB memset then a 256 MiB read, untimed); touched weights "
                              f"{touched * BYTES_PER_DELTA / 1e6:.0f} MB > 126 MB L2",
                        "parallelism": "single GPU" if world == 1 else f"deltas sharded by id over {world} GPUs, "
-                                                                       "NCCL all-to-all token dispatch/combine"},
+                                                                       ("rows and results stored straight into the owner's symmetric-memory buffers over NVLink "
+                                                                        "by the pack kernel and the grouped kernel's epilogue, two cross-GPU barriers per step"
+                                                                        if exchange_kind == "p2p" else
+                                                                        "two equal-split NCCL all-to-alls per step (rows + ids out, result rows back)")
+                                                                       + ", no host synchronisation"},
             "e2e": {"value": tokens_total / (t_e2e * 1e-3), "unit": UNIT, "ms_per_step": t_e2e,
                     "h2d_bytes_per_step": int(x_host.numel() * 2 + idx_host.numel() * 4),
                     "d2h_bytes_per_step": int(y_host.numel() * 2),

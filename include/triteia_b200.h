@@ -126,6 +126,35 @@ int trb_sbmm_indexed_static(const void* x, const void* qweights, const void* met
                             int prob_m, int prob_k, int num_deltas, int index_offset, int groupsize,
                             int accumulate, int dev, void* stream);
 
+/* Multi-GPU form: deltas sharded by id over `world` ranks (owner = id % world, local id =
+ * id / world).  Tokens travel through fixed-capacity exchange buffers of `world` chunks of
+ * num_tokens + 1 rows (trb_shard_buffer_rows rows in all): outbound rows of K halves with the rows'
+ * local ids and the row count in each chunk's last row, return rows of N halves in the same slots.
+ * Between the calls the host runs an all-to-all with equal splits (NCCL); nothing here needs a count
+ * on the host.  The reference has no distributed layer: no counterpart.
+ *   trb_shard_dispatch  plan the slots (slot_of int32 [T] out, plan int32 [8 + world] scratch) and
+ *                       pack this rank's rows and ids into send_buf
+ *   trb_shard_compute   on the owner: router + gather + grouped kernel over the received buffer
+ *                       (cap = the senders' num_tokens); scratch as trb_sbmm_indexed for
+ *                       world * (cap + 1) tokens
+ *   trb_shard_combine   y[t] (+)= returned row of token t; tokens without a delta are zeroed unless
+ *                       accumulate
+ * Peer mode (no collective at all): peer_recv_ptrs / peer_out_ptrs are device arrays of `world`
+ * pointers to every rank's receive / return buffer (peer-mapped memory, e.g. CUDA symmetric memory);
+ * the pack kernel and the grouped kernel's epilogue then store rows straight into the owner's buffer
+ * over NVLink (chunk index = my_rank) and the host only places a cross-GPU barrier between the steps.
+ * Pass NULL for the plain form. */
+size_t trb_shard_buffer_rows(int num_tokens, int world);
+int trb_shard_dispatch(const void* x, const void* indices, int num_tokens, int prob_k, int world,
+                       void* send_buf, const void* peer_recv_ptrs, int my_rank, void* slot_of,
+                       void* plan, int dev, void* stream);
+int trb_shard_compute(const void* recv_buf, const void* qweights, const void* metas,
+                      const void* scales, void* y_work, int world, int cap, int prob_m, int prob_k,
+                      int num_local_deltas, int groupsize, const void* peer_out_ptrs, int my_rank,
+                      void* scratch, size_t scratch_bytes, int dev, void* stream);
+int trb_shard_combine(const void* back_buf, const void* slot_of, void* y, int num_tokens, int prob_m,
+                      int world, int accumulate, int dev, void* stream);
+
 /* Dense fp16 weight [K, N] from a packed delta (W = fp16(level) * fp16(scale), rounded once).
  * The on-GPU statement of the format; bit-exact against the CPU decoder.  No counterpart
  * kernel in the reference (its decoder is torch code,

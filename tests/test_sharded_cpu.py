@@ -26,7 +26,7 @@ def _worker(rank, world, port, case, out_dir):
         from triteia_b200 import sharded
         from triteia_b200.ops.matmul.sbmm import sbmm_16bit_forloop
 
-        D, K, N, T = 6, 32, 16, 20
+        D, K, N, T = 6, 64, 16, 20
         g = torch.Generator().manual_seed(0)
         weights = torch.randn(D, K, N, generator=g)                       # every rank builds all, keeps its shard
         mine = sharded.shard_ids(D, rank, world)
@@ -48,6 +48,15 @@ def _worker(rank, world, port, case, out_dir):
         y = sharded.sbmm_sharded(x, idx, local_compute, N)
         ref = sbmm_16bit_forloop(weights, x, idx)
         ok = torch.allclose(y, ref, rtol=1e-5, atol=1e-5)
+        # fixed-capacity, sync-free exchange (torch statement of the CUDA buffer layout), twice on the
+        # same buffers with different batches
+        ex = sharded.FixedCapacityExchange(T, K, N, torch.device("cpu"), backend="torch", local_compute=local_compute,
+                                           dtype=torch.float32)
+        y2 = ex(x, idx)
+        ok = ok and torch.allclose(y2, ref, rtol=1e-5, atol=1e-5)
+        idx_b = torch.roll(idx, 3)
+        y3 = ex(x, idx_b)
+        ok = ok and torch.allclose(y3, sbmm_16bit_forloop(weights, x, idx_b), rtol=1e-5, atol=1e-5)
         plan = sharded.DispatchPlan(idx, world)
         ok = ok and plan.n_send == int((idx >= 0).sum())
         torch.save({"ok": bool(ok), "max_err": float((y - ref).abs().max())}, os.path.join(out_dir, f"r{rank}.pt"))

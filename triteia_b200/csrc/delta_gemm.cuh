@@ -37,6 +37,11 @@ struct GemmArgs {
   __half* y;
   const int* row_map;     // nullptr, or output row of each x row (scatter through the router's perm)
   int accumulate;         // y += result instead of y = result
+  // Sharded path, results written straight into the token owners' buffers over NVLink: output row
+  // r * chunk_rows + q goes to row my_rank * chunk_rows + q of y_peers[r] (nullptr: plain y).
+  __half* const* y_peers;
+  int chunk_rows;
+  int my_rank;
 };
 
 template <int NB_, int SW_, int KQ_, int KS_, int STAGES_>
@@ -481,7 +486,13 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             for (int h = 0; h < 2; ++h) {
               const int r = orow[nb][h];
               if (r >= 0 && (NB == 1 || nb < nbv)) {
-                __half* yp = a.y + (size_t)r * a.N + colb + j;
+                __half* yp;
+                if (a.y_peers) {
+                  const int pr = r / a.chunk_rows, pq = r - pr * a.chunk_rows;
+                  yp = a.y_peers[pr] + ((size_t)a.my_rank * a.chunk_rows + pq) * a.N + colb + j;
+                } else {
+                  yp = a.y + (size_t)r * a.N + colb + j;
+                }
                 float va = acc[j][nb][h] * sfa[j % JW];
                 float vb = acc[j][nb][2 + h] * sfb[j % JW];
                 if (a.accumulate) {

@@ -217,21 +217,26 @@ extern "C" size_t trb_sbmm_indexed_scratch_bytes(int num_tokens, int prob_k, int
   return b;
 }
 
-extern "C" int trb_sbmm_indexed(const void* x, const void* qweights, const void* metas, const void* scales,
-                                const void* indices, void* y, int num_tokens, int prob_m, int prob_k,
-                                int num_deltas, int index_offset, int groupsize, int accumulate, void* scratch,
-                                size_t scratch_bytes, int dev, void* stream_v) {
-  cudaStream_t stream = (cudaStream_t)stream_v;
+namespace trb {
+// Router + row gather + grouped kernel.  `src` says where the ids come from; num_tokens counts the
+// rows of x and y.  mode: 0 = overwrite rows that have a delta and zero the others, 1 = accumulate,
+// 2 = overwrite rows that have a delta and leave the others untouched.  tile_tokens: 0 = choose.
+int sbmm_indexed_impl(const void* x, const void* qweights, const void* metas, const void* scales, const RouteSrc& src,
+                      void* y, int num_tokens, int prob_m, int prob_k, int num_deltas, int groupsize, int mode,
+                      int tile_tokens, void* scratch, size_t scratch_bytes, int dev, cudaStream_t stream,
+                      const void* y_peers = nullptr, int chunk_rows = 0, int my_rank = 0) {
   if (num_deltas <= 0) return TRB_ERR_BAD_ARG;
   const int rc = check_common(x, qweights, metas, y, scales, prob_m, num_tokens, prob_k, groupsize);
   if (rc == -1) return TRB_OK;
   if (rc != TRB_OK) return rc;
-  if (!indices || !scratch || ((uintptr_t)scratch & 255)) return TRB_ERR_BAD_ARG;
+  if (!scratch || ((uintptr_t)scratch & 255)) return TRB_ERR_BAD_ARG;
   if (scratch_bytes < trb_sbmm_indexed_scratch_bytes(num_tokens, prob_k, num_deltas)) return TRB_ERR_SCRATCH;
   if (cudaSetDevice(dev) != cudaSuccess) return TRB_ERR_CUDA;
 
   const int segs = num_tokens < num_deltas ? num_tokens : num_deltas;
-  const int tt = gemm_tile_tokens((num_tokens + segs - 1) / segs);
+  int tt = tile_tokens;
+  if (tt == 0) tt = gemm_tile_tokens((num_tokens + segs - 1) / segs);
+  if (tt != 8 && tt != 16 && tt != 32 && tt != 64) return TRB_ERR_KERN_SHAPE;
   const int max_tiles = trb_route_max_tiles(num_tokens, num_deltas, tt);
   if (max_tiles > kMaxSegments) return TRB_ERR_KERN_SHAPE;
   const size_t tiles8 = (size_t)trb_route_max_tiles(num_tokens, num_deltas, 8);
@@ -244,10 +249,10 @@ extern "C" int trb_sbmm_indexed(const void* x, const void* qweights, const void*
   int* tile_count = (int*)p; p += align_up(tiles8 * 4, 256);
   void* x_sorted = p;
 
-  int r = route_launch((const int*)indices, num_tokens, num_deltas, tt, index_offset, perm, nullptr, nullptr, nullptr, tile_delta,
-                       tile_start, tile_count, counters, stream);
+  int r = route_launch_src(src, num_tokens, num_deltas, tt, perm, nullptr, nullptr, nullptr, tile_delta, tile_start,
+                           tile_count, counters, nullptr, 0, nullptr, stream);
   if (r != TRB_OK) return r;
-  r = gather_launch(x, perm, counters, x_sorted, y, num_tokens, prob_k, prob_m, accumulate ? 0 : 1, stream);
+  r = gather_launch(x, perm, counters, x_sorted, y, num_tokens, prob_k, prob_m, mode == 0 ? 1 : 0, stream);
   if (r != TRB_OK) return r;
 
   GemmArgs a{};
@@ -260,9 +265,47 @@ extern "C" int trb_sbmm_indexed(const void* x, const void* qweights, const void*
   a.scales = (const __half*)scales;
   a.y = (__half*)y;
   a.row_map = perm;
-  a.accumulate = accumulate;
+  a.accumulate = mode == 1;
+  a.y_peers = (__half* const*)y_peers;
+  a.chunk_rows = chunk_rows;
+  a.my_rank = my_rank;
   GemmCall c{x_sorted, qweights, metas, scales, num_deltas, groupsize, dev, -1, stream};
   return gemm_dispatch(c, a, tt);
+}
+}  // namespace trb
+
+extern "C" int trb_sbmm_indexed(const void* x, const void* qweights, const void* metas, const void* scales,
+                                const void* indices, void* y, int num_tokens, int prob_m, int prob_k,
+                                int num_deltas, int index_offset, int groupsize, int accumulate, void* scratch,
+                                size_t scratch_bytes, int dev, void* stream_v) {
+  if (num_tokens > 0 && !indices) return TRB_ERR_BAD_ARG;
+  RouteSrc src{};
+  src.indices = (const int*)indices;
+  src.id_offset = index_offset;
+  return sbmm_indexed_impl(x, qweights, metas, scales, src, y, num_tokens, prob_m, prob_k, num_deltas, groupsize,
+                           accumulate ? 1 : 0, 0, scratch, scratch_bytes, dev, (cudaStream_t)stream_v);
+}
+
+// Owner-side step of the sharded path: the received exchange buffer (world chunks of cap + 1 rows of K
+// halves, ids in each chunk's last row) goes through the router and the grouped kernel; result rows
+// land in the same slots of `y_work` (world * (cap + 1) rows of N halves), other rows are left alone.
+extern "C" int trb_shard_compute(const void* recv_buf, const void* qweights, const void* metas, const void* scales,
+                                 void* y_work, int world, int cap, int prob_m, int prob_k, int num_local_deltas,
+                                 int groupsize, const void* peer_out_ptrs, int my_rank, void* scratch,
+                                 size_t scratch_bytes, int dev, void* stream_v) {
+  if (world < 1 || cap < 1 || !recv_buf || my_rank < 0 || my_rank >= world) return TRB_ERR_BAD_ARG;
+  const long long rows = (long long)world * (cap + 1);
+  if (rows > 65536) return TRB_ERR_PROB_SHAPE;
+  RouteSrc src{};
+  src.chunk_base = (const unsigned char*)recv_buf;
+  src.cap = cap;
+  src.row_bytes = (long long)prob_k * 2;
+  // Tile size from the tokens a rank expects (cap per rank on average), not from the padded row count.
+  const int segs = cap < num_local_deltas ? cap : num_local_deltas;
+  const int tt = gemm_tile_tokens((cap + segs - 1) / (segs > 0 ? segs : 1));
+  return sbmm_indexed_impl(recv_buf, qweights, metas, scales, src, y_work, (int)rows, prob_m, prob_k, num_local_deltas,
+                           groupsize, 2, tt, scratch, scratch_bytes, dev, (cudaStream_t)stream_v, peer_out_ptrs, cap + 1,
+                           my_rank);
 }
 
 extern "C" int trb_route(const void* indices, int num_tokens, int num_deltas, int tile_tokens, int index_offset,

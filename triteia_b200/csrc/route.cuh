@@ -8,6 +8,7 @@
 // a 32-token step), a block-wide exclusive scan over (id-major, warp-minor) counts gives every
 // (id, warp) pair its first output slot, and a second pass ranks tokens inside each step with
 // match_any + popc.  All integer work; results are bit-exact against the CPU router.
+#pragma once
 #include "common.cuh"
 
 namespace trb {
@@ -52,11 +53,41 @@ __device__ int block_exclusive_scan(int* data, int len, int* warp_tot /* [33] */
   return total;
 }
 
+// Where the ids come from and how an id becomes a bin.
+struct RouteSrc {
+  const int* indices;    // plain mode: one id per token
+  int id_offset;         // id = raw - id_offset
+  int mod;               // > 0: bin by id % mod (planning the dispatch to `mod` ranks)
+  // Chunked mode (chunk_base != nullptr): token t is row t % (cap + 1) of chunk t / (cap + 1) of an
+  // exchange buffer whose chunks are cap + 1 rows of row_bytes; the last row of a chunk holds the ids
+  // of its rows as int32 followed by the number of rows in use.
+  const unsigned char* chunk_base;
+  int cap;
+  long long row_bytes;
+};
+
+__device__ __forceinline__ int route_load_raw(const RouteSrc& s, int t) {
+  if (s.chunk_base == nullptr) return s.indices[t];
+  const int rows = s.cap + 1;
+  const int r = t / rows, q = t - r * rows;
+  if (q == s.cap) return -1;
+  const int* ids = reinterpret_cast<const int*>(s.chunk_base + ((long long)r * rows + s.cap) * s.row_bytes);
+  return q < ids[s.cap] ? ids[q] : -1;
+}
+
+__device__ __forceinline__ int route_bin(const RouteSrc& s, int raw, int D, bool* invalid) {
+  const int id = raw - s.id_offset;
+  *invalid = raw < -1 || (s.mod <= 0 && id >= D);
+  if (id < 0) return 0;
+  if (s.mod > 0) return id % s.mod + 1;
+  return id >= D ? 0 : id + 1;
+}
+
 __global__ void __launch_bounds__(kRouteThreads, 1)
-route_kernel(const int* __restrict__ indices, int T, int D, int W, int TT, int id_offset, int* __restrict__ perm,
+route_kernel(const RouteSrc src, int T, int D, int W, int TT, int* __restrict__ perm,
              int* __restrict__ seg_delta, int* __restrict__ seg_start, int* __restrict__ seg_count,
              int* __restrict__ tile_delta, int* __restrict__ tile_start, int* __restrict__ tile_count,
-             int* __restrict__ counters) {
+             int* __restrict__ counters, int* __restrict__ slot_of, int slot_stride, int* __restrict__ bin_count) {
   extern __shared__ int sm[];
   const int bins = D + 1;             // bin 0 = id -1 (and out-of-range ids)
   int* hist = sm;                     // [bins][W]
@@ -79,10 +110,9 @@ route_kernel(const int* __restrict__ indices, int T, int D, int W, int TT, int i
       const int t = base + lane;
       int bin = -1;
       if (t < t_hi) {
-        const int raw = indices[t];
-        const int id = raw - id_offset;
-        if (raw < -1 || id >= D) atomicAdd(&n_invalid, 1);
-        bin = (id < 0 || id >= D) ? 0 : id + 1;
+        bool bad;
+        bin = route_bin(src, route_load_raw(src, t), D, &bad);
+        if (bad) atomicAdd(&n_invalid, 1);
       }
       const unsigned active = __ballot_sync(0xffffffffu, bin >= 0);
       if (bin >= 0) {
@@ -97,13 +127,13 @@ route_kernel(const int* __restrict__ indices, int T, int D, int W, int TT, int i
   if (tid == 0) bin_start[bins] = T;
   __syncthreads();
 
-  if (perm != nullptr && warp < W) {
+  if ((perm != nullptr || slot_of != nullptr) && warp < W) {
     for (int base = t_lo; base < t_hi; base += 32) {
       const int t = base + lane;
       int bin = -1;
       if (t < t_hi) {
-        const int id = indices[t] - id_offset;
-        bin = (id < 0 || id >= D) ? 0 : id + 1;
+        bool bad;
+        bin = route_bin(src, route_load_raw(src, t), D, &bad);
       }
       const unsigned active = __ballot_sync(0xffffffffu, bin >= 0);
       if (bin >= 0) {
@@ -112,7 +142,10 @@ route_kernel(const int* __restrict__ indices, int T, int D, int W, int TT, int i
         const int first = hist[bin * W + warp];
         __syncwarp(active);
         if (rank == 0) hist[bin * W + warp] = first + __popc(same);
-        perm[first + rank] = t;
+        if (perm) perm[first + rank] = t;
+        // Slot of the token inside its bin (dispatch planning): bin b - 1 owns slots
+        // [(b - 1) * slot_stride, ...); tokens of bin 0 get -1.
+        if (slot_of) slot_of[t] = bin == 0 ? -1 : (bin - 1) * slot_stride + (first + rank - bin_start[bin]);
       }
       __syncwarp();
     }
@@ -146,6 +179,8 @@ route_kernel(const int* __restrict__ indices, int T, int D, int W, int TT, int i
       }
     }
   }
+  if (bin_count)
+    for (int b = tid + 1; b < bins; b += kRouteThreads) bin_count[b - 1] = bin_start[b + 1] - bin_start[b];
   if (tid == 0 && counters) {
     counters[0] = n_seg;
     counters[1] = n_tiles;
@@ -184,11 +219,11 @@ extern "C" int trb_route_max_tiles(int num_tokens, int num_deltas, int tile_toke
 }
 
 namespace trb {
-int route_launch(const int* indices, int T, int D, int TT, int id_offset, int* perm, int* seg_delta, int* seg_start,
-                 int* seg_count, int* tile_delta, int* tile_start, int* tile_count, int* counters,
-                 cudaStream_t stream) {
+int route_launch_src(const RouteSrc& src, int T, int D, int TT, int* perm, int* seg_delta, int* seg_start,
+                     int* seg_count, int* tile_delta, int* tile_start, int* tile_count, int* counters, int* slot_of,
+                     int slot_stride, int* bin_count, cudaStream_t stream) {
   if (T < 0 || T > 65536 || D < 1 || D > 8191 || TT < 1) return TRB_ERR_PROB_SHAPE;
-  if ((indices == nullptr && T > 0) || counters == nullptr) return TRB_ERR_BAD_ARG;
+  if ((src.indices == nullptr && src.chunk_base == nullptr && T > 0) || counters == nullptr) return TRB_ERR_BAD_ARG;
   const int bins = D + 1;
   int W = (50000 - 3 * bins - 1) / bins;   // shared-memory budget of ~195 KiB
   W = W < 1 ? 1 : (W > 32 ? 32 : W);
@@ -201,9 +236,19 @@ int route_launch(const int* indices, int T, int D, int TT, int id_offset, int* p
       return TRB_ERR_CUDA;
     attr_set[dev] = true;
   }
-  route_kernel<<<1, kRouteThreads, smem, stream>>>(indices, T, D, W, TT, id_offset, perm, seg_delta, seg_start, seg_count,
-                                                   tile_delta, tile_start, tile_count, counters);
+  route_kernel<<<1, kRouteThreads, smem, stream>>>(src, T, D, W, TT, perm, seg_delta, seg_start, seg_count, tile_delta,
+                                                   tile_start, tile_count, counters, slot_of, slot_stride, bin_count);
   return cudaGetLastError() == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
+}
+
+int route_launch(const int* indices, int T, int D, int TT, int id_offset, int* perm, int* seg_delta, int* seg_start,
+                 int* seg_count, int* tile_delta, int* tile_start, int* tile_count, int* counters,
+                 cudaStream_t stream) {
+  RouteSrc src{};
+  src.indices = indices;
+  src.id_offset = id_offset;
+  return route_launch_src(src, T, D, TT, perm, seg_delta, seg_start, seg_count, tile_delta, tile_start, tile_count,
+                          counters, nullptr, 0, nullptr, stream);
 }
 
 int gather_launch(const void* x, const int* perm, const int* counters, void* x_sorted, void* y, int T, int K,

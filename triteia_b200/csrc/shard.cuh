@@ -1,0 +1,122 @@
+// Multi-GPU form of the indexed delta matmul: deltas are sharded by id over `world` ranks
+// (owner = id % world, local id = id / world) and tokens travel to the owner and back through
+// fixed-capacity exchange buffers, so that the collectives in between (all-to-all with equal splits,
+// issued by the host through NCCL) need no counts on the host and no host synchronisation.
+//
+// Exchange buffer layout (both directions): `world` chunks, chunk r = rows for / from rank r,
+// cap + 1 rows each.  Outbound chunk: rows 0..cap-1 = activation rows (K halves), row cap = the rows'
+// local delta ids as int32 followed by the number of rows in use.  Return chunk: rows of N halves in
+// the same slots.  The reference has no distributed layer; nothing here has a counterpart in it.
+#pragma once
+
+#include "common.cuh"
+#include "route.cuh"
+
+namespace trb {
+
+// One CTA per token: copy its row into its slot of the send buffer and record its local delta id.
+// CTAs T .. T + world - 1 write the per-chunk row counts.
+__global__ void shard_pack_kernel(const uint4* __restrict__ x, const int* __restrict__ indices,
+                                  const int* __restrict__ slot_of, const int* __restrict__ bin_count,
+                                  unsigned char* __restrict__ send, unsigned char* const* __restrict__ peers,
+                                  int my_rank, int T, int K, int world, int cap) {
+  // Chunk for rank r: in the local send buffer at chunk index r, or (peer mode) straight in rank r's
+  // receive buffer at chunk index my_rank, written over NVLink.
+  const long long row_bytes = (long long)K * 2;
+  auto chunk = [&](int r) -> unsigned char* {
+    return peers ? peers[r] + (long long)my_rank * (cap + 1) * row_bytes : send + (long long)r * (cap + 1) * row_bytes;
+  };
+  const int b = blockIdx.x;
+  if (b >= T) {
+    const int r = b - T;
+    if (r < world && threadIdx.x == 0) {
+      int* ids = reinterpret_cast<int*>(chunk(r) + (long long)cap * row_bytes);
+      ids[cap] = min(bin_count[r], cap);
+    }
+    return;
+  }
+  const int slot = slot_of[b];
+  if (slot < 0) return;
+  const int r = slot / cap, q = slot - r * cap;
+  if (r >= world) return;
+  uint4* dst = reinterpret_cast<uint4*>(chunk(r) + (long long)q * row_bytes);
+  const uint4* srcp = x + (long long)b * (K / 8);
+  for (int i = threadIdx.x; i < K / 8; i += blockDim.x) dst[i] = srcp[i];
+  if (threadIdx.x == 0) {
+    int* ids = reinterpret_cast<int*>(chunk(r) + (long long)cap * row_bytes);
+    ids[q] = indices[b] / world;
+  }
+}
+
+// y[t] (+)= result row of token t's slot; tokens without a delta are zeroed unless accumulating.
+__global__ void shard_combine_kernel(const uint4* __restrict__ back, const int* __restrict__ slot_of,
+                                     uint4* __restrict__ y, int T, int N, int world, int cap, int accumulate) {
+  const int t = blockIdx.x;
+  if (t >= T) return;
+  const int slot = slot_of[t];
+  uint4* dst = y + (long long)t * (N / 8);
+  if (slot < 0) {
+    if (!accumulate)
+      for (int i = threadIdx.x; i < N / 8; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  const int r = slot / cap, q = slot - r * cap;
+  const uint4* srcp = back + ((long long)r * (cap + 1) + q) * (N / 8);
+  for (int i = threadIdx.x; i < N / 8; i += blockDim.x) {
+    uint4 v = srcp[i];
+    if (accumulate) {
+      uint4 o = dst[i];
+      __half2* vh = reinterpret_cast<__half2*>(&v);
+      const __half2* oh = reinterpret_cast<const __half2*>(&o);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) vh[e] = __hadd2(vh[e], oh[e]);
+    }
+    dst[i] = v;
+  }
+}
+
+}  // namespace trb
+
+extern "C" size_t trb_shard_buffer_rows(int num_tokens, int world) {
+  return (num_tokens <= 0 || world <= 0) ? 0 : (size_t)world * ((size_t)num_tokens + 1);
+}
+
+// Plan + pack: slot_of[T] (out), send buffer [world][T + 1][K] halves (out).  plan: int32 [8 + world].
+extern "C" int trb_shard_dispatch(const void* x, const void* indices, int num_tokens, int prob_k, int world,
+                                  void* send_buf, const void* peer_recv_ptrs, int my_rank, void* slot_of, void* plan,
+                                  int dev, void* stream_v) {
+  using namespace trb;
+  cudaStream_t stream = (cudaStream_t)stream_v;
+  if (num_tokens == 0) return TRB_OK;
+  if (num_tokens < 0 || world < 1 || world > 64 || prob_k <= 0 || prob_k % 8 != 0) return TRB_ERR_BAD_ARG;
+  if (!x || !indices || (!send_buf && !peer_recv_ptrs) || !slot_of || !plan) return TRB_ERR_BAD_ARG;
+  if (my_rank < 0 || my_rank >= world) return TRB_ERR_BAD_ARG;
+  if ((long long)num_tokens * 4 + 4 > (long long)prob_k * 2) return TRB_ERR_PROB_SHAPE;  // ids must fit one row
+  if (cudaSetDevice(dev) != cudaSuccess) return TRB_ERR_CUDA;
+  int* counters = (int*)plan;
+  int* bin_count = counters + 8;
+  RouteSrc src{};
+  src.indices = (const int*)indices;
+  src.mod = world;
+  int rc = route_launch_src(src, num_tokens, world, 1 << 30, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
+                            nullptr, counters, (int*)slot_of, num_tokens, bin_count, stream);
+  if (rc != TRB_OK) return rc;
+  shard_pack_kernel<<<num_tokens + world, 128, 0, stream>>>((const uint4*)x, (const int*)indices, (const int*)slot_of,
+                                                           bin_count, (unsigned char*)send_buf,
+                                                           (unsigned char* const*)peer_recv_ptrs, my_rank, num_tokens,
+                                                           prob_k, world, num_tokens);
+  return cudaGetLastError() == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
+}
+
+extern "C" int trb_shard_combine(const void* back_buf, const void* slot_of, void* y, int num_tokens, int prob_m,
+                                 int world, int accumulate, int dev, void* stream_v) {
+  using namespace trb;
+  if (num_tokens == 0) return TRB_OK;
+  if (num_tokens < 0 || world < 1 || prob_m <= 0 || prob_m % 8 != 0 || !back_buf || !slot_of || !y)
+    return TRB_ERR_BAD_ARG;
+  if (cudaSetDevice(dev) != cudaSuccess) return TRB_ERR_CUDA;
+  shard_combine_kernel<<<num_tokens, 128, 0, (cudaStream_t)stream_v>>>((const uint4*)back_buf, (const int*)slot_of,
+                                                                      (uint4*)y, num_tokens, prob_m, world,
+                                                                      num_tokens, accumulate);
+  return cudaGetLastError() == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
+}

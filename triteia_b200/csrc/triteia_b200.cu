@@ -6,6 +6,7 @@
 #include "route.cuh"
 #include "delta_gemm.cuh"
 #include "delta_gemm_host.cuh"
+#include "shard.cuh"
 #include "unpack.cuh"
 #include "lora.cuh"
 #include "no_alloc.cuh"
