@@ -45,6 +45,15 @@ def peaks():
     return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
 
 
+def describe_parallelism(world, exchange_kind):
+    if world == 1:
+        return "single GPU"
+    how = ("rows and results stored straight into the owner's symmetric-memory buffers over NVLink by the pack kernel "
+           "and the grouped kernel's epilogue, two cross-GPU barriers per step" if exchange_kind == "p2p" else
+           "two equal-split NCCL all-to-alls per step (rows + ids out, result rows back)")
+    return f"deltas sharded by id over {world} GPUs; {how}; no host synchronisation"
+
+
 def make_indices(seed, tokens, num_deltas):
     rng = np.random.default_rng(seed)
     idx = rng.integers(0, num_deltas, tokens)
@@ -254,9 +263,41 @@ def run_gpu_arm(args):
     if rank == 0:
         sampler.start()
     t_wall0 = time.perf_counter()
+    # Timed region of `value`: exactly K steps bracketed by barrier + synchronize, CUDA events on the
+    # launching stream, max over ranks below.  No flush inside the bracket: every step streams the
+    # touched deltas (~360 MB per GPU), far more than the 126 MB L2, and they carry an evict-first hint.
+    # One step is captured into a CUDA graph (the library calls neither allocate nor synchronise) and
+    # replayed K times, so the host's launch cost is off the device timeline; --eager disables this.
+    launch_mode = "eager"
+    run_step = step_resident
+    if not args.eager:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step_resident()
+            torch.cuda.current_stream().wait_stream(side)
+            barrier()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                graph_out = step_resident()
+            barrier()
+            graph.replay()
+            barrier()
+            run_step, launch_mode = graph.replay, "cuda-graph replay of one captured step"
+        except Exception as e:   # capture not possible: keep the eager path
+            if rank == 0:
+                print(f"bench.py: graph capture failed ({e}); timing eager launches", file=sys.stderr)
+            run_step = step_resident
     barrier()
-    times = time_steps(step_resident, args.steps, flush)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        run_step()
+    ev1.record()
+    ev1.synchronize()
     barrier()
+    times = [ev0.elapsed_time(ev1) / args.steps]
     # end-to-end: host buffers in, host buffer out, wall clock per step around a stream sync
     e2e_times = []
     for _ in range(args.steps):
@@ -313,15 +354,11 @@ def run_gpu_arm(args):
             "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "deltas_per_gpu": D_PER_GPU, "tokens_per_gpu": TOKENS, "k": K, "n": N_OUT,
                        "groupsize": GROUP, "index_law": "uniform over all deltas, 10% -1, unsorted",
-                       "distinct_deltas_touched_rank0": touched,
-                       "l2": "flushed before every timed step (256 MiB memset then a 256 MiB read, untimed); touched weights "
-                             f"{touched * BYTES_PER_DELTA / 1e6:.0f} MB > 126 MB L2",
-                       "parallelism": "single GPU" if world == 1 else f"deltas sharded by id over {world} GPUs, "
-                                                                       ("rows and results stored straight into the owner's symmetric-memory buffers over NVLink "
-                                                                        "by the pack kernel and the grouped kernel's epilogue, two cross-GPU barriers per step"
-                                                                        if exchange_kind == "p2p" else
-                                                                        "two equal-split NCCL all-to-alls per step (rows + ids out, result rows back)")
-                                                                       + ", no host synchronisation"},
+                       "distinct_deltas_touched_rank0": touched, "launch": launch_mode,
+                       "l2": f"inputs larger than L2: every step streams {touched * BYTES_PER_DELTA / 1e6:.0f} MB of packed "
+                             "deltas (126 MB L2, evict-first loads); the kernel-alone roofline leg and the e2e leg "
+                             "additionally flush L2 before every step (256 MiB memset + 256 MiB read, untimed)",
+                       "parallelism": describe_parallelism(world, exchange_kind if world > 1 else None)},
             "e2e": {"value": tokens_total / (t_e2e * 1e-3), "unit": UNIT, "ms_per_step": t_e2e,
                     "h2d_bytes_per_step": int(x_host.numel() * 2 + idx_host.numel() * 4),
                     "d2h_bytes_per_step": int(y_host.numel() * 2),
@@ -350,6 +387,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
+    ap.add_argument("--eager", action="store_true", help="time eager launches instead of CUDA-graph replays")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -139,15 +139,17 @@ int trb_sbmm_indexed_static(const void* x, const void* qweights, const void* met
  *                       world * (cap + 1) tokens
  *   trb_shard_combine   y[t] (+)= returned row of token t; tokens without a delta are zeroed unless
  *                       accumulate
- * Peer mode (no collective at all): peer_recv_ptrs / peer_out_ptrs are device arrays of `world`
- * pointers to every rank's receive / return buffer (peer-mapped memory, e.g. CUDA symmetric memory);
- * the pack kernel and the grouped kernel's epilogue then store rows straight into the owner's buffer
- * over NVLink (chunk index = my_rank) and the host only places a cross-GPU barrier between the steps.
- * Pass NULL for the plain form. */
+ * Peer form (no collective at all): peer_recv_ptrs / peer_out_ptrs are device arrays of `world`
+ * pointers to every rank's receive buffer / output tensor [num_tokens, N] (peer-mapped memory, e.g.
+ * CUDA symmetric memory).  The pack kernel stores rows straight into the owner's receive buffer over
+ * NVLink (chunk index = my_rank) and clears the rows of y_zero (this rank's output tensor) whose
+ * token has no delta; the grouped kernel's epilogue stores every result row straight into the
+ * source rank's output tensor at the token's own row.  The host only places a cross-GPU barrier
+ * after each of the two calls; trb_shard_combine is not used.  Pass NULL for the plain form. */
 size_t trb_shard_buffer_rows(int num_tokens, int world);
 int trb_shard_dispatch(const void* x, const void* indices, int num_tokens, int prob_k, int world,
-                       void* send_buf, const void* peer_recv_ptrs, int my_rank, void* slot_of,
-                       void* plan, int dev, void* stream);
+                       void* send_buf, const void* peer_recv_ptrs, int my_rank, void* y_zero,
+                       int prob_m, void* slot_of, void* plan, int dev, void* stream);
 int trb_shard_compute(const void* recv_buf, const void* qweights, const void* metas,
                       const void* scales, void* y_work, int world, int cap, int prob_m, int prob_k,
                       int num_local_deltas, int groupsize, const void* peer_out_ptrs, int my_rank,

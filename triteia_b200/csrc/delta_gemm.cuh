@@ -37,11 +37,14 @@ struct GemmArgs {
   __half* y;
   const int* row_map;     // nullptr, or output row of each x row (scatter through the router's perm)
   int accumulate;         // y += result instead of y = result
-  // Sharded path, results written straight into the token owners' buffers over NVLink: output row
-  // r * chunk_rows + q goes to row my_rank * chunk_rows + q of y_peers[r] (nullptr: plain y).
+  // Sharded path, results stored straight into the token owners' output over NVLink: x row
+  // r * chunk_rows + q came from rank r, whose token row is entry chunk_rows + q of the int32 id row
+  // that closes chunk r of the exchange buffer `xchg` (rows of xchg_row_bytes); the result goes to
+  // that row of y_peers[r] (nullptr: plain y).
   __half* const* y_peers;
+  const unsigned char* xchg;
+  long long xchg_row_bytes;
   int chunk_rows;
-  int my_rank;
 };
 
 template <int NB_, int SW_, int KQ_, int KS_, int STAGES_>
@@ -288,6 +291,13 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
           r = w.row0 + t;
           if (a.row_map) r = a.row_map[r];
           if (r < 0 || r >= a.rows) r = -1;
+          if (a.y_peers && r >= 0) {
+            // (source rank << 20) | token row on that rank
+            const int pr = r / a.chunk_rows, pq = r - pr * a.chunk_rows;
+            const int* ids = reinterpret_cast<const int*>(a.xchg + ((long long)pr * a.chunk_rows + a.chunk_rows - 1) * a.xchg_row_bytes);
+            const int trow = ids[a.chunk_rows + pq];
+            r = (trow >= 0 && trow < (1 << 20)) ? ((pr << 20) | trow) : -1;
+          }
         }
         orow[nb][h] = r;
       }
@@ -488,8 +498,7 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
               if (r >= 0 && (NB == 1 || nb < nbv)) {
                 __half* yp;
                 if (a.y_peers) {
-                  const int pr = r / a.chunk_rows, pq = r - pr * a.chunk_rows;
-                  yp = a.y_peers[pr] + ((size_t)a.my_rank * a.chunk_rows + pq) * a.N + colb + j;
+                  yp = a.y_peers[r >> 20] + (size_t)(r & ((1 << 20) - 1)) * a.N + colb + j;
                 } else {
                   yp = a.y + (size_t)r * a.N + colb + j;
                 }

@@ -224,7 +224,7 @@ namespace trb {
 int sbmm_indexed_impl(const void* x, const void* qweights, const void* metas, const void* scales, const RouteSrc& src,
                       void* y, int num_tokens, int prob_m, int prob_k, int num_deltas, int groupsize, int mode,
                       int tile_tokens, void* scratch, size_t scratch_bytes, int dev, cudaStream_t stream,
-                      const void* y_peers = nullptr, int chunk_rows = 0, int my_rank = 0) {
+                      const void* y_peers = nullptr, int chunk_rows = 0) {
   if (num_deltas <= 0) return TRB_ERR_BAD_ARG;
   const int rc = check_common(x, qweights, metas, y, scales, prob_m, num_tokens, prob_k, groupsize);
   if (rc == -1) return TRB_OK;
@@ -267,8 +267,9 @@ int sbmm_indexed_impl(const void* x, const void* qweights, const void* metas, co
   a.row_map = perm;
   a.accumulate = mode == 1;
   a.y_peers = (__half* const*)y_peers;
+  a.xchg = src.chunk_base;
+  a.xchg_row_bytes = src.row_bytes;
   a.chunk_rows = chunk_rows;
-  a.my_rank = my_rank;
   GemmCall c{x_sorted, qweights, metas, scales, num_deltas, groupsize, dev, -1, stream};
   return gemm_dispatch(c, a, tt);
 }
@@ -287,13 +288,17 @@ extern "C" int trb_sbmm_indexed(const void* x, const void* qweights, const void*
 }
 
 // Owner-side step of the sharded path: the received exchange buffer (world chunks of cap + 1 rows of K
-// halves, ids in each chunk's last row) goes through the router and the grouped kernel; result rows
-// land in the same slots of `y_work` (world * (cap + 1) rows of N halves), other rows are left alone.
+// halves, ids in each chunk's last row) goes through the router and the grouped kernel.  Plain form:
+// result rows land in the same slots of `y_work` (world * (cap + 1) rows of N halves), other rows are
+// left alone.  Peer form (peer_out_ptrs != NULL): every result row is stored into its source rank's
+// output tensor [cap, N] at the token's own row, y_work is not used.
 extern "C" int trb_shard_compute(const void* recv_buf, const void* qweights, const void* metas, const void* scales,
                                  void* y_work, int world, int cap, int prob_m, int prob_k, int num_local_deltas,
                                  int groupsize, const void* peer_out_ptrs, int my_rank, void* scratch,
                                  size_t scratch_bytes, int dev, void* stream_v) {
-  if (world < 1 || cap < 1 || !recv_buf || my_rank < 0 || my_rank >= world) return TRB_ERR_BAD_ARG;
+  (void)my_rank;
+  if (world < 1 || cap < 1 || !recv_buf || (!y_work && !peer_out_ptrs)) return TRB_ERR_BAD_ARG;
+  if (peer_out_ptrs && ((long long)(2 * cap + 2) * 4 > (long long)prob_k * 2 || cap >= (1 << 20))) return TRB_ERR_PROB_SHAPE;
   const long long rows = (long long)world * (cap + 1);
   if (rows > 65536) return TRB_ERR_PROB_SHAPE;
   RouteSrc src{};
@@ -303,9 +308,8 @@ extern "C" int trb_shard_compute(const void* recv_buf, const void* qweights, con
   // Tile size from the tokens a rank expects (cap per rank on average), not from the padded row count.
   const int segs = cap < num_local_deltas ? cap : num_local_deltas;
   const int tt = gemm_tile_tokens((cap + segs - 1) / (segs > 0 ? segs : 1));
-  return sbmm_indexed_impl(recv_buf, qweights, metas, scales, src, y_work, (int)rows, prob_m, prob_k, num_local_deltas,
-                           groupsize, 2, tt, scratch, scratch_bytes, dev, (cudaStream_t)stream_v, peer_out_ptrs, cap + 1,
-                           my_rank);
+  return sbmm_indexed_impl(recv_buf, qweights, metas, scales, src, y_work ? y_work : (void*)recv_buf, (int)rows, prob_m, prob_k, num_local_deltas,
+                           groupsize, 2, tt, scratch, scratch_bytes, dev, (cudaStream_t)stream_v, peer_out_ptrs, cap + 1);
 }
 
 extern "C" int trb_route(const void* indices, int num_tokens, int num_deltas, int tile_tokens, int index_offset,

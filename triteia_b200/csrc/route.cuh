@@ -13,12 +13,13 @@
 
 namespace trb {
 
-constexpr int kRouteThreads = 1024;
+constexpr int kRouteThreads = 1024;   // upper bound; small batches launch 256
 
 // Exclusive scan of data[0..len) in shared memory by the whole CTA; returns the total.
 __device__ int block_exclusive_scan(int* data, int len, int* warp_tot /* [33] */) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int per = (len + kRouteThreads - 1) / kRouteThreads;
+  const int nthreads = blockDim.x, nwarps = nthreads >> 5;
+  const int per = (len + nthreads - 1) / nthreads;
   const int lo = min(len, tid * per), hi = min(len, lo + per);
   int sum = 0;
   for (int i = lo; i < hi; ++i) sum += data[i];
@@ -31,7 +32,7 @@ __device__ int block_exclusive_scan(int* data, int len, int* warp_tot /* [33] */
   if (lane == 31) warp_tot[warp] = inc;
   __syncthreads();
   if (warp == 0) {
-    int w = warp_tot[lane];
+    int w = lane < nwarps ? warp_tot[lane] : 0;
     int winc = w;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -98,7 +99,7 @@ route_kernel(const RouteSrc src, int T, int D, int W, int TT, int* __restrict__ 
   __shared__ int n_invalid;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  for (int i = tid; i < bins * W; i += kRouteThreads) hist[i] = 0;
+  for (int i = tid; i < bins * W; i += blockDim.x) hist[i] = 0;
   if (tid == 0) n_invalid = 0;
   __syncthreads();
 
@@ -123,7 +124,7 @@ route_kernel(const RouteSrc src, int T, int D, int W, int TT, int* __restrict__ 
   }
   __syncthreads();
   block_exclusive_scan(hist, bins * W, warp_tot);
-  for (int b = tid; b < bins; b += kRouteThreads) bin_start[b] = hist[b * W];
+  for (int b = tid; b < bins; b += blockDim.x) bin_start[b] = hist[b * W];
   if (tid == 0) bin_start[bins] = T;
   __syncthreads();
 
@@ -153,7 +154,7 @@ route_kernel(const RouteSrc src, int T, int D, int W, int TT, int* __restrict__ 
   __syncthreads();
 
   // Segments (distinct ids >= 0 in increasing order) and their tiles.
-  for (int b = tid; b < bins; b += kRouteThreads) {
+  for (int b = tid; b < bins; b += blockDim.x) {
     const int cnt = bin_start[b + 1] - bin_start[b];
     const bool is_seg = b >= 1 && cnt > 0;
     seg_flag[b] = is_seg ? 1 : 0;
@@ -162,7 +163,7 @@ route_kernel(const RouteSrc src, int T, int D, int W, int TT, int* __restrict__ 
   __syncthreads();
   const int n_seg = block_exclusive_scan(seg_flag, bins, warp_tot);
   const int n_tiles = block_exclusive_scan(tile_cnt, bins, warp_tot);
-  for (int b = tid + 1; b < bins; b += kRouteThreads) {
+  for (int b = tid + 1; b < bins; b += blockDim.x) {
     const int start = bin_start[b], cnt = bin_start[b + 1] - start;
     if (cnt > 0) {
       const int s = seg_flag[b];
@@ -180,7 +181,7 @@ route_kernel(const RouteSrc src, int T, int D, int W, int TT, int* __restrict__ 
     }
   }
   if (bin_count)
-    for (int b = tid + 1; b < bins; b += kRouteThreads) bin_count[b - 1] = bin_start[b + 1] - bin_start[b];
+    for (int b = tid + 1; b < bins; b += blockDim.x) bin_count[b - 1] = bin_start[b + 1] - bin_start[b];
   if (tid == 0 && counters) {
     counters[0] = n_seg;
     counters[1] = n_tiles;
@@ -225,8 +226,13 @@ int route_launch_src(const RouteSrc& src, int T, int D, int TT, int* perm, int* 
   if (T < 0 || T > 65536 || D < 1 || D > 8191 || TT < 1) return TRB_ERR_PROB_SHAPE;
   if ((src.indices == nullptr && src.chunk_base == nullptr && T > 0) || counters == nullptr) return TRB_ERR_BAD_ARG;
   const int bins = D + 1;
+  // Small batches: 8 warps (cheaper block syncs), and no more histogram copies than 32-token pieces.
+  const int threads = (T <= 2048 && bins <= 2048) ? 256 : kRouteThreads;
   int W = (50000 - 3 * bins - 1) / bins;   // shared-memory budget of ~195 KiB
-  W = W < 1 ? 1 : (W > 32 ? 32 : W);
+  const int w_cap = threads / 32, w_need = (T + 31) / 32;
+  W = W > w_cap ? w_cap : W;
+  W = W > w_need ? w_need : W;
+  W = W < 1 ? 1 : W;
   const size_t smem = (size_t)(bins * W + 3 * bins + 1) * sizeof(int);
   static bool attr_set[64] = {};
   int dev = 0;
@@ -236,7 +242,7 @@ int route_launch_src(const RouteSrc& src, int T, int D, int TT, int* perm, int* 
       return TRB_ERR_CUDA;
     attr_set[dev] = true;
   }
-  route_kernel<<<1, kRouteThreads, smem, stream>>>(src, T, D, W, TT, perm, seg_delta, seg_start, seg_count, tile_delta,
+  route_kernel<<<1, threads, smem, stream>>>(src, T, D, W, TT, perm, seg_delta, seg_start, seg_count, tile_delta,
                                                    tile_start, tile_count, counters, slot_of, slot_stride, bin_count);
   return cudaGetLastError() == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
 }

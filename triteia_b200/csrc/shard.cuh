@@ -5,7 +5,7 @@
 //
 // Exchange buffer layout (both directions): `world` chunks, chunk r = rows for / from rank r,
 // cap + 1 rows each.  Outbound chunk: rows 0..cap-1 = activation rows (K halves), row cap = the rows'
-// local delta ids as int32 followed by the number of rows in use.  Return chunk: rows of N halves in
+// local delta ids as int32, the number of rows in use, then each row's token row on the sender.  Return chunk: rows of N halves in
 // the same slots.  The reference has no distributed layer; nothing here has a counterpart in it.
 #pragma once
 
@@ -19,7 +19,7 @@ namespace trb {
 __global__ void shard_pack_kernel(const uint4* __restrict__ x, const int* __restrict__ indices,
                                   const int* __restrict__ slot_of, const int* __restrict__ bin_count,
                                   unsigned char* __restrict__ send, unsigned char* const* __restrict__ peers,
-                                  int my_rank, int T, int K, int world, int cap) {
+                                  int my_rank, uint4* __restrict__ y_zero, int N, int T, int K, int world, int cap) {
   // Chunk for rank r: in the local send buffer at chunk index r, or (peer mode) straight in rank r's
   // receive buffer at chunk index my_rank, written over NVLink.
   const long long row_bytes = (long long)K * 2;
@@ -36,7 +36,12 @@ __global__ void shard_pack_kernel(const uint4* __restrict__ x, const int* __rest
     return;
   }
   const int slot = slot_of[b];
-  if (slot < 0) return;
+  if (slot < 0) {
+    // Peer form: nobody will write this token's output row, so it is cleared here.
+    if (y_zero)
+      for (int i = threadIdx.x; i < N / 8; i += blockDim.x) y_zero[(long long)b * (N / 8) + i] = make_uint4(0, 0, 0, 0);
+    return;
+  }
   const int r = slot / cap, q = slot - r * cap;
   if (r >= world) return;
   uint4* dst = reinterpret_cast<uint4*>(chunk(r) + (long long)q * row_bytes);
@@ -45,6 +50,7 @@ __global__ void shard_pack_kernel(const uint4* __restrict__ x, const int* __rest
   if (threadIdx.x == 0) {
     int* ids = reinterpret_cast<int*>(chunk(r) + (long long)cap * row_bytes);
     ids[q] = indices[b] / world;
+    if ((long long)(2 * cap + 2) * 4 <= row_bytes) ids[cap + 1 + q] = b;   // the token's own row, for peer-form results
   }
 }
 
@@ -83,8 +89,8 @@ extern "C" size_t trb_shard_buffer_rows(int num_tokens, int world) {
 
 // Plan + pack: slot_of[T] (out), send buffer [world][T + 1][K] halves (out).  plan: int32 [8 + world].
 extern "C" int trb_shard_dispatch(const void* x, const void* indices, int num_tokens, int prob_k, int world,
-                                  void* send_buf, const void* peer_recv_ptrs, int my_rank, void* slot_of, void* plan,
-                                  int dev, void* stream_v) {
+                                  void* send_buf, const void* peer_recv_ptrs, int my_rank, void* y_zero, int prob_m,
+                                  void* slot_of, void* plan, int dev, void* stream_v) {
   using namespace trb;
   cudaStream_t stream = (cudaStream_t)stream_v;
   if (num_tokens == 0) return TRB_OK;
@@ -103,8 +109,8 @@ extern "C" int trb_shard_dispatch(const void* x, const void* indices, int num_to
   if (rc != TRB_OK) return rc;
   shard_pack_kernel<<<num_tokens + world, 128, 0, stream>>>((const uint4*)x, (const int*)indices, (const int*)slot_of,
                                                            bin_count, (unsigned char*)send_buf,
-                                                           (unsigned char* const*)peer_recv_ptrs, my_rank, num_tokens,
-                                                           prob_k, world, num_tokens);
+                                                           (unsigned char* const*)peer_recv_ptrs, my_rank, (uint4*)y_zero,
+                                                           prob_m, num_tokens, prob_k, world, num_tokens);
   return cudaGetLastError() == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
 }
 

@@ -94,7 +94,9 @@ class FixedCapacityExchange:
     trb_shard_combine with an NCCL all-to-all (equal splits) after the first two.
     backend "p2p": no collective; the receive and return buffers are CUDA symmetric memory
     (torch.distributed._symmetric_memory), the pack kernel and the grouped kernel's epilogue store
-    rows straight into the owner's buffer over NVLink, and a cross-GPU barrier separates the steps.  backend "torch": the same buffer layout written with torch ops and a
+    rows straight into the owner's receive buffer / the source's output tensor over NVLink, and a
+    cross-GPU barrier follows each of the two steps.  The returned tensor is this object's output
+    buffer: the next call overwrites it.  backend "torch": the same buffer layout written with torch ops and a
     caller-supplied local_compute(x_rows, local_ids) -> rows; it exists so that the layout and the
     collectives can be tested on CPU ranks (gloo).
     """
@@ -115,12 +117,12 @@ class FixedCapacityExchange:
 
             grp = group if group is not None else dist.group.WORLD
             self.recv = symm_mem.empty(rows, k, dtype=dtype, device=device)
-            self.y_back = symm_mem.empty(rows, n_out, dtype=dtype, device=device)
+            self.y_out = symm_mem.empty(max(num_tokens, 1), n_out, dtype=dtype, device=device)
             self.recv.zero_()
-            self.y_back.zero_()
+            self.y_out.zero_()
             self.h_recv = symm_mem.rendezvous(self.recv, grp)
-            self.h_back = symm_mem.rendezvous(self.y_back, grp)
-            self.send = self.y_work = None
+            self.h_out = symm_mem.rendezvous(self.y_out, grp)
+            self.send = self.y_work = self.y_back = None
         else:
             self.send = torch.zeros(rows, k, dtype=dtype, device=device)
             self.recv = torch.zeros(rows, k, dtype=dtype, device=device)
@@ -192,20 +194,24 @@ class FixedCapacityExchange:
             p2p = self.backend == "p2p"
             _lib.check(lib.trb_shard_dispatch(ptr(x), ptr(indices), self.T, self.K, self.world, ptr(self.send),
                                               self.h_recv.buffer_ptrs_dev if p2p else None, self.rank,
+                                              ptr(self.y_out) if p2p else None, self.N,
                                               ptr(self.slot_of), ptr(self.plan), dev, st), "shard_dispatch")
             if p2p:
                 self.h_recv.barrier(channel=0)
             else:
                 dist.all_to_all_single(self.recv, self.send, group=self.group)
             _lib.check(lib.trb_shard_compute(ptr(self.recv), ptr(self.q), ptr(self.m), ptr(self.s),
-                                             ptr(self.y_back) if p2p else ptr(self.y_work), self.world, self.T, self.N,
+                                             None if p2p else ptr(self.y_work), self.world, self.T, self.N,
                                              self.K, self.d_local, self.groupsize,
-                                             self.h_back.buffer_ptrs_dev if p2p else None, self.rank,
+                                             self.h_out.buffer_ptrs_dev if p2p else None, self.rank,
                                              ptr(self.scratch), self.scratch.numel(), dev, st), "shard_compute")
             if p2p:
-                self.h_back.barrier(channel=0)
-            else:
-                dist.all_to_all_single(self.y_back, self.y_work, group=self.group)
+                self.h_out.barrier(channel=0)
+                if base_out is not None:
+                    base_out += self.y_out[: self.T]
+                    return base_out
+                return self.y_out[: self.T]
+            dist.all_to_all_single(self.y_back, self.y_work, group=self.group)
             y = base_out if base_out is not None else torch.empty(self.T, self.N, dtype=x.dtype, device=x.device)
             _lib.check(lib.trb_shard_combine(ptr(self.y_back), ptr(self.slot_of), ptr(y), self.T, self.N, self.world,
                                              int(base_out is not None), dev, st), "shard_combine")
