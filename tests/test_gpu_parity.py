@@ -308,6 +308,38 @@ def test_sbmm_linearity_full_size(cuda):
     assert torch.equal(yp, y[p])
 
 
+# ------------------------------------------------------------------ prefill-sized tiles (tcgen05 kernel)
+@pytest.mark.parametrize("groupsize", [-1, 128])
+@pytest.mark.parametrize("tokens", [40, 256, 300, 700])
+def test_matmul_prefill_tiles(cuda, tokens, groupsize):
+    ops = _ops()
+    q, meta, s = packed(384, 512, groupsize, seed=tokens)
+    x = torch.randn(tokens, 512, dtype=torch.float16, device=cuda, generator=torch.Generator(cuda).manual_seed(tokens))
+    y = ops.matmul_4bit_2_4(q, x, meta, s)
+    check(y, oracle.matmul_2_4(q.cpu().numpy(), x.cpu().numpy(), meta.cpu().numpy(), s.cpu().numpy()))
+    assert torch.equal(y, ops.matmul_4bit_2_4(q, x, meta, s))
+
+
+@pytest.mark.parametrize("groupsize", [-1, 128])
+@pytest.mark.parametrize("base", [False, True])
+def test_sbmm_prefill_segments(cuda, groupsize, base):
+    """Contiguous segments of a few hundred tokens per delta (the prefill configuration's shape)."""
+    ops = _ops()
+    D, K, N = 3, 384, 256
+    qs, metas, ss = packed(N, K, groupsize, seed=23, num=D)
+    counts = [300, 129, 512]
+    idx = np.concatenate([np.full(30, -1)] + [np.full(c, d) for d, c in enumerate(counts)]).astype(np.int32)
+    T = len(idx)
+    x = torch.randn(T, K, dtype=torch.float16, device=cuda, generator=torch.Generator(cuda).manual_seed(5))
+    idx_t = torch.from_numpy(idx).to(cuda)
+    bw = (torch.randn(N, K, device=cuda, generator=torch.Generator(cuda).manual_seed(6)) * 0.02).half() if base else None
+    y = ops.sbmm_4bit_2_4_native(qs, x, metas, ss, idx_t, base_weight=bw)
+    check(y, sbmm_ref(qs, metas, ss, x, idx_t, bw), mean_tol=None if base else MEAN_TOL)
+    p = torch.randperm(T, device=cuda, generator=torch.Generator(cuda).manual_seed(2))
+    yp = ops.sbmm_4bit_2_4_native(qs, x[p].contiguous(), metas, ss, idx_t[p].contiguous(), base_weight=bw)
+    assert torch.equal(yp, y[p])
+
+
 # ------------------------------------------------------------------ bmm
 @pytest.mark.parametrize("b", [1, 4, 16])
 def test_bmm(cuda, b):

@@ -97,6 +97,49 @@ static int launch_cfg(const GemmCall& c, const GemmArgs& a) {
   return cudaGetLastError() == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
 }
 
+// Prefill-sized tiles: the tcgen05 / TMEM kernel.
+static int launch_tc(const GemmCall& c, const GemmArgs& a) {
+  using Cfg = TcCfg;
+  const int slabs = a.K / 32;
+  const int groups = a.grouped ? a.K / 128 : 1;
+  CUtensorMap tx, tq, tm, ts;
+  if (!make_map_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, c.x, (uint64_t)a.rows, (uint64_t)a.K, Cfg::TT, 64,
+                   CU_TENSOR_MAP_SWIZZLE_128B))
+    return TRB_ERR_CUDA;
+  if (!make_map_2d(&tq, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, c.q, (uint64_t)c.num_deltas * slabs, 2ull * a.N, 2, 256,
+                   CU_TENSOR_MAP_SWIZZLE_NONE))
+    return TRB_ERR_CUDA;
+  if (!make_map_2d(&tm, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, c.meta, (uint64_t)c.num_deltas * slabs, (uint64_t)a.N, 2, 128,
+                   CU_TENSOR_MAP_SWIZZLE_NONE))
+    return TRB_ERR_CUDA;
+  if (a.grouped) {
+    if (!make_map_2d(&ts, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, c.s, (uint64_t)c.num_deltas * groups, (uint64_t)a.N, 1, 128,
+                     CU_TENSOR_MAP_SWIZZLE_NONE))
+      return TRB_ERR_CUDA;
+  } else {
+    ts = tm;  // never dereferenced
+  }
+  static bool attr_set[64] = {};
+  if (c.dev >= 0 && c.dev < 64 && !attr_set[c.dev]) {
+    if (cudaFuncSetAttribute(delta_gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_ALLOC) !=
+        cudaSuccess)
+      return TRB_ERR_CUDA;
+    attr_set[c.dev] = true;
+  }
+  int grid = sm_count(c.dev);
+  if (c.sms > 0 && c.sms < grid) grid = c.sms;
+  const int n_stripes = (a.N + 127) / 128;
+  long long max_tiles;
+  if (a.mode == kSegSingle) max_tiles = (a.rows + Cfg::TT - 1) / Cfg::TT;
+  else if (a.mode == kSegIdentity) max_tiles = a.rows;
+  else max_tiles = (long long)a.rows / Cfg::TT + (a.n_seg_ptr ? kMaxSegments : a.n_seg);
+  const long long max_items = max_tiles * n_stripes;
+  if (max_items < grid) grid = (int)(max_items > 0 ? max_items : 1);
+  delta_gemm_tc_kernel<<<grid, Cfg::THREADS, Cfg::SMEM_ALLOC, c.stream>>>(tx, tq, tm, ts, a);
+  return cudaGetLastError() == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
+}
+static_assert(TcCfg::SMEM_ALLOC <= 232448, "shared memory budget of one sm_100 CTA");
+
 using CfgT8 = GemmCfg<1, 2, 4, 16, 6>;
 using CfgT16 = GemmCfg<2, 2, 4, 16, 4>;
 using CfgT32 = GemmCfg<4, 2, 4, 8, 5>;
@@ -109,7 +152,7 @@ int gemm_tile_tokens(int tokens_per_segment) {
   if (tokens_per_segment <= 8) return 8;
   if (tokens_per_segment <= 16) return 16;
   if (tokens_per_segment <= 32) return 32;
-  return 64;
+  return 256;   // tcgen05 kernel
 }
 
 static int check_common(const void* A, const void* B, const void* meta, void* C, const void* s, int N, int T, int K,
@@ -132,6 +175,7 @@ int gemm_dispatch(const GemmCall& c, const GemmArgs& a, int tile_tokens) {
     case 16: return launch_cfg<CfgT16>(c, a);
     case 32: return launch_cfg<CfgT32>(c, a);
     case 64: return launch_cfg<CfgT64>(c, a);
+    case 256: return a.y_peers ? TRB_ERR_KERN_SHAPE : launch_tc(c, a);
     default: return TRB_ERR_KERN_SHAPE;
   }
 }
@@ -236,7 +280,8 @@ int sbmm_indexed_impl(const void* x, const void* qweights, const void* metas, co
   const int segs = num_tokens < num_deltas ? num_tokens : num_deltas;
   int tt = tile_tokens;
   if (tt == 0) tt = gemm_tile_tokens((num_tokens + segs - 1) / segs);
-  if (tt != 8 && tt != 16 && tt != 32 && tt != 64) return TRB_ERR_KERN_SHAPE;
+  if (y_peers && tt > 64) tt = 64;   // the peer-store epilogue exists in the mma.sp kernel only
+  if (tt != 8 && tt != 16 && tt != 32 && tt != 64 && tt != 256) return TRB_ERR_KERN_SHAPE;
   const int max_tiles = trb_route_max_tiles(num_tokens, num_deltas, tt);
   if (max_tiles > kMaxSegments) return TRB_ERR_KERN_SHAPE;
   const size_t tiles8 = (size_t)trb_route_max_tiles(num_tokens, num_deltas, 8);

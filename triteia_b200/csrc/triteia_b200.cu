@@ -5,6 +5,7 @@
 #include "common.cuh"
 #include "route.cuh"
 #include "delta_gemm.cuh"
+#include "delta_gemm_tc.cuh"
 #include "delta_gemm_host.cuh"
 #include "shard.cuh"
 #include "unpack.cuh"
