@@ -236,7 +236,7 @@ def run_gpu_arm(args):
             exchange = sharded.FixedCapacityExchange(TOKENS, K, N_OUT, dev, backend="cuda", qweights=qs, metas=metas,
                                                      scales=ss)
         step_resident = lambda: exchange(x_dev, idx_dev)
-        launches_per_step = 6   # dispatch plan + pack, router + gather + grouped kernel, combine
+        launches_per_step = 5 if exchange_kind == "p2p" else 6   # plan + pack, router + gather + grouped kernel (+ combine)
 
     def step_e2e():
         xd = x_host.to(dev, non_blocking=True)
@@ -380,6 +380,110 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------- other workloads (1 GPU)
+def _event_time(fn, steps, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        fn()
+    b.record()
+    b.synchronize()
+    return a.elapsed_time(b) / steps
+
+
+def run_prefill(args):
+    """BASELINE config 5: 32 deltas 5120x13824 (or 13824x5120 with --shape down), group 128, 8192 tokens in
+    16 contiguous segments of 512 (deltas 0..15); optional SGMV rank-64 LoRA on the same segments.
+    Tensor-bound: flops are dense-equivalent 2*T*K*N (the reference's convention, bench_sbmm.py:17)."""
+    import triteia_b200.ops as ops
+    from triteia_b200 import _lib
+    from triteia_b200.capi import sbmm_2_4
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    k, n = (5120, 13824) if args.shape == "up" else (13824, 5120)
+    T, D, SEG, R = 8192, 32, 16, 64
+    qs, metas, ss = ops.random_packed_deltas(D, k, n, groupsize=128, device=dev, seed=1)
+    g = torch.Generator(dev).manual_seed(0)
+    x = torch.randn(T, k, device=dev, generator=g).half()
+    idx = torch.arange(SEG, device=dev, dtype=torch.int32).repeat_interleave(T // SEG)
+    A = (torch.randn(SEG, k, R, device=dev, generator=g) / k ** 0.5).half()
+    B = (torch.randn(SEG, R, n, device=dev, generator=g) / R ** 0.5).half()
+    uniq = torch.arange(SEG, device=dev, dtype=torch.int32)
+    counts = torch.full((SEG,), T // SEG, device=dev, dtype=torch.int32)
+    starts = (uniq * (T // SEG)).int()
+    yk = torch.empty(T, n, dtype=torch.float16, device=dev)
+    ws = torch.zeros(SEG, n // 8, dtype=torch.int32, device=dev)
+    sampler = ClockSampler(0)
+    sampler.start()
+    t_step = _event_time(lambda: ops.sbmm_4bit_2_4_native(qs, x, metas, ss, idx), args.steps, max(3, args.warmup))
+    t_kern = _event_time(lambda: sbmm_2_4(x, qs, metas, yk, ss, uniq, ws, starts, counts), args.steps, 3)
+    t_lora = _event_time(lambda: ops.lora_sgmv(A, B, x, idx), max(1, args.steps // 4), 2)
+    clocks = sampler.stop()
+    flops = 2.0 * T * k * n
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    dense = float(json.load(open(path))["bf16_tflops"]) if os.path.exists(path) else 1590.0
+    ach = flops / (t_kern * 1e-3) / 1e12
+    line = {"metric": METRIC, "value": T / (t_step * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": t_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"sbmm-prefill-32x{k}x{n}-g128-8192tok-16seg", "sgmv_rank64_ms": t_lora,
+                       "l2": "inputs larger than L2 (442 MB of packed deltas touched, 84-226 MB of activations)"},
+            "gpu_launches": 3 * args.steps,
+            "roofline": {"bound": "tensor", "achieved": ach, "peak": 2 * dense, "unit": "TFLOP/s", "frac": ach / (2 * dense),
+                         "peak_source": "2 x measured dense bf16 burst (MEASURED_PEAKS.json has no sparse entry)",
+                         "frac_of_dense_peak": ach / dense, "kernel": "delta_gemm_tc_kernel", "kernel_ms": t_kern,
+                         "algorithmic_flops": flops, "traffic": None},
+            "clocks": clocks, "device_status": _lib.device_status(0)}
+    print(json.dumps(line))
+
+
+def run_ldmm(args):
+    """BASELINE config 3: fp16 base [11008, 4096] ~N(0, 0.02), 32 per-channel deltas 4096 -> 11008, 32 LoRA
+    adapters of rank 16, 256 decode tokens, ids Zipf(1.2) over the 64 ids through a seeded permutation."""
+    import triteia_b200.ops as ops
+    from triteia_b200 import _lib
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    k, n, T, M, D, R = 4096, 11008, 256, 32, 32, 16
+    qs, metas, ss = ops.random_packed_deltas(D, k, n, groupsize=-1, device=dev, seed=2)
+    g = torch.Generator(dev).manual_seed(0)
+    base = (torch.randn(n, k, device=dev, generator=g) * 0.02).half()
+    A = (torch.randn(M, k, R, device=dev, generator=g) / k ** 0.5).half()
+    B = (torch.randn(M, R, n, device=dev, generator=g) / R ** 0.5).half()
+    x = torch.randn(T, k, device=dev, generator=g).half()
+    rng = np.random.default_rng(0)
+    p = np.arange(1, M + D + 1, dtype=np.float64) ** -1.2
+    ids = rng.permutation(M + D)[rng.choice(M + D, T, p=p / p.sum())].astype(np.int32)
+    idx = torch.from_numpy(ids).to(dev)
+    touched_d = len({int(i) for i in ids if i >= M})
+    touched_l = len({int(i) for i in ids if 0 <= i < M})
+    sampler = ClockSampler(0)
+    sampler.start()
+    t_step = _event_time(lambda: ops.ldmm(idx, x, A, B, qs, metas, ss, base_weight=base), args.steps, max(3, args.warmup))
+    t_base = _event_time(lambda: torch.matmul(x, base.t()), args.steps, 3)
+    clocks = sampler.stop()
+    alg = (n * k * 2 + touched_d * (k * n // 4 + k * n // 8 + n * 2) + touched_l * (k * R + R * n) * 2 + T * k * 2 + T * n * 2)
+    peak, peak_src = peaks()
+    ach = alg / (t_step * 1e-3) / 1e9
+    line = {"metric": "ldmm_tokens_per_s", "value": T / (t_step * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": t_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "ldmm-256tok-4096x11008-32deltas-32lora-r16-zipf1.2", "deltas_touched": touched_d,
+                       "adapters_touched": touched_l, "base_gemm_ms": t_base,
+                       "l2": f"inputs larger than L2 ({alg / 1e6:.0f} MB streamed per step)"},
+            "gpu_launches": 4 * args.steps,
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                         "peak_source": peak_src, "kernel": "whole step (library base GEMM + LoRA + router + gather + grouped kernel)",
+                         "algorithmic_bytes": alg, "traffic": None},
+            "clocks": clocks, "device_status": _lib.device_status(0)}
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -388,7 +492,14 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of CUDA-graph replays")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "ldmm"],
+                    help="decode = the headline sbmm configuration (default); prefill / ldmm: 1-GPU extra legs")
+    ap.add_argument("--shape", default="up", choices=["up", "down"], help="prefill: 5120x13824 (up) or 13824x5120")
     args = ap.parse_args()
+    if args.workload == "prefill":
+        return run_prefill(args)
+    if args.workload == "ldmm":
+        return run_ldmm(args)
     if args.impl == "reference":
         run_reference_arm(args)
     else:

@@ -213,83 +213,110 @@ __global__ void __launch_bounds__(256) lora_indexed_kernel(T* __restrict__ Y, co
 }
 
 // ---- SGMV: y[seg] += x[seg] @ W_seg, 64-token x BN-column tiles on mma.sync m16n8k16 ----
-// grid = (column tiles, token-tile upper bound, problems); CTAs past a segment's end return.
+// grid = (column tiles, token-tile lanes, problems); each CTA walks the token tiles of its problem
+// with stride gridDim.y.  K runs through a 3-stage cp.async ring of 64-deep slices; fragments come
+// from ldmatrix (x4 for the token rows, x2.trans for the row-major weight slice).
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool pred) {
+  const int bytes = pred ? 16 : 0;   // zero-fill when the source is out of range
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr) : "memory");
+}
+
+template <int BN>
+struct SgmvSmem {
+  static constexpr int BK = 64, STAGES = 3;
+  static constexpr int XLD = BK + 8, WLD = BN + 8;              // halves; +8 keeps ldmatrix rows on distinct banks
+  static constexpr int X_BYTES = 64 * XLD * 2, W_BYTES = BK * WLD * 2;
+  static constexpr int STAGE_BYTES = X_BYTES + W_BYTES;
+  static constexpr int BYTES = STAGES * STAGE_BYTES;
+};
+
 template <class T, int BN>
 __global__ void __launch_bounds__(128) sgmv_kernel(T* __restrict__ Y, const T* __restrict__ X,
                                                    const T* const* __restrict__ Wp, const int32_t* __restrict__ seg,
                                                    int d_in, int d_out, int layer_idx) {
-  constexpr int BK = 32;
-  __shared__ __align__(16) T xs[64][BK + 8];
-  __shared__ __align__(16) T ws[BK][BN + 8];
+  using SM = SgmvSmem<BN>;
+  constexpr int BK = SM::BK, STAGES = SM::STAGES;
+  extern __shared__ __align__(16) uint8_t sgmv_smem[];
+  const uint32_t sbase = smem_u32(sgmv_smem);
   const int prob = blockIdx.z;
   const int r0 = max(0, seg[prob]), r1 = seg[prob + 1];
   const int col_base = blockIdx.x * BN;
   const T* W = Wp[prob] + (int64_t)layer_idx * d_in * d_out;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, m = lane & 3;
+  const int k_slices = (d_in + BK - 1) / BK;
 
   for (int row_base = r0 + blockIdx.y * 64; row_base < r1; row_base += gridDim.y * 64) {
-  float acc[BN / 8][4];
-#pragma unroll
-  for (int i = 0; i < BN / 8; ++i)
-#pragma unroll
-    for (int c = 0; c < 4; ++c) acc[i][c] = 0.f;
-
-  for (int k0 = 0; k0 < d_in; k0 += BK) {
-    // x tile: 64 rows x 32 k = 256 vectors of 8
-    for (int v = tid; v < 64 * (BK / 8); v += 128) {
-      const int r = v / (BK / 8), c = (v % (BK / 8)) * 8;
-      uint4 val = make_uint4(0, 0, 0, 0);
-      if (row_base + r < r1 && k0 + c < d_in)
-        val = *reinterpret_cast<const uint4*>(X + (int64_t)(row_base + r) * d_in + k0 + c);
-      *reinterpret_cast<uint4*>(&xs[r][c]) = val;
-    }
-    for (int v = tid; v < BK * (BN / 8); v += 128) {
-      const int r = v / (BN / 8), c = (v % (BN / 8)) * 8;
-      uint4 val = make_uint4(0, 0, 0, 0);
-      if (k0 + r < d_in && col_base + c < d_out)
-        val = *reinterpret_cast<const uint4*>(W + (int64_t)(k0 + r) * d_out + col_base + c);
-      *reinterpret_cast<uint4*>(&ws[r][c]) = val;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int kk = 0; kk < BK; kk += 16) {
-      uint32_t a[4];
-      const T* xr0 = &xs[warp * 16 + g][kk + 2 * m];
-      const T* xr1 = &xs[warp * 16 + g + 8][kk + 2 * m];
-      a[0] = *reinterpret_cast<const uint32_t*>(xr0);
-      a[1] = *reinterpret_cast<const uint32_t*>(xr1);
-      a[2] = *reinterpret_cast<const uint32_t*>(xr0 + 8);
-      a[3] = *reinterpret_cast<const uint32_t*>(xr1 + 8);
-#pragma unroll
-      for (int nt = 0; nt < BN / 8; ++nt) {
-        const int n = nt * 8 + g;
-        const uint16_t* wcol = reinterpret_cast<const uint16_t*>(&ws[0][0]) + n;
-        constexpr int LD = BN + 8;
-        const uint32_t b0 = (uint32_t)wcol[(kk + 2 * m) * LD] | ((uint32_t)wcol[(kk + 2 * m + 1) * LD] << 16);
-        const uint32_t b1 = (uint32_t)wcol[(kk + 2 * m + 8) * LD] | ((uint32_t)wcol[(kk + 2 * m + 9) * LD] << 16);
-        if constexpr (sizeof(T) == 2 && std::is_same<T, __half>::value) mma_m16n8k16(acc[nt], a, b0, b1);
-        else mma_m16n8k16_bf16(acc[nt], a, b0, b1);
+    auto load_slice = [&](int ks, int stage) {
+      const int k0 = ks * BK;
+      const uint32_t xs = sbase + stage * SM::STAGE_BYTES, ws = xs + SM::X_BYTES;
+      for (int v = tid; v < 64 * (BK / 8); v += 128) {
+        const int r = v / (BK / 8), c = (v % (BK / 8)) * 8;
+        const bool ok = row_base + r < r1 && k0 + c < d_in;
+        cp_async16(xs + (r * SM::XLD + c) * 2, ok ? (const void*)(X + (int64_t)(row_base + r) * d_in + k0 + c) : (const void*)X, ok);
       }
+      for (int v = tid; v < BK * (BN / 8); v += 128) {
+        const int r = v / (BN / 8), c = (v % (BN / 8)) * 8;
+        const bool ok = k0 + r < d_in && col_base + c < d_out;
+        cp_async16(ws + (r * SM::WLD + c) * 2, ok ? (const void*)(W + (int64_t)(k0 + r) * d_out + col_base + c) : (const void*)W, ok);
+      }
+    };
+    float acc[BN / 8][4];
+#pragma unroll
+    for (int i = 0; i < BN / 8; ++i)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[i][c] = 0.f;
+
+#pragma unroll
+    for (int p = 0; p < STAGES - 1; ++p) {
+      if (p < k_slices) load_slice(p, p);
+      cp_async_commit();
     }
-    __syncthreads();
-  }
+    for (int ks = 0; ks < k_slices; ++ks) {
+      cp_async_wait<STAGES - 2>();
+      __syncthreads();
+      if (ks + STAGES - 1 < k_slices) load_slice(ks + STAGES - 1, (ks + STAGES - 1) % STAGES);
+      cp_async_commit();
+      const uint32_t xs = sbase + (ks % STAGES) * SM::STAGE_BYTES, ws = xs + SM::X_BYTES;
 #pragma unroll
-  for (int nt = 0; nt < BN / 8; ++nt) {
-    const int col = col_base + nt * 8 + 2 * m;
-    if (col < d_out) {
+      for (int kk = 0; kk < BK; kk += 16) {
+        uint32_t af[4];
+        // rows warp*16 + (lane % 16), k offset kk + 8 * (lane / 16): matrices (r0-7,k0-7),(r8-15,k0-7),(r0-7,k8-15),(r8-15,k8-15)
+        ldmatrix_x4(af, xs + ((warp * 16 + (lane & 15)) * SM::XLD + kk + 8 * (lane >> 4)) * 2);
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int row = row_base + warp * 16 + g + 8 * h;
-        if (row < r1) {
-          uint32_t* yp = reinterpret_cast<uint32_t*>(Y + (int64_t)row * d_out + col);
-          const float2 old = Cvt<T>::to_f2(*yp);
-          T o2[2] = {Cvt<T>::from_f(old.x + acc[nt][2 * h]), Cvt<T>::from_f(old.y + acc[nt][2 * h + 1])};
-          *yp = *reinterpret_cast<uint32_t*>(o2);
+        for (int nt = 0; nt < BN / 8; ++nt) {
+          uint32_t b0, b1;
+          // weight slice rows kk + (lane % 16), columns nt*8..+7, transposed on load
+          ldmatrix_x2_trans(b0, b1, ws + ((kk + (lane & 15)) * SM::WLD + nt * 8) * 2);
+          if constexpr (std::is_same<T, __half>::value) mma_m16n8k16(acc[nt], af, b0, b1);
+          else mma_m16n8k16_bf16(acc[nt], af, b0, b1);
         }
       }
     }
-  }
+    cp_async_wait<0>();
+    __syncthreads();
+#pragma unroll
+    for (int nt = 0; nt < BN / 8; ++nt) {
+      const int col = col_base + nt * 8 + 2 * m;
+      if (col < d_out) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int row = row_base + warp * 16 + g + 8 * h;
+          if (row < r1) {
+            uint32_t* yp = reinterpret_cast<uint32_t*>(Y + (int64_t)row * d_out + col);
+            const float2 old = Cvt<T>::to_f2(*yp);
+            T o2[2] = {Cvt<T>::from_f(old.x + acc[nt][2 * h]), Cvt<T>::from_f(old.y + acc[nt][2 * h + 1])};
+            *yp = *reinterpret_cast<uint32_t*>(o2);
+          }
+        }
+      }
+    }
   }  // token tiles
 }
 
@@ -315,7 +342,9 @@ static void sgmv_launch_bn(void* y, const void* x, const void* w, const void* s,
   int gy = (4 * 148 + col_tiles * num_problems - 1) / (col_tiles * num_problems);
   gy = gy < 1 ? 1 : (gy > 64 ? 64 : gy);
   dim3 grid(col_tiles, gy, num_problems);
-  sgmv_kernel<T, BN><<<grid, 128, 0, st>>>((T*)y, (const T*)x, (const T* const*)w, (const int32_t*)s, d_in, d_out,
+  if (SgmvSmem<BN>::BYTES > 48 * 1024)
+    cudaFuncSetAttribute(sgmv_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SgmvSmem<BN>::BYTES);
+  sgmv_kernel<T, BN><<<grid, 128, SgmvSmem<BN>::BYTES, st>>>((T*)y, (const T*)x, (const T* const*)w, (const int32_t*)s, d_in, d_out,
                                             layer_idx);
 }
 
