@@ -28,7 +28,7 @@ struct TcCfg {
   static constexpr int SW = 2;              // 64-column blocks per stripe (UMMA M = 128)
   static constexpr int KC = 64;             // dense K per pipeline stage (one 128-byte swizzle atom)
   static constexpr int STAGES = 4;
-  static constexpr int DECODE_WARPS = 8;
+  static constexpr int DECODE_WARPS = 16;          // 8 or 16: each lane decodes 16 / DECODE_WARPS weight words per stage
   static constexpr int EPI_WARPS = 4;
   static constexpr int THREADS = (2 + DECODE_WARPS + EPI_WARPS) * 32;
   static constexpr int A_BYTES = 128 * KC * 2;           // 16 KiB
@@ -263,24 +263,31 @@ delta_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
     }
   } else if (warp < 2 + Cfg::DECODE_WARPS) {
     // ------------------------------ decode warps: packed -> A tile ------------------------------
-    // Warp dw handles column block cb = dw / 4 and the row groups g0 = 2 * (dw % 4), g0 + 1; lane =
-    // (slab s, lane-in-quad m, register j): it decodes weight word (s, cb, g, m, j) for both g.
+    // Warp dw handles column block cb and U row groups g of it; lane = (slab s, lane-in-quad m,
+    // register j): it decodes weight word (s, cb, g, m, j) for each of its g.
+    constexpr int U = 16 / Cfg::DECODE_WARPS;
     const int dw = warp - 2;
-    const int cb = dw >> 2;
-    const int s = lane >> 4, m = (lane >> 2) & 3, j = lane & 3;
-    uint32_t q_off[2], m_off[2], s_off[2], st_off[2][4];
+    const int cb = dw / (Cfg::DECODE_WARPS / 2);
+    // Lane bits are (j high, s, m, j low): the 16 lanes of a half warp then hold two rows (j low) x eight
+    // pieces, and when even-j lanes store their K-group-m piece while odd-j lanes store their
+    // group-(m+4) piece (and the other way round in the next instruction) every 8-byte store of a half
+    // warp lands in its own bank pair of the swizzled tile.
+    const int s = (lane >> 3) & 1, m = (lane >> 1) & 3, j = ((lane >> 4) << 1) | (lane & 1);
+    const bool jodd = lane & 1;
+    uint32_t q_off[U], m_off[U], s_off[U], st_off[U][4];
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const int g = 2 * (dw & 3) + u;
+    for (int u = 0; u < U; ++u) {
+      const int g = U * (dw % (Cfg::DECODE_WARPS / 2)) + u;
       q_off[u] = Cfg::Q_OFF + s * 1024 + cb * 512 + (4 * g + m) * 16 + j * 4;
       m_off[u] = Cfg::M_OFF + s * 512 + cb * 256 + (2 * (j & 1) + 32 * (j >> 1) + 4 * g) * 4;
       s_off[u] = Cfg::S_OFF + (cb * 64 + 8 * g + 2 * j) * 2;
       const int n0 = cb * 64 + 8 * g + j;            // block-0 row; block-1 row is n0 + 4
 #pragma unroll
-      for (int p = 0; p < 4; ++p) {                  // pieces: (n0, grp m), (n0, grp m+4), (n1, m), (n1, m+4)
+      for (int t = 0; t < 4; ++t) {                  // store t writes piece p: (n0, grp m), (n0, grp m+4), (n1, m), (n1, m+4)
+        const int p = (t & 2) | ((t & 1) ^ (jodd ? 1 : 0));
         const int n = n0 + 4 * (p >> 1);
         const int kc8 = 8 * s + m + 4 * (p & 1);     // 8-byte piece index inside the 128-byte row
-        st_off[u][p] = Cfg::A_OFF + (n >> 3) * 1024 + (n & 7) * 128 + ((((kc8 >> 1) ^ (n & 7))) << 4) + (kc8 & 1) * 8;
+        st_off[u][t] = Cfg::A_OFF + (n >> 3) * 1024 + (n & 7) * 128 + ((((kc8 >> 1) ^ (n & 7))) << 4) + (kc8 & 1) * 8;
       }
     }
     const uint32_t lut_addr = smem_base + Cfg::LUT_OFF;
@@ -292,8 +299,9 @@ delta_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
       for (int kc = 0; kc < k_chunks; ++kc) {
         mbar_wait(&full_bar[st], phase, dead);
         const uint32_t sb = smem_base + st * Cfg::STAGE_BYTES;
+#ifndef TRB_EXP_TC_NODECODE
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
+        for (int u = 0; u < U; ++u) {
           const uint32_t q = lds32(sb + q_off[u]);
           const uint2 mw = lds64(sb + m_off[u]);       // .x: K 0-15 of the slab, .y: K 16-31; low half n0, high half n1
           uint32_t v[4];                               // stored pairs of pieces 0..3
@@ -308,11 +316,17 @@ delta_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
           const uint32_t nib[4] = {(mw.x >> (4 * m)) & 15u, (mw.y >> (4 * m)) & 15u, (mw.x >> (16 + 4 * m)) & 15u,
                                    (mw.y >> (16 + 4 * m)) & 15u};
 #pragma unroll
-          for (int p = 0; p < 4; ++p) {
-            const uint32_t sel = lds32(lut_addr + nib[p] * 4);
-            sts64(sb + st_off[u][p], __byte_perm(v[p], 0, sel & 0xffffu), __byte_perm(v[p], 0, sel >> 16));
+          for (int t = 0; t < 4; ++t) {
+            const int pa = t, pb = t ^ 1;              // odd-j lanes swap the two K groups of a row
+            const uint32_t val = jodd ? v[pb] : v[pa];
+            const uint32_t nb = jodd ? nib[pb] : nib[pa];
+            // PRMT selector from the 16-entry table: byte q of sel picks the source bytes of output
+            // half q (first stored value at position nb & 3, second at nb >> 2, zero elsewhere).
+            const uint32_t sel = lds32(lut_addr + nb * 4);
+            sts64(sb + st_off[u][t], __byte_perm(val, 0, sel), __byte_perm(val, 0, sel >> 16));
           }
         }
+#endif
         fence_proxy_async();      // the tensor core reads the tile through the async proxy
         __syncwarp();
         if (lane == 0) mbar_arrive(&aready_bar[st]);
