@@ -462,3 +462,113 @@ def test_no_device_side_timeouts(cuda):
     from triteia_b200 import _lib as L
 
     assert L.device_status(0) == 0
+
+
+# ------------------------------------------------------------------ reference test shapes and full-size properties
+def test_sbmm_reference_test_shape_zipf(cuda):
+    """("zipf:1.5", 128 requests, 2 models, 4096 x 12288), sorted — tests/ops/test_sbmm.py:15-31."""
+    ops = _ops()
+    qs, metas, ss = packed(12288, 4096, -1, seed=31, num=2)
+    np.random.seed(3)
+    idx = torch.sort(ops.generate_model_distribution("zipf:1.5", 128, 2, device=cuda)).values.int()
+    x = torch.randn(128, 4096, dtype=torch.float16, device=cuda, generator=torch.Generator(cuda).manual_seed(3))
+    ref = sbmm_ref(qs, metas, ss, x, idx, None)
+    for fn in (ops.sbmm_4bit_2_4_native, ops.sbmm_4bit_2_4_forloop, ops.sbmm_4bit_2_4_multilaunch):
+        check(fn(qs, x, metas, ss, idx), ref)
+
+
+def test_sbmm_tensor_parallel_chunks(cuda):
+    """Column- and row-chunked packing (tests/ops/test_sbmm_tp.py:15-91): concatenated / summed per-chunk
+    outputs equal the unchunked result."""
+    ops = _ops()
+    torch.manual_seed(5)
+    D, K, N, tp = 3, 256, 512, 2
+    uncs, col_parts, row_parts = [], [], []
+    for d in range(D):
+        unc, q, s, meta = ops.gen_sparse_quant4_NT(N, K, device=cuda)
+        uncs.append(unc)
+        col_parts.append(ops.torch_weight_to_sparse_marlin(unc, s, tp_size=tp, chunk_by="column"))
+        row_parts.append(ops.torch_weight_to_sparse_marlin(unc, s, tp_size=tp, chunk_by="row"))
+    x = torch.randn(10, K, dtype=torch.float16, device=cuda)
+    idx = torch.tensor([-1, 0, 0, 1, 1, 1, 2, 2, 2, 2], dtype=torch.int32, device=cuda)
+    ref = ops.sbmm_16bit_forloop(torch.stack(uncs), x, idx).float().cpu().numpy()
+    cols = []
+    for c in range(tp):
+        qs = torch.stack([col_parts[d][0][c] for d in range(D)])
+        ss = torch.stack([col_parts[d][1][c] for d in range(D)])
+        ms = torch.stack([col_parts[d][2][c] for d in range(D)])
+        cols.append(ops.sbmm_4bit_2_4_native(qs, x, ms, ss, idx))
+    check(torch.cat(cols, dim=1), ref, mean_tol=5e-3)
+    acc = 0
+    for c in range(tp):
+        qs = torch.stack([row_parts[d][0][c] for d in range(D)])
+        ss = torch.stack([row_parts[d][1][c] for d in range(D)])
+        ms = torch.stack([row_parts[d][2][c] for d in range(D)])
+        acc = acc + ops.sbmm_4bit_2_4_native(qs, x[:, c * K // tp:(c + 1) * K // tp].contiguous(), ms, ss, idx).float()
+    check(acc, ref, mean_tol=5e-3)
+
+
+def test_bmm_reference_shape(cuda):
+    """b in {4, 8, 16}, 512^3 — tests/ops/test_bmm.py:12-47 (mean-relative < 1e-3)."""
+    ops = _ops()
+    for b in (4, 8):
+        qs, metas, ss = packed(512, 512, -1, seed=40 + b, num=b)
+        x = torch.randn(b, 1, 512, dtype=torch.float16, device=cuda, generator=torch.Generator(cuda).manual_seed(b))
+        y = ops.bmm_4bit_2_4(qs, x, metas, ss)
+        ref = np.stack([oracle.matmul_2_4(qs[i].cpu().numpy(), x[i].cpu().numpy(), metas[i].cpu().numpy(),
+                                          ss[i].cpu().numpy()) for i in range(b)]).reshape(b, 512)
+        check(y.reshape(b, 512), ref, mean_tol=1e-3)
+
+
+def test_ldmm_full_size_properties(cuda):
+    """BASELINE ldmm configuration at full size (4096 -> 11008, 32 deltas + 32 rank-16 adapters, 256 tokens,
+    Zipf(1.2) ids): agreement with the per-id loop path, doubling the input doubles the output, permuting
+    tokens permutes rows; a sample of rows against the oracle."""
+    ops = _ops()
+    K, N, T, M, D, R = 4096, 11008, 256, 32, 32, 16
+    qs, metas, ss = ops.random_packed_deltas(D, K, N, device=cuda, seed=2, scale_lo=0.001, scale_hi=0.01)
+    g = torch.Generator(cuda).manual_seed(0)
+    base = (torch.randn(N, K, device=cuda, generator=g) * 0.02).half()
+    A = (torch.randn(M, K, R, device=cuda, generator=g) / K ** 0.5).half()
+    B = (torch.randn(M, R, N, device=cuda, generator=g) / R ** 0.5).half()
+    x = torch.randn(T, K, device=cuda, generator=g).half()
+    rng = np.random.default_rng(0)
+    p = np.arange(1, M + D + 1, dtype=np.float64) ** -1.2
+    idx = torch.from_numpy(rng.permutation(M + D)[rng.choice(M + D, T, p=p / p.sum())].astype(np.int32)).to(cuda)
+    y = ops.ldmm(idx, x, A, B, qs, metas, ss, base_weight=None)
+    yb = ops.baseline_ldmm(idx, x, A, B, qs, metas, ss, base_weight=None)
+    assert oracle.row_rel_err(y.float().cpu().numpy(), yb.float().cpu().numpy()).max() <= 1e-2
+    y2 = ops.ldmm(idx, (x * 2).contiguous(), A, B, qs, metas, ss)
+    normal = y.abs() >= 1e-2
+    assert torch.allclose(y2.float()[normal], 2 * y.float()[normal], rtol=2e-3, atol=0)   # LoRA adds in fp16
+    perm = torch.randperm(T, device=cuda, generator=torch.Generator(cuda).manual_seed(1))
+    yp = ops.ldmm(idx[perm].contiguous(), x[perm].contiguous(), A, B, qs, metas, ss)
+    assert torch.equal(yp, y[perm])
+    yfull = ops.ldmm(idx, x, A, B, qs, metas, ss, base_weight=base)
+    rows = [0, 17, 101, 255]
+    sub = torch.tensor(rows, device=cuda)
+    ref = oracle.ldmm(idx[sub].cpu().numpy(), x[sub].cpu().numpy(), A.cpu().numpy(), B.cpu().numpy(), qs.cpu().numpy(),
+                      metas.cpu().numpy(), ss.cpu().numpy(), base.cpu().numpy())
+    check(yfull[sub], ref, mean_tol=None)
+
+
+def test_sbmm_prefill_full_size_properties(cuda):
+    """BASELINE prefill configuration (5120 -> 13824, group 128, 8192 tokens in 16 segments of 512, 16 of 32
+    deltas resident here): the tcgen05 path against the oracle on a sample of rows, linearity, and equality
+    with the small-tile kernel on a 24-token slice of the same deltas."""
+    ops = _ops()
+    K, N, T, SEG, D = 5120, 13824, 8192, 16, 16
+    qs, metas, ss = ops.random_packed_deltas(D, K, N, groupsize=128, device=cuda, seed=1, scale_lo=0.001, scale_hi=0.01)
+    x = torch.randn(T, K, device=cuda, generator=torch.Generator(cuda).manual_seed(0)).half()
+    idx = torch.arange(SEG, device=cuda, dtype=torch.int32).repeat_interleave(T // SEG)
+    y = ops.sbmm_4bit_2_4_native(qs, x, metas, ss, idx)
+    y2 = ops.sbmm_4bit_2_4_native(qs, (x * 2).contiguous(), metas, ss, idx)
+    normal = y.abs() >= 1e-3
+    assert torch.equal(y2[normal], (y * 2)[normal])
+    rows = torch.tensor([0, 511, 512, 4095, 8191], device=cuda)
+    ref = oracle.sbmm(qs.cpu().numpy()[[0, 1, 7, 15]], x[rows].cpu().numpy(), metas.cpu().numpy()[[0, 1, 7, 15]],
+                      ss.cpu().numpy()[[0, 1, 7, 15]], np.array([0, 0, 1, 2, 3]))
+    check(y[rows], ref)
+    small = torch.cat([torch.arange(0, 8), torch.arange(512, 520), torch.arange(8184, 8192)]).to(cuda)
+    ys = ops.sbmm_4bit_2_4_native(qs, x[small].contiguous(), metas, ss, idx[small].contiguous())
+    assert oracle.row_rel_err(ys.float().cpu().numpy(), y[small].float().cpu().numpy()).max() <= 2e-3

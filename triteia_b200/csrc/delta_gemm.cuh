@@ -247,7 +247,7 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   // accumulated on their own and scaled once per stage in fp32 (small token tiles); large token
   // tiles scale every weight in fp16 instead, which costs less than scaling many accumulators.
   constexpr bool kPostScale = (NB <= 2);
-  constexpr bool kBulkLoad = (NB <= 2);
+  constexpr bool kBulkLoad = (NB == 1);   // larger tiles would spill: they load slab by slab
   const int box = cb / Cfg::QB, within = cb % Cfg::QB;
   // Per-lane byte offsets inside a stage, fixed for the whole kernel.
   const uint32_t q_off = Cfg::Q_OFF + box * (KS * Cfg::QB * 512) + within * 512 + lane * 16 + kq * SPW * (Cfg::QB * 512);
