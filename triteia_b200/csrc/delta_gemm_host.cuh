@@ -97,9 +97,10 @@ static int launch_cfg(const GemmCall& c, const GemmArgs& a) {
   return cudaGetLastError() == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
 }
 
-// Prefill-sized tiles: the tcgen05 / TMEM kernel.
-static int launch_tc(const GemmCall& c, const GemmArgs& a) {
-  using Cfg = TcCfg;
+// Prefill-sized tiles: the tcgen05 / TMEM kernels (sparse instruction by default; the dense-expanding
+// kernel is kept selectable with TRB_TC_DENSE=1 in the environment for comparison).
+template <class Cfg, class Kernel>
+static int launch_tc_impl(Kernel kernel, const GemmCall& c, const GemmArgs& a) {
   const int slabs = a.K / 32;
   const int groups = a.grouped ? a.K / 128 : 1;
   CUtensorMap tx, tq, tm, ts;
@@ -121,8 +122,7 @@ static int launch_tc(const GemmCall& c, const GemmArgs& a) {
   }
   static bool attr_set[64] = {};
   if (c.dev >= 0 && c.dev < 64 && !attr_set[c.dev]) {
-    if (cudaFuncSetAttribute(delta_gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_ALLOC) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_ALLOC) != cudaSuccess)
       return TRB_ERR_CUDA;
     attr_set[c.dev] = true;
   }
@@ -135,10 +135,18 @@ static int launch_tc(const GemmCall& c, const GemmArgs& a) {
   else max_tiles = (long long)a.rows / Cfg::TT + (a.n_seg_ptr ? kMaxSegments : a.n_seg);
   const long long max_items = max_tiles * n_stripes;
   if (max_items < grid) grid = (int)(max_items > 0 ? max_items : 1);
-  delta_gemm_tc_kernel<<<grid, Cfg::THREADS, Cfg::SMEM_ALLOC, c.stream>>>(tx, tq, tm, ts, a);
+  kernel<<<grid, Cfg::THREADS, Cfg::SMEM_ALLOC, c.stream>>>(tx, tq, tm, ts, a);
   return cudaGetLastError() == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
 }
-static_assert(TcCfg::SMEM_ALLOC <= 232448, "shared memory budget of one sm_100 CTA");
+static int launch_tc(const GemmCall& c, const GemmArgs& a) {
+  static const bool dense = [] {
+    const char* e = getenv("TRB_TC_DENSE");
+    return e != nullptr && e[0] == '1';
+  }();
+  if (dense) return launch_tc_impl<TcCfg>(delta_gemm_tc_kernel, c, a);
+  return launch_tc_impl<TcSpCfg>(delta_gemm_tcsp_kernel, c, a);
+}
+static_assert(TcCfg::SMEM_ALLOC <= 232448 && TcSpCfg::SMEM_ALLOC <= 232448, "shared memory budget of one sm_100 CTA");
 
 using CfgT8 = GemmCfg<1, 2, 4, 16, 6>;
 using CfgT16 = GemmCfg<2, 2, 4, 16, 4>;

@@ -1,0 +1,358 @@
+// Grouped 2:4-sparse int4 delta GEMM for prefill-sized token tiles on the SPARSE fifth-generation
+// tensor-core instruction: tcgen05.mma.sp (kind::f16, M = 128 output features x N = 256 tokens x
+// K = 32 dense per instruction), A operand = the STORED halves of the 2:4 weights in shared memory
+// (16 per row and instruction), 2:4 metadata in tensor memory, fp32 accumulator in tensor memory.
+//
+// Per 64-K chunk and per CTA:
+//   producer warp   TMA: packed weights + metadata + scales of a 128-column stripe and the activation
+//                   tile [256 tokens x 64 K] (128-byte swizzle, the B operand as it lands)
+//   8 decode warps  nibbles -> fp16 (x group scale) stored as half2 pairs into the compressed A tile
+//                   [128 features x 32 stored halves] (64-byte swizzle, K-major); the same warps copy
+//                   the chunk's metadata into TMEM with tcgen05.st: the packed format already holds,
+//                   per 32-K slab, one 16-bit field per row and K half in the tensor core's ordered
+//                   2-bit-index form, so a TMEM cell (lane = 16*(row/16) + 8*(K half) + row%8) is two
+//                   such fields (rows r and r + 8) picked from two packed words with one PRMT
+//   MMA warp        one thread issues 2 tcgen05.mma.sp per chunk; the metadata operand is the even
+//                   column of the chunk's column pair, the instruction descriptor's id2 selects the
+//                   slab; tcgen05.commit hands the stage back / publishes the tile
+//   4 epilogue warps tcgen05.ld, scale, convert, 32 consecutive features of one token per warp store
+// TMEM: columns [0, 256) accumulator, [256, 264) metadata (a column pair per pipeline stage).
+#pragma once
+
+#include "delta_gemm_tc.cuh"
+
+namespace trb {
+
+struct TcSpCfg {
+  static constexpr int TT = 256;
+  static constexpr int SW = 2;
+  static constexpr int KC = 64;             // dense K per stage = two sparse MMAs
+  static constexpr int STAGES = 4;
+  static constexpr int DECODE_WARPS = 8;
+  static constexpr int EPI_WARPS = 4;
+  static constexpr int THREADS = (2 + DECODE_WARPS + EPI_WARPS) * 32;
+  static constexpr int A_BYTES = 128 * (KC / 2) * 2;     // 8 KiB of stored halves
+  static constexpr int B_BYTES = TT * KC * 2;            // 32 KiB
+  static constexpr int Q_BYTES = 2 * 256 * 4;
+  static constexpr int M_BYTES = 2 * 128 * 4;
+  static constexpr int S_BYTES = 256;
+  static constexpr int A_OFF = 0;
+  static constexpr int B_OFF = A_OFF + A_BYTES;
+  static constexpr int Q_OFF = B_OFF + B_BYTES;
+  static constexpr int M_OFF = Q_OFF + Q_BYTES;
+  static constexpr int S_OFF = M_OFF + M_BYTES;
+  static constexpr int STAGE_BYTES = (S_OFF + S_BYTES + 1023) / 1024 * 1024;
+  static constexpr int ROWS_OFF = STAGES * STAGE_BYTES;                   // int [TT] output rows
+  static constexpr int PREFIX_OFF = ROWS_OFF + TT * 4;
+  static constexpr int BAR_OFF = PREFIX_OFF + (kMaxSegments + 2) * 4;
+  static constexpr int NUM_BARS = 3 * STAGES + 2;
+  static constexpr int SMEM_BYTES = BAR_OFF + NUM_BARS * 8 + 16;
+  static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;
+  static constexpr uint32_t TMEM_COLS = 512;
+  static constexpr uint32_t META_COL = 256;             // even: column pairs start on even columns
+};
+
+// K-major, 64-byte swizzle: rows of 64 bytes, 8-row groups 512 bytes apart, layout type 4.
+__device__ __forceinline__ uint64_t tc_smem_desc_sw64(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(512 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)4 << 61;
+  return d;
+}
+
+// Sparse kind::f16: the dense descriptor plus the sparsity flag (bit 2) and the metadata id (bits 0-1).
+__device__ __forceinline__ void tc_mma_sp_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t e_tmem,
+                                              uint32_t id2, uint32_t accumulate) {
+  const uint32_t idesc = kTcIdesc | (1u << 2) | (id2 & 3u);
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.sp.cta_group::1.kind::f16 [%0], %1, %2, [%9], %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u),
+        "r"(e_tmem)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_st1(uint32_t taddr, uint32_t v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+
+__global__ void __launch_bounds__(TcSpCfg::THREADS, 1)
+delta_gemm_tcsp_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_q,
+                       const __grid_constant__ CUtensorMap tm_m, const __grid_constant__ CUtensorMap tm_s,
+                       const GemmArgs a) {
+  using Cfg = TcSpCfg;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  int* rows = reinterpret_cast<int*>(smem + Cfg::ROWS_OFF);
+  int* prefix = reinterpret_cast<int*>(smem + Cfg::PREFIX_OFF);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::BAR_OFF);   // TMA data of a stage landed
+  uint64_t* aready_bar = full_bar + STAGES;                                // A tile + metadata of a stage written
+  uint64_t* empty_bar = aready_bar + STAGES;                               // MMAs of a stage retired
+  uint64_t* accready_bar = empty_bar + STAGES;                             // accumulator complete
+  uint64_t* accfree_bar = accready_bar + 1;                                // accumulator drained
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accfree_bar + 1);
+  volatile int* dead = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  int n_seg = a.n_seg_ptr ? *a.n_seg_ptr : a.n_seg;
+  n_seg = max(0, min(n_seg, kMaxSegments));
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&aready_bar[s], Cfg::DECODE_WARPS);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(accready_bar, 1);
+    mbar_init(accfree_bar, Cfg::EPI_WARPS);
+    *dead = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(Cfg::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  int total_tiles;
+  if (a.mode == kSegList) {
+    if (warp == 0) {
+      int running = 0;
+      for (int base = 0; base < n_seg; base += 32) {
+        const int s = base + lane;
+        int c = 0;
+        if (s < n_seg) {
+          const int cnt = a.seg_count[s];
+          c = cnt > 0 ? (cnt + Cfg::TT - 1) / Cfg::TT : 0;
+        }
+        int inc = c;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int v = __shfl_up_sync(0xffffffffu, inc, o);
+          if (lane >= o) inc += v;
+        }
+        if (s < n_seg) prefix[s] = running + inc - c;
+        running += __shfl_sync(0xffffffffu, inc, 31);
+      }
+      if (lane == 0) prefix[n_seg] = running;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (a.mode == kSegList) total_tiles = prefix[n_seg];
+  else total_tiles = a.mode == kSegSingle ? (a.rows + Cfg::TT - 1) / Cfg::TT : a.rows;
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int n_stripes = (a.N + 127) / 128;
+  const int n_items = total_tiles * n_stripes;
+  const int slabs = a.K / 32;
+  const int k_chunks = a.K / Cfg::KC;
+  const int groups = a.grouped ? a.K / 128 : 1;
+  const uint32_t smem_base = smem_u32(smem);
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      prefetch_tmap(&tm_x);
+      prefetch_tmap(&tm_q);
+      prefetch_tmap(&tm_m);
+      if (a.grouped) prefetch_tmap(&tm_s);
+      const uint64_t pol_w = policy_evict_first();
+      const uint64_t pol_x = policy_evict_last();
+      const uint32_t stage_tx = Cfg::B_BYTES + Cfg::Q_BYTES + Cfg::M_BYTES + (a.grouped ? Cfg::S_BYTES : 0);
+      int st = 0;
+      uint32_t phase = 0;
+      for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+        const WorkItem w = decode_item<Cfg>(a, prefix, n_seg, n_stripes, item);
+        if (!w.ok) continue;
+        for (int kc = 0; kc < k_chunks; ++kc) {
+          mbar_wait(&empty_bar[st], phase ^ 1, dead);
+          uint8_t* sbase = smem + st * Cfg::STAGE_BYTES;
+          mbar_arrive_expect_tx(&full_bar[st], stage_tx);
+          tma_load_2d_hint(sbase + Cfg::B_OFF, &tm_x, kc * Cfg::KC, w.row0, &full_bar[st], pol_x);
+          const int wrow = w.delta * slabs + kc * 2;
+          tma_load_2d_hint(sbase + Cfg::Q_OFF, &tm_q, (w.col0 / 64) * 128, wrow, &full_bar[st], pol_w);
+          tma_load_2d_hint(sbase + Cfg::M_OFF, &tm_m, (w.col0 / 64) * 64, wrow, &full_bar[st], pol_w);
+          if (a.grouped)
+            tma_load_2d_hint(sbase + Cfg::S_OFF, &tm_s, w.col0, w.delta * groups + kc / 2, &full_bar[st], pol_w);
+          if (++st == STAGES) { st = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      int st = 0;
+      uint32_t phase = 0, use = 0;
+      for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+        const WorkItem w = decode_item<Cfg>(a, prefix, n_seg, n_stripes, item);
+        if (!w.ok) continue;
+        mbar_wait(accfree_bar, (use & 1) ^ 1, dead);
+        tc_fence_after();
+        for (int kc = 0; kc < k_chunks; ++kc) {
+          mbar_wait(&full_bar[st], phase, dead);
+          mbar_wait(&aready_bar[st], phase, dead);
+          tc_fence_after();
+          const uint32_t sb = smem_base + st * Cfg::STAGE_BYTES;
+          const uint64_t adesc = tc_smem_desc_sw64(sb + Cfg::A_OFF);
+          const uint64_t bdesc = tc_smem_desc(sb + Cfg::B_OFF);
+          const uint32_t e_tmem = tmem_base + Cfg::META_COL + 2 * st;
+#pragma unroll
+          for (int k = 0; k < 2; ++k)   // per instruction: 32 bytes of stored A, 64 bytes of B, metadata column k of the pair
+            tc_mma_sp_f16(tmem_base, adesc + 2 * k, bdesc + 4 * k, e_tmem, k, (kc > 0 || k > 0) ? 1u : 0u);
+          tc_commit(&empty_bar[st]);
+          if (++st == STAGES) { st = 0; phase ^= 1; }
+        }
+        tc_commit(accready_bar);
+        ++use;
+      }
+    }
+  } else if (warp < 2 + Cfg::DECODE_WARPS) {
+    // ------------------------------ decode warps: packed -> compressed A tile + metadata ------------------------------
+    // Warp dw handles column block cb = dw / 4 and row groups g = 2 * (dw % 4) + u; lane bits are
+    // (j high, slab s, lane-in-quad m, j low): it decodes weight word (s, cb, g, m, j) for u = 0, 1.
+    const int dw = warp - 2;
+    const int cb = dw >> 2;
+    const int s = (lane >> 3) & 1, m = (lane >> 1) & 3, j = ((lane >> 4) << 1) | (lane & 1);
+    uint32_t q_off[2], s_off[2], st_off[2][4];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int g = 2 * (dw & 3) + u;
+      q_off[u] = Cfg::Q_OFF + s * 1024 + cb * 512 + (4 * g + m) * 16 + j * 4;
+      s_off[u] = Cfg::S_OFF + (cb * 64 + 8 * g + 2 * j) * 2;
+      const int n0 = cb * 64 + 8 * g + j;            // block-0 row; block-1 row is n0 + 4
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {                  // pairs: (n0, grp m), (n0, grp m+4), (n1, m), (n1, m+4)
+        const int n = n0 + 4 * (p >> 1);
+        const int kc4 = 8 * s + m + 4 * (p & 1);     // 4-byte pair index inside the 64-byte row (= K group of the chunk)
+        st_off[u][p] = Cfg::A_OFF + (n >> 3) * 512 + (n & 7) * 64 + ((((kc4 >> 2) ^ ((n >> 1) & 3))) << 4) + (kc4 & 3) * 4;
+      }
+    }
+    // Metadata duty: TMEM lanes of this warp's quadrant, slab ms of the chunk.  Lane L of the tile is
+    // (row block L / 16, K half (L / 8) % 2, row L % 8): its cell is the 16-bit field of that K half for
+    // rows r = 16 * (L / 16) + L % 8 (low) and r + 8 (high).  Row r of the stripe is column block r / 64,
+    // group g = (r % 64) / 8, position r % 8 = j + 4 * hi: its field is the low (hi = 0) or high half of
+    // metadata word 2 * (j & 1) + 32 * (j >> 1) + 4 * g + (K half) of that block; r + 8 is group g + 1.
+    const int quad = warp & 3;
+    const int ms = dw >> 2;
+    const int L = quad * 32 + lane;
+    const int mr = 16 * (L >> 4) + (L & 7);
+    const int mk1 = (L >> 3) & 1;
+    const int mj = mr & 3, mhi = (mr >> 2) & 1, mg = (mr & 63) >> 3;
+    const uint32_t ma_off = Cfg::M_OFF + ms * 512 + ((mr >> 6) * 64 + 2 * (mj & 1) + 32 * (mj >> 1) + 4 * mg + mk1) * 4;
+    const uint32_t msel = mhi ? 0x7632u : 0x5410u;
+    const uint32_t e_lane = tmem_base + ((uint32_t)(quad * 32) << 16) + Cfg::META_COL + ms;
+
+    int st = 0;
+    uint32_t phase = 0;
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+      const WorkItem w = decode_item<Cfg>(a, prefix, n_seg, n_stripes, item);
+      if (!w.ok) continue;
+      for (int kc = 0; kc < k_chunks; ++kc) {
+        mbar_wait(&full_bar[st], phase, dead);
+        const uint32_t sb = smem_base + st * Cfg::STAGE_BYTES;
+#ifndef TRB_EXP_TC_NODECODE
+        {
+          const uint32_t wa = lds32(sb + ma_off), wb = lds32(sb + ma_off + 16);
+          tc_st1(e_lane + 2 * st, __byte_perm(wa, wb, msel));
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const uint32_t q = lds32(sb + q_off[u]);
+          uint32_t v[4];
+          int4x4_to_half2x2(q, v[0], v[1]);
+          int4x4_to_half2x2(q >> 8, v[2], v[3]);
+          if (a.grouped) {
+            const uint32_t sc = lds32(sb + s_off[u]);  // (scale of n0, scale of n1)
+            const uint32_t s0 = __byte_perm(sc, 0, 0x1010), s1 = __byte_perm(sc, 0, 0x3232);
+            v[0] = hmul2_u32(v[0], s0); v[1] = hmul2_u32(v[1], s0);
+            v[2] = hmul2_u32(v[2], s1); v[3] = hmul2_u32(v[3], s1);
+          }
+#pragma unroll
+          for (int p = 0; p < 4; ++p) sts32(sb + st_off[u][p], v[p]);
+        }
+#endif
+        tc_wait_st();
+        fence_proxy_async();      // the tensor core reads the A tile through the async proxy
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&aready_bar[st]);
+        if (++st == STAGES) { st = 0; phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue warps ------------------------------
+    const int ew = warp - 2 - Cfg::DECODE_WARPS;
+    const int quad = warp & 3;
+    uint32_t use = 0;
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+      const WorkItem w = decode_item<Cfg>(a, prefix, n_seg, n_stripes, item);
+      if (!w.ok) continue;
+      for (int t = ew * 32 + lane; t < Cfg::TT; t += Cfg::EPI_WARPS * 32) {
+        int r = -1;
+        if (t < w.valid) {
+          r = w.row0 + t;
+          if (a.row_map) r = a.row_map[r];
+          if (r < 0 || r >= a.rows) r = -1;
+        }
+        rows[t] = r;
+      }
+      const int n = w.col0 + quad * 32 + lane;
+      float sf = 1.f;
+      if (!a.grouped && n < a.N) sf = __half2float(a.scales[(size_t)w.delta * a.N + n]);
+      named_bar_sync(4, Cfg::EPI_WARPS * 32);
+      mbar_wait(accready_bar, use & 1, dead);
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
+      const int nbatch = (w.valid + 31) >> 5;
+      for (int b = 0; b < nbatch; ++b) {
+        uint32_t v[32];
+        tc_ld32(taddr + b * 32, v);
+        tc_wait_ld();
+        if (b == nbatch - 1) {
+          // The accumulator is in registers: the next item's MMAs may overwrite it.
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(accfree_bar);
+        }
+        if (n < a.N) {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const int r = rows[b * 32 + c];
+            if (r >= 0) {
+              __half* yp = a.y + (size_t)r * a.N + n;
+              float val = __uint_as_float(v[c]) * sf;
+              if (a.accumulate) val += __half2float(*yp);
+              *yp = __float2half_rn(val);
+            }
+          }
+        }
+      }
+      named_bar_sync(4, Cfg::EPI_WARPS * 32);          // rows[] is rewritten for the next item after this
+      ++use;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::TMEM_COLS) : "memory");
+  }
+}
+
+}  // namespace trb
