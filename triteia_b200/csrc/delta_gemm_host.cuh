@@ -144,6 +144,8 @@ static int launch_tc(const GemmCall& c, const GemmArgs& a) {
     return e != nullptr && e[0] == '1';
   }();
   if (dense) return launch_tc_impl<TcCfg>(delta_gemm_tc_kernel, c, a);
+  // The sparse kernel writes y in 16-byte pieces of 8 output features.
+  if ((reinterpret_cast<uintptr_t>(a.y) & 15) != 0 || (a.N & 7) != 0) return TRB_ERR_KERN_SHAPE;
   return launch_tc_impl<TcSpCfg>(delta_gemm_tcsp_kernel, c, a);
 }
 static_assert(TcCfg::SMEM_ALLOC <= 232448 && TcSpCfg::SMEM_ALLOC <= 232448, "shared memory budget of one sm_100 CTA");

@@ -43,7 +43,8 @@ struct TcSpCfg {
   static constexpr int S_OFF = M_OFF + M_BYTES;
   static constexpr int STAGE_BYTES = (S_OFF + S_BYTES + 1023) / 1024 * 1024;
   static constexpr int ROWS_OFF = STAGES * STAGE_BYTES;                   // int [TT] output rows
-  static constexpr int PREFIX_OFF = ROWS_OFF + TT * 4;
+  static constexpr int XPOSE_OFF = ROWS_OFF + TT * 4;                     // [EPI_WARPS][32 tokens][32 features] halves
+  static constexpr int PREFIX_OFF = XPOSE_OFF + EPI_WARPS * 2048;
   static constexpr int BAR_OFF = PREFIX_OFF + (kMaxSegments + 2) * 4;
   static constexpr int NUM_BARS = 3 * STAGES + 2;
   static constexpr int SMEM_BYTES = BAR_OFF + NUM_BARS * 8 + 16;
@@ -329,17 +330,36 @@ delta_gemm_tcsp_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
           __syncwarp();
           if (lane == 0) mbar_arrive(accfree_bar);
         }
-        if (n < a.N) {
+        // Transpose the 32-token x 32-feature block through a private 2 KiB patch of shared memory, so
+        // that a lane stores 8 consecutive features (16 bytes) of one token instead of one feature.
+        {
+          __half* patch = reinterpret_cast<__half*>(smem + Cfg::XPOSE_OFF + ew * 2048);
 #pragma unroll
-          for (int c = 0; c < 32; ++c) {
+          for (int c = 0; c < 32; ++c) patch[c * 32 + lane] = __float2half_rn(__uint_as_float(v[c]) * sf);
+          __syncwarp();
+          const int f8 = (lane & 3) * 8;                    // feature offset of this lane's 16-byte piece
+          const int nb = w.col0 + quad * 32 + f8;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int c = i * 8 + (lane >> 2);              // token of the batch
             const int r = rows[b * 32 + c];
-            if (r >= 0) {
-              __half* yp = a.y + (size_t)r * a.N + n;
-              float val = __uint_as_float(v[c]) * sf;
-              if (a.accumulate) val += __half2float(*yp);
-              *yp = __float2half_rn(val);
+            if (r >= 0 && nb < a.N) {
+              uint4 o = *reinterpret_cast<const uint4*>(patch + c * 32 + f8);
+              uint4* yp = reinterpret_cast<uint4*>(a.y + (size_t)r * a.N + nb);
+              if (a.accumulate) {
+                const uint4 old = *yp;
+                __half2* oh = reinterpret_cast<__half2*>(&o);
+                const __half2* ph = reinterpret_cast<const __half2*>(&old);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 x = __half22float2(oh[e]), y2 = __half22float2(ph[e]);
+                  oh[e] = __floats2half2_rn(x.x + y2.x, x.y + y2.y);
+                }
+              }
+              *yp = o;
             }
           }
+          __syncwarp();
         }
       }
       named_bar_sync(4, Cfg::EPI_WARPS * 32);          // rows[] is rewritten for the next item after this
