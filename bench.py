@@ -435,7 +435,7 @@ def run_prefill(args):
             "gpu_launches": 3 * args.steps,
             "roofline": {"bound": "tensor", "achieved": ach, "peak": 2 * dense, "unit": "TFLOP/s", "frac": ach / (2 * dense),
                          "peak_source": "2 x measured dense bf16 burst (MEASURED_PEAKS.json has no sparse entry)",
-                         "frac_of_dense_peak": ach / dense, "kernel": "delta_gemm_tc_kernel", "kernel_ms": t_kern,
+                         "frac_of_dense_peak": ach / dense, "kernel": ("delta_gemm_tc_kernel" if os.environ.get("TRB_TC_DENSE") == "1" else "delta_gemm_tcsp_kernel"), "kernel_ms": t_kern,
                          "algorithmic_flops": flops, "traffic": None},
             "clocks": clocks, "device_status": _lib.device_status(0)}
     print(json.dumps(line))

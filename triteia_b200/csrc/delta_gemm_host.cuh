@@ -104,7 +104,7 @@ static int launch_tc_impl(Kernel kernel, const GemmCall& c, const GemmArgs& a) {
   const int slabs = a.K / 32;
   const int groups = a.grouped ? a.K / 128 : 1;
   CUtensorMap tx, tq, tm, ts;
-  if (!make_map_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, c.x, (uint64_t)a.rows, (uint64_t)a.K, Cfg::TT, 64,
+  if (!make_map_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, c.x, (uint64_t)a.rows, (uint64_t)a.K, Cfg::B_ROWS, 64,
                    CU_TENSOR_MAP_SWIZZLE_128B))
     return TRB_ERR_CUDA;
   if (!make_map_2d(&tq, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, c.q, (uint64_t)c.num_deltas * slabs, 2ull * a.N, 2, 256,
@@ -120,35 +120,59 @@ static int launch_tc_impl(Kernel kernel, const GemmCall& c, const GemmArgs& a) {
   } else {
     ts = tm;  // never dereferenced
   }
-  static bool attr_set[64] = {};
+  static bool attr_set[64] = {};   // one per instantiation of this template, that is per kernel
   if (c.dev >= 0 && c.dev < 64 && !attr_set[c.dev]) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_ALLOC) != cudaSuccess)
       return TRB_ERR_CUDA;
     attr_set[c.dev] = true;
   }
+  constexpr int ctas = Cfg::CTAS;
   int grid = sm_count(c.dev);
   if (c.sms > 0 && c.sms < grid) grid = c.sms;
-  const int n_stripes = (a.N + 127) / 128;
+  grid /= ctas;                      // work items go to CTAs, or to clusters of two
+  if (grid < 1) grid = 1;
+  const int n_stripes = (a.N + Cfg::SW * 64 - 1) / (Cfg::SW * 64);
   long long max_tiles;
   if (a.mode == kSegSingle) max_tiles = (a.rows + Cfg::TT - 1) / Cfg::TT;
   else if (a.mode == kSegIdentity) max_tiles = a.rows;
   else max_tiles = (long long)a.rows / Cfg::TT + (a.n_seg_ptr ? kMaxSegments : a.n_seg);
   const long long max_items = max_tiles * n_stripes;
   if (max_items < grid) grid = (int)(max_items > 0 ? max_items : 1);
-  kernel<<<grid, Cfg::THREADS, Cfg::SMEM_ALLOC, c.stream>>>(tx, tq, tm, ts, a);
-  return cudaGetLastError() == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
+  if constexpr (ctas == 1) {
+    kernel<<<grid, Cfg::THREADS, Cfg::SMEM_ALLOC, c.stream>>>(tx, tq, tm, ts, a);
+    return cudaGetLastError() == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
+  } else {
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(grid * ctas);
+    lc.blockDim = dim3(Cfg::THREADS);
+    lc.dynamicSmemBytes = Cfg::SMEM_ALLOC;
+    lc.stream = c.stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = ctas;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    lc.attrs = at;
+    lc.numAttrs = 1;
+    return cudaLaunchKernelEx(&lc, kernel, tx, tq, tm, ts, a) == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
+  }
 }
 static int launch_tc(const GemmCall& c, const GemmArgs& a) {
   static const bool dense = [] {
     const char* e = getenv("TRB_TC_DENSE");
     return e != nullptr && e[0] == '1';
   }();
+  static const bool single = [] {
+    const char* e = getenv("TRB_TC_PAIR");
+    return e != nullptr && e[0] == '0';
+  }();
   if (dense) return launch_tc_impl<TcCfg>(delta_gemm_tc_kernel, c, a);
   // The sparse kernel writes y in 16-byte pieces of 8 output features.
   if ((reinterpret_cast<uintptr_t>(a.y) & 15) != 0 || (a.N & 7) != 0) return TRB_ERR_KERN_SHAPE;
-  return launch_tc_impl<TcSpCfg>(delta_gemm_tcsp_kernel, c, a);
+  if (single) return launch_tc_impl<TcSpCfg>(delta_gemm_tcsp_kernel<false>, c, a);
+  return launch_tc_impl<TcSpPairCfg>(delta_gemm_tcsp_kernel<true>, c, a);
 }
-static_assert(TcCfg::SMEM_ALLOC <= 232448 && TcSpCfg::SMEM_ALLOC <= 232448, "shared memory budget of one sm_100 CTA");
+static_assert(TcCfg::SMEM_ALLOC <= 232448 && TcSpCfg::SMEM_ALLOC <= 232448 && TcSpPairCfg::SMEM_ALLOC <= 232448, "shared memory budget of one sm_100 CTA");
 
 using CfgT8 = GemmCfg<1, 2, 4, 16, 6>;
 using CfgT16 = GemmCfg<2, 2, 4, 16, 4>;

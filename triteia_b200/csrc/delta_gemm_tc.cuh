@@ -25,7 +25,9 @@ namespace trb {
 
 struct TcCfg {
   static constexpr int TT = 256;            // tokens per tile (UMMA N)
+  static constexpr int B_ROWS = TT;         // tokens staged by one CTA
   static constexpr int SW = 2;              // 64-column blocks per stripe (UMMA M = 128)
+  static constexpr int CTAS = 1;
   static constexpr int KC = 64;             // dense K per pipeline stage (one 128-byte swizzle atom)
   static constexpr int STAGES = 4;
   static constexpr int DECODE_WARPS = 16;          // 8 or 16: each lane decodes 16 / DECODE_WARPS weight words per stage
@@ -299,7 +301,6 @@ delta_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
       for (int kc = 0; kc < k_chunks; ++kc) {
         mbar_wait(&full_bar[st], phase, dead);
         const uint32_t sb = smem_base + st * Cfg::STAGE_BYTES;
-#ifndef TRB_EXP_TC_NODECODE
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           const uint32_t q = lds32(sb + q_off[u]);
@@ -326,7 +327,6 @@ delta_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
             sts64(sb + st_off[u][t], __byte_perm(val, 0, sel), __byte_perm(val, 0, sel >> 16));
           }
         }
-#endif
         fence_proxy_async();      // the tensor core reads the tile through the async proxy
         __syncwarp();
         if (lane == 0) mbar_arrive(&aready_bar[st]);

@@ -23,16 +23,23 @@
 
 namespace trb {
 
-struct TcSpCfg {
+// PAIR: two CTAs of a cluster share one tcgen05.mma.sp.cta_group::2 (M = 256 features, 128 per CTA;
+// each CTA stages half of the token tile), which halves the activation bytes every SM pulls through
+// its shared memory per flop.
+template <bool PAIR_>
+struct TcSpCfgT {
+  static constexpr bool PAIR = PAIR_;
+  static constexpr int CTAS = PAIR ? 2 : 1;
   static constexpr int TT = 256;
-  static constexpr int SW = 2;
+  static constexpr int SW = 2 * CTAS;       // 64-column blocks per work item (128 columns per CTA)
   static constexpr int KC = 64;             // dense K per stage = two sparse MMAs
-  static constexpr int STAGES = 4;
+  static constexpr int STAGES = PAIR ? 6 : 4;
+  static constexpr int B_ROWS = TT / CTAS;  // tokens of the tile staged by one CTA
   static constexpr int DECODE_WARPS = 8;
   static constexpr int EPI_WARPS = 4;
   static constexpr int THREADS = (2 + DECODE_WARPS + EPI_WARPS) * 32;
   static constexpr int A_BYTES = 128 * (KC / 2) * 2;     // 8 KiB of stored halves
-  static constexpr int B_BYTES = TT * KC * 2;            // 32 KiB
+  static constexpr int B_BYTES = B_ROWS * KC * 2;        // 32 KiB, 16 KiB per CTA of a pair
   static constexpr int Q_BYTES = 2 * 256 * 4;
   static constexpr int M_BYTES = 2 * 128 * 4;
   static constexpr int S_BYTES = 256;
@@ -52,6 +59,8 @@ struct TcSpCfg {
   static constexpr uint32_t TMEM_COLS = 512;
   static constexpr uint32_t META_COL = 256;             // even: column pairs start on even columns
 };
+using TcSpCfg = TcSpCfgT<false>;
+using TcSpPairCfg = TcSpCfgT<true>;
 
 // K-major, 64-byte swizzle: rows of 64 bytes, 8-row groups 512 bytes apart, layout type 4.
 __device__ __forceinline__ uint64_t tc_smem_desc_sw64(uint32_t smem_addr) {
@@ -86,11 +95,74 @@ __device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
   asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 
-__global__ void __launch_bounds__(TcSpCfg::THREADS, 1)
+// ---- cluster-of-two helpers ----
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address of the same shared-memory location in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  __syncwarp();
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded like mbar_wait; observes arrivals made by the other CTA of the pair.
+__device__ __forceinline__ void mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* dead) {
+  uint32_t polls = 0;
+  while (!mbar_try_wait_cluster(bar, parity)) {
+    if (*dead) return;
+    if (++polls > kMaxPolls) {
+      *dead = 1;
+      atomicExch(&g_device_status, TRB_ERR_TIMEOUT);
+      return;
+    }
+  }
+}
+// One instruction for both CTAs: M = 256 (128 TMEM lanes in each CTA), N = 256 tokens (128 rows of B
+// from each CTA's shared memory), descriptors and TMEM addresses are CTA-relative and equal in both.
+__device__ __forceinline__ void tc_mma_sp_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t e_tmem,
+                                                   uint32_t id2, uint32_t accumulate) {
+  constexpr uint32_t kIdesc = (1u << 4) | ((256u >> 3) << 17) | ((256u >> 4) << 24) | (1u << 2);
+  const uint32_t idesc = kIdesc | (id2 & 3u);
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.sp.cta_group::2.kind::f16 [%0], %1, %2, [%6], %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(e_tmem)
+      : "memory");
+}
+// Arrive on the barrier at this shared-memory offset in both CTAs once the pair's MMAs issued so far retire.
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"((uint16_t)3)
+               : "memory");
+}
+
+template <bool PAIR>
+__global__ void __launch_bounds__(TcSpCfgT<PAIR>::THREADS, 1)
 delta_gemm_tcsp_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_q,
                        const __grid_constant__ CUtensorMap tm_m, const __grid_constant__ CUtensorMap tm_s,
                        const GemmArgs a) {
-  using Cfg = TcSpCfg;
+  using Cfg = TcSpCfgT<PAIR>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -114,19 +186,26 @@ delta_gemm_tcsp_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&aready_bar[s], Cfg::DECODE_WARPS);
+      mbar_init(&aready_bar[s], Cfg::DECODE_WARPS * Cfg::CTAS);   // pair: the leader's barrier counts both CTAs' warps
       mbar_init(&empty_bar[s], 1);
     }
     mbar_init(accready_bar, 1);
-    mbar_init(accfree_bar, Cfg::EPI_WARPS);
+    mbar_init(accfree_bar, Cfg::EPI_WARPS * Cfg::CTAS);
     *dead = 0;
     fence_mbar_init();
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                 "r"(Cfg::TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                   "r"(Cfg::TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                   "r"(Cfg::TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   int total_tiles;
   if (a.mode == kSegList) {
@@ -153,13 +232,20 @@ delta_gemm_tcsp_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();     // both CTAs' barriers exist before any remote arrive
   tc_fence_after();
   if (a.mode == kSegList) total_tiles = prefix[n_seg];
   else total_tiles = a.mode == kSegSingle ? (a.rows + Cfg::TT - 1) / Cfg::TT : a.rows;
   const uint32_t tmem_base = *tmem_slot;
 
-  const int n_stripes = (a.N + 127) / 128;
+  const int n_stripes = (a.N + Cfg::SW * 64 - 1) / (Cfg::SW * 64);
   const int n_items = total_tiles * n_stripes;
+  // Work items go round-robin over CTAs, or over CTA pairs: CTA `rank` of a pair owns columns
+  // [col0 + 128 * rank, +128) of the item and stages tokens [row0 + 128 * rank, +128) of its tile.
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  const int item0 = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int item_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  const int my_col = (int)rank * 128;
   const int slabs = a.K / 32;
   const int k_chunks = a.K / Cfg::KC;
   const int groups = a.grouped ? a.K / 128 : 1;
@@ -177,14 +263,15 @@ delta_gemm_tcsp_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
       const uint32_t stage_tx = Cfg::B_BYTES + Cfg::Q_BYTES + Cfg::M_BYTES + (a.grouped ? Cfg::S_BYTES : 0);
       int st = 0;
       uint32_t phase = 0;
-      for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-        const WorkItem w = decode_item<Cfg>(a, prefix, n_seg, n_stripes, item);
+      for (int item = item0; item < n_items; item += item_step) {
+        WorkItem w = decode_item<Cfg>(a, prefix, n_seg, n_stripes, item);
+      w.col0 += my_col;
         if (!w.ok) continue;
         for (int kc = 0; kc < k_chunks; ++kc) {
           mbar_wait(&empty_bar[st], phase ^ 1, dead);
           uint8_t* sbase = smem + st * Cfg::STAGE_BYTES;
           mbar_arrive_expect_tx(&full_bar[st], stage_tx);
-          tma_load_2d_hint(sbase + Cfg::B_OFF, &tm_x, kc * Cfg::KC, w.row0, &full_bar[st], pol_x);
+          tma_load_2d_hint(sbase + Cfg::B_OFF, &tm_x, kc * Cfg::KC, w.row0 + (int)rank * Cfg::B_ROWS, &full_bar[st], pol_x);
           const int wrow = w.delta * slabs + kc * 2;
           tma_load_2d_hint(sbase + Cfg::Q_OFF, &tm_q, (w.col0 / 64) * 128, wrow, &full_bar[st], pol_w);
           tma_load_2d_hint(sbase + Cfg::M_OFF, &tm_m, (w.col0 / 64) * 64, wrow, &full_bar[st], pol_w);
@@ -196,29 +283,41 @@ delta_gemm_tcsp_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
+    if (lane == 0 && rank == 0) {
       int st = 0;
       uint32_t phase = 0, use = 0;
-      for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-        const WorkItem w = decode_item<Cfg>(a, prefix, n_seg, n_stripes, item);
+      for (int item = item0; item < n_items; item += item_step) {
+        WorkItem w = decode_item<Cfg>(a, prefix, n_seg, n_stripes, item);
+      w.col0 += my_col;
         if (!w.ok) continue;
-        mbar_wait(accfree_bar, (use & 1) ^ 1, dead);
+        if constexpr (PAIR) mbar_wait_cluster(accfree_bar, (use & 1) ^ 1, dead);
+        else mbar_wait(accfree_bar, (use & 1) ^ 1, dead);
         tc_fence_after();
         for (int kc = 0; kc < k_chunks; ++kc) {
-          mbar_wait(&full_bar[st], phase, dead);
-          mbar_wait(&aready_bar[st], phase, dead);
+          if constexpr (PAIR) {
+            // Every decode warp of both CTAs arrives after its own CTA's TMA data landed and its part of
+            // the A tile and metadata is written: the one barrier covers both CTAs' operands.
+            mbar_wait_cluster(&aready_bar[st], phase, dead);
+          } else {
+            mbar_wait(&full_bar[st], phase, dead);
+            mbar_wait(&aready_bar[st], phase, dead);
+          }
           tc_fence_after();
           const uint32_t sb = smem_base + st * Cfg::STAGE_BYTES;
           const uint64_t adesc = tc_smem_desc_sw64(sb + Cfg::A_OFF);
           const uint64_t bdesc = tc_smem_desc(sb + Cfg::B_OFF);
           const uint32_t e_tmem = tmem_base + Cfg::META_COL + 2 * st;
 #pragma unroll
-          for (int k = 0; k < 2; ++k)   // per instruction: 32 bytes of stored A, 64 bytes of B, metadata column k of the pair
-            tc_mma_sp_f16(tmem_base, adesc + 2 * k, bdesc + 4 * k, e_tmem, k, (kc > 0 || k > 0) ? 1u : 0u);
-          tc_commit(&empty_bar[st]);
+          for (int k = 0; k < 2; ++k) {  // per instruction: 32 bytes of stored A, 64 bytes of B, metadata column k of the pair
+            if constexpr (PAIR) tc_mma_sp_f16_pair(tmem_base, adesc + 2 * k, bdesc + 4 * k, e_tmem, k, (kc > 0 || k > 0) ? 1u : 0u);
+            else tc_mma_sp_f16(tmem_base, adesc + 2 * k, bdesc + 4 * k, e_tmem, k, (kc > 0 || k > 0) ? 1u : 0u);
+          }
+          if constexpr (PAIR) tc_commit_pair(&empty_bar[st]);
+          else tc_commit(&empty_bar[st]);
           if (++st == STAGES) { st = 0; phase ^= 1; }
         }
-        tc_commit(accready_bar);
+        if constexpr (PAIR) tc_commit_pair(accready_bar);
+        else tc_commit(accready_bar);
         ++use;
       }
     }
@@ -258,15 +357,16 @@ delta_gemm_tcsp_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
     const uint32_t msel = mhi ? 0x7632u : 0x5410u;
     const uint32_t e_lane = tmem_base + ((uint32_t)(quad * 32) << 16) + Cfg::META_COL + ms;
 
+    const uint32_t aready_leader = PAIR ? mapa_shared(smem_u32(aready_bar), 0) : 0u;
     int st = 0;
     uint32_t phase = 0;
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-      const WorkItem w = decode_item<Cfg>(a, prefix, n_seg, n_stripes, item);
+    for (int item = item0; item < n_items; item += item_step) {
+      WorkItem w = decode_item<Cfg>(a, prefix, n_seg, n_stripes, item);
+      w.col0 += my_col;
       if (!w.ok) continue;
       for (int kc = 0; kc < k_chunks; ++kc) {
         mbar_wait(&full_bar[st], phase, dead);
         const uint32_t sb = smem_base + st * Cfg::STAGE_BYTES;
-#ifndef TRB_EXP_TC_NODECODE
         {
           const uint32_t wa = lds32(sb + ma_off), wb = lds32(sb + ma_off + 16);
           tc_st1(e_lane + 2 * st, __byte_perm(wa, wb, msel));
@@ -286,12 +386,14 @@ delta_gemm_tcsp_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
 #pragma unroll
           for (int p = 0; p < 4; ++p) sts32(sb + st_off[u][p], v[p]);
         }
-#endif
         tc_wait_st();
         fence_proxy_async();      // the tensor core reads the A tile through the async proxy
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&aready_bar[st]);
+        if (lane == 0) {
+          if constexpr (PAIR) mbar_arrive_cluster(aready_leader + st * 8);
+          else mbar_arrive(&aready_bar[st]);
+        }
         if (++st == STAGES) { st = 0; phase ^= 1; }
       }
     }
@@ -300,8 +402,9 @@ delta_gemm_tcsp_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
     const int ew = warp - 2 - Cfg::DECODE_WARPS;
     const int quad = warp & 3;
     uint32_t use = 0;
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-      const WorkItem w = decode_item<Cfg>(a, prefix, n_seg, n_stripes, item);
+    for (int item = item0; item < n_items; item += item_step) {
+      WorkItem w = decode_item<Cfg>(a, prefix, n_seg, n_stripes, item);
+      w.col0 += my_col;
       if (!w.ok) continue;
       for (int t = ew * 32 + lane; t < Cfg::TT; t += Cfg::EPI_WARPS * 32) {
         int r = -1;
@@ -328,7 +431,10 @@ delta_gemm_tcsp_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
           // The accumulator is in registers: the next item's MMAs may overwrite it.
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(accfree_bar);
+          if (lane == 0) {
+            if constexpr (PAIR) mbar_arrive_cluster(mapa_shared(smem_u32(accfree_bar), 0));
+            else mbar_arrive(accfree_bar);
+          }
         }
         // Transpose the 32-token x 32-feature block through a private 2 KiB patch of shared memory, so
         // that a lane stores 8 consecutive features (16 bytes) of one token instead of one feature.
@@ -369,9 +475,13 @@ delta_gemm_tcsp_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
 
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();   // neither CTA leaves, or frees TMEM, while the other may still touch it
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::TMEM_COLS) : "memory");
+    if constexpr (PAIR)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::TMEM_COLS) : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::TMEM_COLS) : "memory");
   }
 }
 
