@@ -35,7 +35,8 @@ struct TcSpCfgT {
   static constexpr int KC = 64;             // dense K per stage = two sparse MMAs
   static constexpr int STAGES = PAIR ? 6 : 4;
   static constexpr int B_ROWS = TT / CTAS;  // tokens of the tile staged by one CTA
-  static constexpr int DECODE_WARPS = 8;
+  static constexpr int DECODE_TEAMS = 2;    // teams of 8 warps take alternate K chunks
+  static constexpr int DECODE_WARPS = 8 * DECODE_TEAMS;
   static constexpr int EPI_WARPS = 4;
   static constexpr int THREADS = (2 + DECODE_WARPS + EPI_WARPS) * 32;
   static constexpr int A_BYTES = 128 * (KC / 2) * 2;     // 8 KiB of stored halves
@@ -186,7 +187,7 @@ delta_gemm_tcsp_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&aready_bar[s], Cfg::DECODE_WARPS * Cfg::CTAS);   // pair: the leader's barrier counts both CTAs' warps
+      mbar_init(&aready_bar[s], 8 * Cfg::CTAS);   // pair: the leader's barrier counts both CTAs' warps
       mbar_init(&empty_bar[s], 1);
     }
     mbar_init(accready_bar, 1);
@@ -325,7 +326,8 @@ delta_gemm_tcsp_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
     // ------------------------------ decode warps: packed -> compressed A tile + metadata ------------------------------
     // Warp dw handles column block cb = dw / 4 and row groups g = 2 * (dw % 4) + u; lane bits are
     // (j high, slab s, lane-in-quad m, j low): it decodes weight word (s, cb, g, m, j) for u = 0, 1.
-    const int dw = warp - 2;
+    const int team = (warp - 2) >> 3;
+    const int dw = (warp - 2) & 7;
     const int cb = dw >> 2;
     const int s = (lane >> 3) & 1, m = (lane >> 1) & 3, j = ((lane >> 4) << 1) | (lane & 1);
     uint32_t q_off[2], s_off[2], st_off[2][4];
@@ -359,12 +361,16 @@ delta_gemm_tcsp_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
 
     const uint32_t aready_leader = PAIR ? mapa_shared(smem_u32(aready_bar), 0) : 0u;
     int st = 0;
-    uint32_t phase = 0;
+    uint32_t phase = 0, chunk = 0;
     for (int item = item0; item < n_items; item += item_step) {
       WorkItem w = decode_item<Cfg>(a, prefix, n_seg, n_stripes, item);
       w.col0 += my_col;
       if (!w.ok) continue;
-      for (int kc = 0; kc < k_chunks; ++kc) {
+      for (int kc = 0; kc < k_chunks; ++kc, ++chunk) {
+        if ((int)(chunk % Cfg::DECODE_TEAMS) != team) {     // the other team's chunk
+          if (++st == STAGES) { st = 0; phase ^= 1; }
+          continue;
+        }
         mbar_wait(&full_bar[st], phase, dead);
         const uint32_t sb = smem_base + st * Cfg::STAGE_BYTES;
         {
