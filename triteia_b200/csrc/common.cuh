@@ -83,7 +83,7 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volati
   uint32_t polls = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return;
-    if (*dead) return;
+    if ((polls & 15u) == 0 && *dead) return;   // the flag is a shared-memory read: not on every poll
     if (++polls > kMaxPolls) {
       *dead = 1;
       atomicExch(&g_device_status, TRB_ERR_TIMEOUT);

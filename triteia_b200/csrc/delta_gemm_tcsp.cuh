@@ -1,22 +1,35 @@
 // Grouped 2:4-sparse int4 delta GEMM for prefill-sized token tiles on the SPARSE fifth-generation
-// tensor-core instruction: tcgen05.mma.sp (kind::f16, M = 128 output features x N = 256 tokens x
-// K = 32 dense per instruction), A operand = the STORED halves of the 2:4 weights in shared memory
-// (16 per row and instruction), 2:4 metadata in tensor memory, fp32 accumulator in tensor memory.
+// tensor-core instruction: tcgen05.mma.sp (kind::f16, K = 32 dense per instruction), A operand = the
+// STORED halves of the 2:4 weights in shared memory (16 per row and instruction), 2:4 metadata in
+// tensor memory, fp32 accumulator in tensor memory.
+//
+// Two forms of one kernel template:
+//   PAIR (default)  two CTAs of a cluster issue one tcgen05.mma.sp.cta_group::2 per instruction:
+//                   M = 256 output features (128 per CTA: each CTA decodes its own stripe and holds its
+//                   own accumulator and metadata) x N = 256 tokens (each CTA stages 128 of them).  The
+//                   leader CTA's MMA thread issues for both; every decode warp of both CTAs arrives on
+//                   the leader's barrier; tcgen05.commit with a CTA mask hands stages back to both.
+//                   Half the activation bytes per SM and flop: the kernel is bound by what one SM can
+//                   pull through TMA and shared memory, not by the tensor pipe.
+//   single CTA      M = 128 x N = 256 per CTA (kept selectable for comparison).
 //
 // Per 64-K chunk and per CTA:
-//   producer warp   TMA: packed weights + metadata + scales of a 128-column stripe and the activation
-//                   tile [256 tokens x 64 K] (128-byte swizzle, the B operand as it lands)
-//   8 decode warps  nibbles -> fp16 (x group scale) stored as half2 pairs into the compressed A tile
-//                   [128 features x 32 stored halves] (64-byte swizzle, K-major); the same warps copy
-//                   the chunk's metadata into TMEM with tcgen05.st: the packed format already holds,
-//                   per 32-K slab, one 16-bit field per row and K half in the tensor core's ordered
-//                   2-bit-index form, so a TMEM cell (lane = 16*(row/16) + 8*(K half) + row%8) is two
-//                   such fields (rows r and r + 8) picked from two packed words with one PRMT
+//   producer warps  TMA, one thread each: the activation tile [tokens x 64 K] (128-byte swizzle, the B
+//                   operand as it lands) / packed weights + metadata + scales of the CTA's 128 columns
+//   16 decode warps two teams of eight on alternate chunks: nibbles -> fp16 (x group scale) stored as
+//                   half2 pairs into the compressed A tile [128 features x 32 stored halves] (64-byte
+//                   swizzle, K-major); the same warps copy the chunk's metadata into TMEM with
+//                   tcgen05.st: the packed format already holds, per 32-K slab, one 16-bit field per
+//                   row and K half in the tensor core's ordered 2-bit-index form, so a TMEM cell
+//                   (lane = 16*(row/16) + 8*(K half) + row%8) is two such fields (rows r and r + 8)
+//                   picked from two packed words with one PRMT
 //   MMA warp        one thread issues 2 tcgen05.mma.sp per chunk; the metadata operand is the even
 //                   column of the chunk's column pair, the instruction descriptor's id2 selects the
 //                   slab; tcgen05.commit hands the stage back / publishes the tile
-//   4 epilogue warps tcgen05.ld, scale, convert, 32 consecutive features of one token per warp store
-// TMEM: columns [0, 256) accumulator, [256, 264) metadata (a column pair per pipeline stage).
+//   4 epilogue warps tcgen05.ld, scale, convert, transpose 32 x 32 blocks through shared memory and
+//                   store 16-byte pieces (8 features of one token)
+// TMEM: columns [0, 256) accumulator, [256, 256 + 2 * stages) metadata (a column pair per stage).
+// Every wait is bounded; both CTAs of a pair meet at a cluster barrier before either leaves.
 #pragma once
 
 #include "delta_gemm_tc.cuh"
@@ -38,7 +51,7 @@ struct TcSpCfgT {
   static constexpr int DECODE_TEAMS = 2;    // teams of 8 warps take alternate K chunks
   static constexpr int DECODE_WARPS = 8 * DECODE_TEAMS;
   static constexpr int EPI_WARPS = 4;
-  static constexpr int THREADS = (2 + DECODE_WARPS + EPI_WARPS) * 32;
+  static constexpr int THREADS = (3 + DECODE_WARPS + EPI_WARPS) * 32;
   static constexpr int A_BYTES = 128 * (KC / 2) * 2;     // 8 KiB of stored halves
   static constexpr int B_BYTES = B_ROWS * KC * 2;        // 32 KiB, 16 KiB per CTA of a pair
   static constexpr int Q_BYTES = 2 * 256 * 4;
@@ -130,7 +143,7 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
 __device__ __forceinline__ void mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* dead) {
   uint32_t polls = 0;
   while (!mbar_try_wait_cluster(bar, parity)) {
-    if (*dead) return;
+    if ((polls & 15u) == 0 && *dead) return;
     if (++polls > kMaxPolls) {
       *dead = 1;
       atomicExch(&g_device_status, TRB_ERR_TIMEOUT);
@@ -253,31 +266,25 @@ delta_gemm_tcsp_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
   const uint32_t smem_base = smem_u32(smem);
 
   if (warp == 0) {
-    // ------------------------------ TMA producer ------------------------------
+    // ------------------------------ TMA producer: activations ------------------------------
     if (lane == 0) {
       prefetch_tmap(&tm_x);
       prefetch_tmap(&tm_q);
       prefetch_tmap(&tm_m);
       if (a.grouped) prefetch_tmap(&tm_s);
-      const uint64_t pol_w = policy_evict_first();
       const uint64_t pol_x = policy_evict_last();
       const uint32_t stage_tx = Cfg::B_BYTES + Cfg::Q_BYTES + Cfg::M_BYTES + (a.grouped ? Cfg::S_BYTES : 0);
       int st = 0;
       uint32_t phase = 0;
       for (int item = item0; item < n_items; item += item_step) {
         WorkItem w = decode_item<Cfg>(a, prefix, n_seg, n_stripes, item);
-      w.col0 += my_col;
         if (!w.ok) continue;
         for (int kc = 0; kc < k_chunks; ++kc) {
           mbar_wait(&empty_bar[st], phase ^ 1, dead);
           uint8_t* sbase = smem + st * Cfg::STAGE_BYTES;
+          // The stage's one arrival, carrying the bytes of this load and of the weight producer's loads.
           mbar_arrive_expect_tx(&full_bar[st], stage_tx);
           tma_load_2d_hint(sbase + Cfg::B_OFF, &tm_x, kc * Cfg::KC, w.row0 + (int)rank * Cfg::B_ROWS, &full_bar[st], pol_x);
-          const int wrow = w.delta * slabs + kc * 2;
-          tma_load_2d_hint(sbase + Cfg::Q_OFF, &tm_q, (w.col0 / 64) * 128, wrow, &full_bar[st], pol_w);
-          tma_load_2d_hint(sbase + Cfg::M_OFF, &tm_m, (w.col0 / 64) * 64, wrow, &full_bar[st], pol_w);
-          if (a.grouped)
-            tma_load_2d_hint(sbase + Cfg::S_OFF, &tm_s, w.col0, w.delta * groups + kc / 2, &full_bar[st], pol_w);
           if (++st == STAGES) { st = 0; phase ^= 1; }
         }
       }
@@ -289,7 +296,7 @@ delta_gemm_tcsp_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
       uint32_t phase = 0, use = 0;
       for (int item = item0; item < n_items; item += item_step) {
         WorkItem w = decode_item<Cfg>(a, prefix, n_seg, n_stripes, item);
-      w.col0 += my_col;
+        w.col0 += my_col;
         if (!w.ok) continue;
         if constexpr (PAIR) mbar_wait_cluster(accfree_bar, (use & 1) ^ 1, dead);
         else mbar_wait(accfree_bar, (use & 1) ^ 1, dead);
@@ -371,7 +378,8 @@ delta_gemm_tcsp_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
           if (++st == STAGES) { st = 0; phase ^= 1; }
           continue;
         }
-        mbar_wait(&full_bar[st], phase, dead);
+        if (dw == 0) mbar_wait(&full_bar[st], phase, dead);   // one warp of the team polls
+        named_bar_sync(5 + team, 256);
         const uint32_t sb = smem_base + st * Cfg::STAGE_BYTES;
         {
           const uint32_t wa = lds32(sb + ma_off), wb = lds32(sb + ma_off + 16);
@@ -403,6 +411,29 @@ delta_gemm_tcsp_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
         if (++st == STAGES) { st = 0; phase ^= 1; }
       }
     }
+  } else if (warp == 2 + Cfg::DECODE_WARPS + Cfg::EPI_WARPS) {
+    // ------------------------------ TMA producer: packed weights, metadata, scales ------------------------------
+    // A thread of its own: the TMA unit takes the small boxes while the activation box is in flight.
+    if (lane == 0) {
+      const uint64_t pol_w = policy_evict_first();
+      int st = 0;
+      uint32_t phase = 0;
+      for (int item = item0; item < n_items; item += item_step) {
+        WorkItem w = decode_item<Cfg>(a, prefix, n_seg, n_stripes, item);
+        w.col0 += my_col;
+        if (!w.ok) continue;
+        for (int kc = 0; kc < k_chunks; ++kc) {
+          mbar_wait(&empty_bar[st], phase ^ 1, dead);
+          uint8_t* sbase = smem + st * Cfg::STAGE_BYTES;
+          const int wrow = w.delta * slabs + kc * 2;
+          tma_load_2d_hint(sbase + Cfg::Q_OFF, &tm_q, (w.col0 / 64) * 128, wrow, &full_bar[st], pol_w);
+          tma_load_2d_hint(sbase + Cfg::M_OFF, &tm_m, (w.col0 / 64) * 64, wrow, &full_bar[st], pol_w);
+          if (a.grouped)
+            tma_load_2d_hint(sbase + Cfg::S_OFF, &tm_s, w.col0, w.delta * groups + kc / 2, &full_bar[st], pol_w);
+          if (++st == STAGES) { st = 0; phase ^= 1; }
+        }
+      }
+    }
   } else {
     // ------------------------------ epilogue warps ------------------------------
     const int ew = warp - 2 - Cfg::DECODE_WARPS;
@@ -424,8 +455,21 @@ delta_gemm_tcsp_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
       const int n = w.col0 + quad * 32 + lane;
       float sf = 1.f;
       if (!a.grouped && n < a.N) sf = __half2float(a.scales[(size_t)w.delta * a.N + n]);
+      // One warp polls the barrier (a shared-memory access per poll), the others park on the
+      // hardware barrier; the wait spans the whole K loop of the item, so the poller backs off.
+      if (ew == 0) {
+        uint32_t polls = 0;
+        while (!mbar_try_wait(accready_bar, use & 1)) {
+          __nanosleep(128);
+          if ((polls & 15u) == 0 && *dead) break;
+          if (++polls > kMaxPolls) {
+            *dead = 1;
+            atomicExch(&g_device_status, TRB_ERR_TIMEOUT);
+            break;
+          }
+        }
+      }
       named_bar_sync(4, Cfg::EPI_WARPS * 32);
-      mbar_wait(accready_bar, use & 1, dead);
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
       const int nbatch = (w.valid + 31) >> 5;
