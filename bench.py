@@ -316,11 +316,14 @@ def run_gpu_arm(args):
         uniq, starts, counts = _segments(idx_sorted)
         touched = int(uniq.numel())
     else:
-        mine = (idx_dev >= 0) & (idx_dev % world == rank)
-        loc = torch.div(idx_dev[mine], world, rounding_mode="floor")
+        # what this rank's grouped kernel sees in a step: the tokens of EVERY rank whose delta it owns
+        # (all ranks draw their ids from seed = rank, so they can be restated here without a collective)
+        all_idx = torch.from_numpy(np.concatenate([make_indices(r, TOKENS, total_deltas) for r in range(world)])).to(dev)
+        mine = (all_idx >= 0) & (all_idx % world == rank)
+        loc = torch.div(all_idx[mine], world, rounding_mode="floor")
         o2 = torch.argsort(loc, stable=True)
         idx_sorted = loc[o2].int().contiguous()
-        x_sorted = x_dev[mine][o2].contiguous()
+        x_sorted = x_dev.repeat(world, 1)[mine][o2].contiguous()
         uniq, starts, counts = _segments(idx_sorted)
         touched = int(uniq.numel())
     y_k = torch.empty(x_sorted.shape[0], N_OUT, dtype=torch.float16, device=dev)
@@ -354,7 +357,7 @@ def run_gpu_arm(args):
             "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "deltas_per_gpu": D_PER_GPU, "tokens_per_gpu": TOKENS, "k": K, "n": N_OUT,
                        "groupsize": GROUP, "index_law": "uniform over all deltas, 10% -1, unsorted",
-                       "distinct_deltas_touched_rank0": touched, "launch": launch_mode,
+                       "distinct_local_deltas_touched_rank0": touched, "launch": launch_mode,
                        "l2": f"inputs larger than L2: every step streams {touched * BYTES_PER_DELTA / 1e6:.0f} MB of packed "
                              "deltas (126 MB L2, evict-first loads); the kernel-alone roofline leg and the e2e leg "
                              "additionally flush L2 before every step (256 MiB memset + 256 MiB read, untimed)",
