@@ -259,6 +259,43 @@ def run_gpu_arm(args):
         step_e2e()
     barrier()
 
+    class E2ESlot:
+        """One in-flight end-to-end step: pinned host buffers, device staging, a stream and a CUDA
+        graph of [copy x and ids in, the public op, copy y out]."""
+
+        def __init__(self):
+            self.x_host, self.idx_host = x_host.clone().pin_memory(), idx_host.clone().pin_memory()
+            self.y_host = torch.empty(TOKENS, N_OUT, dtype=torch.float16).pin_memory()
+            self.x_dev, self.idx_dev = torch.empty_like(x_dev), torch.empty_like(idx_dev)
+            self.stream = torch.cuda.Stream()
+            self.graph = None
+
+        def body(self):
+            self.x_dev.copy_(self.x_host, non_blocking=True)
+            self.idx_dev.copy_(self.idx_host, non_blocking=True)
+            if world == 1:
+                y = ops.sbmm_4bit_2_4_native(qs, self.x_dev, metas, ss, self.idx_dev)
+            else:
+                y = exchange(self.x_dev, self.idx_dev)
+            self.y_host.copy_(y, non_blocking=True)
+            return y
+
+        def capture(self):
+            with torch.cuda.stream(self.stream):
+                self.body()
+            self.stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=self.stream):
+                self.keep = self.body()
+            self.graph = g
+
+        def launch(self):
+            with torch.cuda.stream(self.stream):
+                if self.graph is not None:
+                    self.graph.replay()
+                else:
+                    self.body()
+
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -298,7 +335,7 @@ def run_gpu_arm(args):
     ev1.synchronize()
     barrier()
     times = [ev0.elapsed_time(ev1) / args.steps]
-    # end-to-end: host buffers in, host buffer out, wall clock per step around a stream sync
+    # end-to-end latency of one step: host buffers in, host buffer out, wall clock around a stream sync
     e2e_times = []
     for _ in range(args.steps):
         flush()
@@ -306,6 +343,36 @@ def run_gpu_arm(args):
         t0 = time.perf_counter()
         step_e2e()
         e2e_times.append((time.perf_counter() - t0) * 1e3)
+    barrier()
+    # end-to-end throughput: K steps, every one copying its inputs in from pinned host memory and its
+    # result back; at N = 1 three steps are in flight on three streams so the copies of one overlap the
+    # kernels of the other (the host waits for a slot's previous result before it reuses the slot).
+    # With the cross-GPU exchange one step is in flight: its buffers and barriers are single.
+    # No flush: every step streams the touched deltas, far more than the L2.
+    slots = [E2ESlot() for _ in range(int(os.environ.get("TRB_E2E_SLOTS", "3")) if world == 1 else 1)]
+    e2e_mode = "eager"
+    if not args.eager:
+        try:
+            for sl in slots:
+                sl.capture()
+            e2e_mode = "cuda-graph replay"
+        except Exception as e:
+            if rank == 0:
+                print(f"bench.py: e2e graph capture failed ({e}); eager e2e steps", file=sys.stderr)
+            for sl in slots:
+                sl.graph = None
+    barrier()
+    for i in range(2 * len(slots)):
+        slots[i % len(slots)].launch()
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        sl = slots[i % len(slots)]
+        sl.stream.synchronize()      # the slot's previous result is in host memory
+        sl.launch()
+    for sl in slots:
+        sl.stream.synchronize()
+    t_e2e_pipe = (time.perf_counter() - t0) * 1e3 / args.steps
     barrier()
 
     # dominant kernel alone (grouped kernel through the segment-list entry point), rank-local
@@ -341,9 +408,9 @@ def run_gpu_arm(args):
     t_e2e = statistics.mean(e2e_times)
     t_kern = statistics.mean(k_times)
     if world > 1:
-        t = torch.tensor([t_step, t_e2e], device=dev, dtype=torch.float64)
+        t = torch.tensor([t_step, t_e2e, t_e2e_pipe], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        t_step, t_e2e = t.tolist()
+        t_step, t_e2e, t_e2e_pipe = t.tolist()
     status = _lib.device_status(local_rank)
 
     if rank == 0:
@@ -362,10 +429,14 @@ def run_gpu_arm(args):
                              "deltas (126 MB L2, evict-first loads); the kernel-alone roofline leg and the e2e leg "
                              "additionally flush L2 before every step (256 MiB memset + 256 MiB read, untimed)",
                        "parallelism": describe_parallelism(world, exchange_kind if world > 1 else None)},
-            "e2e": {"value": tokens_total / (t_e2e * 1e-3), "unit": UNIT, "ms_per_step": t_e2e,
+            "e2e": {"value": tokens_total / (t_e2e_pipe * 1e-3), "unit": UNIT, "ms_per_step": t_e2e_pipe,
                     "h2d_bytes_per_step": int(x_host.numel() * 2 + idx_host.numel() * 4),
                     "d2h_bytes_per_step": int(y_host.numel() * 2),
-                    "note": "sbmm_4bit_2_4_native from pinned host buffers; packed deltas stay resident (model state)"},
+                    "steps_in_flight": len(slots), "launch": e2e_mode,
+                    "latency_ms_one_step": t_e2e, "latency_tokens_per_s": tokens_total / (t_e2e * 1e-3),
+                    "note": "sbmm_4bit_2_4_native from pinned host buffers, every step copies x and ids in and y "
+                            "out; packed deltas stay resident (model state); latency_* is one step alone after "
+                            "an L2 flush"},
             "gpu_launches": launches_per_step * args.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_src, "kernel": "delta_gemm_kernel", "kernel_ms": t_kern,
