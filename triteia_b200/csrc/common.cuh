@@ -213,6 +213,13 @@ __device__ __forceinline__ void int4x4_to_half2x2(uint32_t q, uint32_t& lo, uint
   hi = *reinterpret_cast<uint32_t*>(&hr);
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may
+// start while its predecessor in the stream still runs; pdl_wait() returns once that predecessor has
+// completed and its writes are visible (no-op without the attribute).  pdl_launch_dependents() lets
+// the successor start early (no-op when the successor was launched without the attribute).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t s) {
   __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&s));
   return *reinterpret_cast<uint32_t*>(&r);

@@ -150,9 +150,6 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   const int warp = tid >> 5;
   const int lane = tid & 31;
 
-  int n_seg = a.n_seg_ptr ? *a.n_seg_ptr : a.n_seg;
-  n_seg = max(0, min(n_seg, kMaxSegments));
-
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -161,6 +158,11 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     *dead = 0;
     fence_mbar_init();
   }
+  pdl_wait();   // everything below reads what the kernels launched before this one wrote
+
+  int n_seg = a.n_seg_ptr ? *a.n_seg_ptr : a.n_seg;
+  n_seg = max(0, min(n_seg, kMaxSegments));
+
   // Tiles-per-segment prefix sums (list mode).  Warp 0 scans 32 segments per step.
   int total_tiles;
   if (a.mode == kSegList) {

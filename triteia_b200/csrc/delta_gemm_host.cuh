@@ -94,8 +94,17 @@ static int launch_cfg(const GemmCall& c, const GemmArgs& a) {
   else max_tiles = (long long)a.rows / Cfg::TT + (a.n_seg_ptr ? kMaxSegments : a.n_seg);
   const long long max_items = max_tiles * n_stripes;
   if (max_items < grid) grid = (int)(max_items > 0 ? max_items : 1);
-  delta_gemm_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_ALLOC, c.stream>>>(tx, tq, tm, ts, a);
-  return cudaGetLastError() == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3(grid);
+  lc.blockDim = dim3(Cfg::THREADS);
+  lc.dynamicSmemBytes = Cfg::SMEM_ALLOC;
+  lc.stream = c.stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // the kernel waits (pdl_wait) before it reads
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = at;
+  lc.numAttrs = 1;
+  return cudaLaunchKernelEx(&lc, delta_gemm_kernel<Cfg>, tx, tq, tm, ts, a) == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
 }
 
 // Prefill-sized tiles: the tcgen05 / TMEM kernels (sparse instruction by default; the dense-expanding
@@ -139,24 +148,21 @@ static int launch_tc_impl(Kernel kernel, const GemmCall& c, const GemmArgs& a) {
   else max_tiles = (long long)a.rows / Cfg::TT + (a.n_seg_ptr ? kMaxSegments : a.n_seg);
   const long long max_items = max_tiles * n_stripes;
   if (max_items < grid) grid = (int)(max_items > 0 ? max_items : 1);
-  if constexpr (ctas == 1) {
-    kernel<<<grid, Cfg::THREADS, Cfg::SMEM_ALLOC, c.stream>>>(tx, tq, tm, ts, a);
-    return cudaGetLastError() == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
-  } else {
-    cudaLaunchConfig_t lc = {};
-    lc.gridDim = dim3(grid * ctas);
-    lc.blockDim = dim3(Cfg::THREADS);
-    lc.dynamicSmemBytes = Cfg::SMEM_ALLOC;
-    lc.stream = c.stream;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeClusterDimension;
-    at[0].val.clusterDim.x = ctas;
-    at[0].val.clusterDim.y = 1;
-    at[0].val.clusterDim.z = 1;
-    lc.attrs = at;
-    lc.numAttrs = 1;
-    return cudaLaunchKernelEx(&lc, kernel, tx, tq, tm, ts, a) == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
-  }
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3(grid * ctas);
+  lc.blockDim = dim3(Cfg::THREADS);
+  lc.dynamicSmemBytes = Cfg::SMEM_ALLOC;
+  lc.stream = c.stream;
+  cudaLaunchAttribute at[2];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = ctas;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // the kernels wait (pdl_wait) before they read
+  at[1].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = at;
+  lc.numAttrs = 2;
+  return cudaLaunchKernelEx(&lc, kernel, tx, tq, tm, ts, a) == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
 }
 static int launch_tc(const GemmCall& c, const GemmArgs& a) {
   static const bool dense = [] {

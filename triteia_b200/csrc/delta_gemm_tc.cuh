@@ -141,6 +141,7 @@ delta_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
   const int warp = tid >> 5;
   const int lane = tid & 31;
 
+  pdl_wait();   // launched with programmatic serialization: the predecessor's writes are visible after this
   int n_seg = a.n_seg_ptr ? *a.n_seg_ptr : a.n_seg;
   n_seg = max(0, min(n_seg, kMaxSegments));
 

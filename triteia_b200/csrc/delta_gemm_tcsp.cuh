@@ -194,8 +194,7 @@ delta_gemm_tcsp_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
   const int warp = tid >> 5;
   const int lane = tid & 31;
 
-  int n_seg = a.n_seg_ptr ? *a.n_seg_ptr : a.n_seg;
-  n_seg = max(0, min(n_seg, kMaxSegments));
+  int n_seg = 0;
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -221,6 +220,9 @@ delta_gemm_tcsp_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
       asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
   }
+  pdl_wait();   // everything below reads what the kernels launched before this one wrote
+  n_seg = a.n_seg_ptr ? *a.n_seg_ptr : a.n_seg;
+  n_seg = max(0, min(n_seg, kMaxSegments));
   int total_tiles;
   if (a.mode == kSegList) {
     if (warp == 0) {

@@ -90,6 +90,7 @@ route_kernel(const RouteSrc src, int T, int D, int W, int TT, int* __restrict__ 
              int* __restrict__ tile_delta, int* __restrict__ tile_start, int* __restrict__ tile_count,
              int* __restrict__ counters, int* __restrict__ slot_of, int slot_stride, int* __restrict__ bin_count) {
   extern __shared__ int sm[];
+  pdl_launch_dependents();
   const int bins = D + 1;             // bin 0 = id -1 (and out-of-range ids)
   int* hist = sm;                     // [bins][W]
   int* bin_start = hist + bins * W;   // [bins + 1]
@@ -195,6 +196,8 @@ __global__ void gather_rows_kernel(const uint4* __restrict__ x, const int* __res
                                    const int* __restrict__ counters, uint4* __restrict__ x_sorted,
                                    uint4* __restrict__ y, int T, int k_vec, int n_vec, int zero_base_rows) {
   const int p = blockIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();                          // perm and counters come from the router launched just before
   if (p >= T) return;
   const int src = perm[p];
   if (src < 0 || src >= T) return;
@@ -260,8 +263,18 @@ int route_launch(const int* indices, int T, int D, int TT, int id_offset, int* p
 int gather_launch(const void* x, const int* perm, const int* counters, void* x_sorted, void* y, int T, int K,
                   int N, int zero_base_rows, cudaStream_t stream) {
   if (T == 0) return TRB_OK;
-  gather_rows_kernel<<<T, 128, 0, stream>>>((const uint4*)x, perm, counters, (uint4*)x_sorted, (uint4*)y, T,
-                                            K / 8, N / 8, zero_base_rows);
-  return cudaGetLastError() == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3(T);
+  lc.blockDim = dim3(128);
+  lc.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = at;
+  lc.numAttrs = 1;
+  return cudaLaunchKernelEx(&lc, gather_rows_kernel, (const uint4*)x, perm, counters, (uint4*)x_sorted, (uint4*)y, T,
+                            K / 8, N / 8, zero_base_rows) == cudaSuccess
+             ? TRB_OK
+             : TRB_ERR_CUDA;
 }
 }  // namespace trb
