@@ -47,9 +47,8 @@ struct GemmArgs {
   int chunk_rows;
 };
 
-template <int NB_, int SW_, int KQ_, int KS_, int STAGES_, int OCC_ = 1>
+template <int NB_, int SW_, int KQ_, int KS_, int STAGES_>
 struct GemmCfg {
-  static constexpr int OCC = OCC_;        // CTAs resident per SM (each with its own pipeline)
   static constexpr int NB = NB_;          // token blocks of 8 per tile
   static constexpr int SW = SW_;          // 64-column blocks per stripe
   static constexpr int KQ = KQ_;          // warps sharing one column block (split over slabs)
@@ -133,7 +132,7 @@ __device__ __forceinline__ WorkItem decode_item(const GemmArgs& a, const int* pr
 }
 
 template <class Cfg>
-__global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
+__global__ void __launch_bounds__(Cfg::THREADS, 1)
 delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_q,
                   const __grid_constant__ CUtensorMap tm_m, const __grid_constant__ CUtensorMap tm_s,
                   const GemmArgs a) {

@@ -85,7 +85,6 @@ static int launch_cfg(const GemmCall& c, const GemmArgs& a) {
   }
   int grid = sm_count(c.dev);
   if (c.sms > 0 && c.sms < grid) grid = c.sms;
-  grid *= Cfg::OCC;
   // Upper bound on work items known on the host: never launch more CTAs than that.
   const int n_stripes = (a.N + Cfg::SW * 64 - 1) / (Cfg::SW * 64);
   long long max_tiles;
@@ -212,12 +211,7 @@ int gemm_dispatch(const GemmCall& c, const GemmArgs& a, int tile_tokens) {
   cudaError_t e = cudaSetDevice(c.dev);
   if (e != cudaSuccess) return TRB_ERR_CUDA;
   switch (tile_tokens) {
-    case 8: {
-      static const int occ2 = [] { const char* e = getenv("TRB_EXP_T8"); return e ? atoi(e) : 0; }();
-      if (occ2 == 2) return launch_cfg<GemmCfg<1, 2, 4, 16, 3, 2>>(c, a);
-      if (occ2 == 3) return launch_cfg<GemmCfg<1, 2, 4, 8, 6, 2>>(c, a);
-      return launch_cfg<CfgT8>(c, a);
-    }
+    case 8: return launch_cfg<CfgT8>(c, a);
     case 16: return launch_cfg<CfgT16>(c, a);
     case 32: return launch_cfg<CfgT32>(c, a);
     case 64: return launch_cfg<CfgT64>(c, a);
