@@ -69,7 +69,10 @@ struct GemmCfg {
   static constexpr int X_BYTES = NXBOX * X_BOX_BYTES;
   static constexpr int Q_BYTES = KS * SW * 512;
   static constexpr int M_BYTES = KS * SW * 256;
-  static constexpr int S_BYTES = (KS / 4) * SW * 128;
+  static constexpr int SB = SW >= 4 ? 4 : SW;       // column blocks per scale TMA box (a box dimension is at most 256)
+  static constexpr int NSBOX = SW / SB;
+  static constexpr int S_BOX_BYTES = (KS / 4) * SB * 128;
+  static constexpr int S_BYTES = NSBOX * S_BOX_BYTES;
   static constexpr int X_OFF = 0;
   static constexpr int Q_OFF = (X_BYTES + 1023) / 1024 * 1024;
   static constexpr int M_OFF = Q_OFF + Q_BYTES;
@@ -229,9 +232,12 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             tma_load_2d_hint(sbase + Cfg::M_OFF + b * (KS * Cfg::QB * 256), &tm_m,
                              (w.col0 / 64 + b * Cfg::QB) * 64, wrow, &full_bar[st], pol_w);
           }
-          if (a.grouped)
-            tma_load_2d_hint(sbase + Cfg::S_OFF, &tm_s, w.col0, w.delta * groups + ks * (KS / 4), &full_bar[st],
-                             pol_w);
+          if (a.grouped) {
+#pragma unroll
+            for (int b = 0; b < Cfg::NSBOX; ++b)
+              tma_load_2d_hint(sbase + Cfg::S_OFF + b * Cfg::S_BOX_BYTES, &tm_s, w.col0 + b * Cfg::SB * 64,
+                               w.delta * groups + ks * (KS / 4), &full_bar[st], pol_w);
+          }
           if (++st == STAGES) { st = 0; phase ^= 1; }
         }
       }
@@ -254,7 +260,8 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   // Per-lane byte offsets inside a stage, fixed for the whole kernel.
   const uint32_t q_off = Cfg::Q_OFF + box * (KS * Cfg::QB * 512) + within * 512 + lane * 16 + kq * SPW * (Cfg::QB * 512);
   const uint32_t m_off = Cfg::M_OFF + box * (KS * Cfg::QB * 256) + within * 256 + lane * 4 + kq * SPW * (Cfg::QB * 256);
-  const uint32_t s_off = Cfg::S_OFF + ((kq * SPW) / 4) * (SW * 128) + cb * 128 + g8 * 16;
+  const uint32_t s_off = Cfg::S_OFF + (cb / Cfg::SB) * Cfg::S_BOX_BYTES + ((kq * SPW) / 4) * (Cfg::SB * 128) +
+                         (cb % Cfg::SB) * 128 + g8 * 16;
   // ldmatrix row address of slab i of this warp: 16-byte chunk 4*slab + lane/8 of the stage's K
   // range lives in activation box chunk/8 at swizzled chunk position (chunk%8) ^ (row%8).
   uint32_t x_off[SPW];

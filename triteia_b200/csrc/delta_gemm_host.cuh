@@ -71,7 +71,7 @@ static int launch_cfg(const GemmCall& c, const GemmArgs& a) {
     return TRB_ERR_CUDA;
   if (a.grouped) {
     if (!make_map_2d(&ts, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, c.s, (uint64_t)c.num_deltas * groups, (uint64_t)a.N,
-                     Cfg::KS / 4, Cfg::SW * 64, CU_TENSOR_MAP_SWIZZLE_NONE))
+                     Cfg::KS / 4, Cfg::SB * 64, CU_TENSOR_MAP_SWIZZLE_NONE))
       return TRB_ERR_CUDA;
   } else {
     ts = tm;  // never dereferenced
@@ -181,10 +181,13 @@ static int launch_tc(const GemmCall& c, const GemmArgs& a) {
 static_assert(TcCfg::SMEM_ALLOC <= 232448 && TcSpCfg::SMEM_ALLOC <= 232448 && TcSpPairCfg::SMEM_ALLOC <= 232448, "shared memory budget of one sm_100 CTA");
 
 using CfgT8 = GemmCfg<1, 2, 4, 16, 6>;
+// Wide outputs: 256-column items, two warps per column block.  Half as many work items, so half the
+// per-item cost (descriptor search, partial-sum exchange, epilogue) per byte streamed.
+using CfgT8W = GemmCfg<1, 4, 2, 8, 7>;
 using CfgT16 = GemmCfg<2, 2, 4, 16, 4>;
 using CfgT32 = GemmCfg<4, 2, 4, 8, 5>;
 using CfgT64 = GemmCfg<8, 4, 2, 4, 5>;
-static_assert(CfgT8::SMEM_ALLOC <= 232448 && CfgT16::SMEM_ALLOC <= 232448 && CfgT32::SMEM_ALLOC <= 232448 &&
+static_assert(CfgT8W::SMEM_ALLOC <= 232448 && CfgT8::SMEM_ALLOC <= 232448 && CfgT16::SMEM_ALLOC <= 232448 && CfgT32::SMEM_ALLOC <= 232448 &&
                   CfgT64::SMEM_ALLOC <= 232448,
               "shared memory budget of one sm_100 CTA");
 
@@ -211,7 +214,7 @@ int gemm_dispatch(const GemmCall& c, const GemmArgs& a, int tile_tokens) {
   cudaError_t e = cudaSetDevice(c.dev);
   if (e != cudaSuccess) return TRB_ERR_CUDA;
   switch (tile_tokens) {
-    case 8: return launch_cfg<CfgT8>(c, a);
+    case 8: return (a.N % 256 == 0 && a.N >= 2048) ? launch_cfg<CfgT8W>(c, a) : launch_cfg<CfgT8>(c, a);
     case 16: return launch_cfg<CfgT16>(c, a);
     case 32: return launch_cfg<CfgT32>(c, a);
     case 64: return launch_cfg<CfgT64>(c, a);
