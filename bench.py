@@ -558,6 +558,117 @@ def run_ldmm(args):
     print(json.dumps(line))
 
 
+def run_stack(args):
+    """BASELINE config 4 (the linear stack): L layers of the seven Llama-2-7B linears, 128 deltas sharded by
+    id over the ranks, 512 tokens in all (512 / N per rank), delta id ~ Zipf(1.5); one dispatch and one
+    combine per pass.  Strong scaling: the total work is fixed as N grows."""
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=dev) if world > 1 else dist.init_process_group(
+        "nccl", init_method="tcp://127.0.0.1:%d" % (29700 + os.getpid() % 200), rank=0, world_size=1, device_id=dev)
+    from triteia_b200 import _lib, stack
+
+    D, T_total, L, group = 128, 512, args.layers, 128
+    T = T_total // world
+    t0 = time.perf_counter()
+    shard = stack.random_stack_shard(D, rank, world, L, groupsize=group, device=dev, seed=3)
+    local = stack.DeltaStackShard(shard)
+    torch.cuda.synchronize()
+    t_build = time.perf_counter() - t0
+    rng = np.random.default_rng(7)
+    p = np.arange(1, D + 1, dtype=np.float64) ** -1.5
+    ids_all = rng.choice(D, T_total, p=p / p.sum()).astype(np.int32)          # the same batch for every N
+    g = torch.Generator().manual_seed(7)
+    x4096_all = torch.randn(T_total, 4096, generator=g).half()
+    x11008_all = torch.randn(T_total, 11008, generator=g).half()
+    sl = slice(rank * T, (rank + 1) * T)
+    host = {4096: x4096_all[sl].contiguous().pin_memory(), 11008: x11008_all[sl].contiguous().pin_memory()}
+    idx_host = torch.from_numpy(ids_all[sl].copy()).pin_memory()
+    xs = {k: v.to(dev) for k, v in host.items()}
+    idx = idx_host.to(dev)
+    y_host = torch.empty(T, 4096, dtype=torch.float16).pin_memory()
+    cs_host = torch.empty(T, dtype=torch.float32).pin_memory()
+
+    def step():
+        return stack.stack_sharded(xs, idx, local, 4096)
+
+    def step_e2e():
+        xd = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
+        idd = idx_host.to(dev, non_blocking=True)
+        y, cs = stack.stack_sharded(xd, idd, local, 4096)
+        y_host.copy_(y, non_blocking=True)
+        cs_host.copy_(cs, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    step_e2e()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    ev1.synchronize()
+    barrier()
+    t_step = ev0.elapsed_time(ev1) / args.steps
+    tw = time.perf_counter()
+    for _ in range(args.steps):
+        step_e2e()
+    t_e2e = (time.perf_counter() - tw) * 1e3 / args.steps
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    mine = set(range(rank, D, world))
+    touched_local = len({int(i) for i in ids_all if int(i) in mine})
+    per_layer = sum(k * n // 4 + k * n // 8 + (k // group) * n * 2 for _, k, n in stack.LLAMA_7B_LINEARS)
+    t = torch.tensor([t_step, t_e2e, float(touched_local)], device=dev, dtype=torch.float64)
+    if world > 1:
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        t_step, t_e2e, touched_max = tmax.tolist()
+    else:
+        touched_max = touched_local
+    status = _lib.device_status(local_rank)
+    if rank == 0:
+        peak, peak_src = peaks()
+        alg = touched_max * per_layer * L          # the busiest rank's delta bytes: what bounds the pass
+        ach = alg / (t_step * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "stack_tokens_per_s", "value": T_total / (t_step * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": t_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"stack-llama7b-linears-{L}layers-128deltas-512tok-zipf1.5-g128", "layers": L,
+                       "tokens_total": T_total, "linears_per_pass": 7 * L, "ms_per_layer": t_step / L,
+                       "distinct_deltas_touched": len(set(int(i) for i in ids_all)),
+                       "touched_on_busiest_rank": int(touched_max), "build_s": t_build,
+                       "l2": "inputs larger than L2 (every linear streams its touched deltas: 6-17 MB each, all distinct)",
+                       "parallelism": "single GPU" if world == 1 else
+                       f"deltas sharded by id over {world} GPUs; one NCCL all-to-all dispatch of [x4096|x11008] rows + ids "
+                       "and one combine (last output + checksums) per pass; one host read of the counts per pass"},
+            "e2e": {"value": T_total / (t_e2e * 1e-3), "unit": UNIT, "ms_per_step": t_e2e,
+                    "h2d_bytes_per_step": int(T * (4096 + 11008) * 2 + T * 4), "d2h_bytes_per_step": int(T * 4096 * 2 + T * 4)},
+            "gpu_launches": 14 * L * args.steps,
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                         "peak_source": peak_src, "kernel": "whole pass on the busiest rank (grouped kernel + row checksum per linear)",
+                         "algorithmic_bytes": alg, "traffic": None},
+            "clocks": clocks, "device_status": status}))
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -566,14 +677,18 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of CUDA-graph replays")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "ldmm"],
-                    help="decode = the headline sbmm configuration (default); prefill / ldmm: 1-GPU extra legs")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "ldmm", "stack"],
+                    help="decode = the headline sbmm configuration (default); prefill / ldmm: 1-GPU extra legs; "
+                         "stack = the sharded linear stack (any number of GPUs, strong scaling)")
+    ap.add_argument("--layers", type=int, default=8, help="stack: number of layers (8 fits one GPU: 78 GB of deltas)")
     ap.add_argument("--shape", default="up", choices=["up", "down"], help="prefill: 5120x13824 (up) or 13824x5120")
     args = ap.parse_args()
     if args.workload == "prefill":
         return run_prefill(args)
     if args.workload == "ldmm":
         return run_ldmm(args)
+    if args.workload == "stack":
+        return run_stack(args)
     if args.impl == "reference":
         run_reference_arm(args)
     else:

@@ -164,6 +164,13 @@ int trb_shard_combine(const void* back_buf, const void* slot_of, void* y, int nu
 int trb_unpack_2_4(const void* B, const void* meta, const void* s, void* w_out, int prob_m,
                    int prob_k, int groupsize, int dev, void* stream);
 
+/* sums[r] = (accumulate ? sums[r] : 0) + sum over n of y[r, n]: fp32 per-row checksum of an fp16
+ * matrix [rows, prob_m] (prob_m % 8 == 0, y 16-byte aligned), fixed summation order.  Used by the
+ * sharded linear-stack scenario (BASELINE config "full Llama-2-7B-shaped linear stack") to return
+ * one number per token and linear instead of every output row.  No counterpart in the reference. */
+int trb_row_checksum(const void* y, void* sums, int rows, int prob_m, int accumulate, int dev,
+                     void* stream);
+
 /* BGMV: Y[b, :] += scale * W[indices[b], layer_idx] @ X[b, :], W [M, L, h_out, h_in]
  * contiguous, indices int64 [B].  Replaces bgmv_kernel<feat_in, feat_out, T>
  * (csrc/ops/bgmv_config.h:3-7, csrc/ops/bgmv_impl.cuh:186-207); any h_in, h_out that are

@@ -73,3 +73,72 @@ def test_sharded_exchange_cuda(cuda, tmp_path, world, backend):
         res = torch.load(os.path.join(str(tmp_path), f"r{r}.pt"))
         assert res["status"] == 0
         assert res["err"] <= 1e-2, res
+
+
+def _stack_worker(rank, world, port, out_dir):
+    """Sharded stack of independent delta linears (one dispatch and one combine for all layers) on
+    the CUDA segment-list entry point + row checksum kernel, against the CPU oracle over the whole
+    delta set."""
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from triteia_b200 import stack, _lib
+        from oracle import ops as oracle
+
+        D, T, L = 8, 48, 2
+        linears = (("a", 256, 256), ("b", 256, 384), ("c", 384, 256))
+        shard = stack.random_stack_shard(D, rank, world, L, linears=linears, groupsize=128, device=dev, seed=11)
+        # the whole set, drawn on the same device type (a CUDA generator's stream differs from a CPU one),
+        # then moved to the host for the oracle; the shard is the matching rows of it
+        full = stack.random_stack_shard(D, 0, 1, L, linears=linears, groupsize=128, device=dev, seed=11)
+        mine = list(range(rank, D, world))
+        same = all(torch.equal(shard[l][j].qweights, full[l][j].qweights[mine]) and
+                   torch.equal(shard[l][j].scales, full[l][j].scales[mine]) for l in range(L) for j in range(3))
+        for layer in full:
+            for lin in layer:
+                lin.qweights, lin.metas, lin.scales = lin.qweights.cpu(), lin.metas.cpu(), lin.scales.cpu()
+        local = stack.DeltaStackShard(shard)
+        worst_y, worst_cs = 0.0, 0.0
+        for call in range(2):
+            gen = torch.Generator().manual_seed(31 * rank + call)
+            xs = {256: torch.randn(T, 256, generator=gen).half().to(dev), 384: torch.randn(T, 384, generator=gen).half().to(dev)}
+            idx = torch.randint(-1, D, (T,), generator=gen, dtype=torch.int32).to(dev)
+            if call == 1:
+                idx[: T // 2] = 3            # a hot delta
+            y, cs = stack.stack_sharded(xs, idx, local, linears[-1][2])
+            torch.cuda.synchronize()
+            idx_np = idx.cpu().numpy()
+            cs_ref = np.zeros(T, dtype=np.float64)
+            l1 = np.zeros(T, dtype=np.float64)
+            ref = None
+            for l in range(L):
+                for j, (_, k, n) in enumerate(linears):
+                    lin = full[l][j]
+                    ref = oracle.sbmm(lin.qweights.numpy(), xs[k].cpu().numpy(), lin.metas.numpy(), lin.scales.numpy(), idx_np)
+                    cs_ref += ref.astype(np.float64).sum(axis=1)
+                    l1 += np.abs(ref).astype(np.float64).sum(axis=1)
+            worst_y = max(worst_y, float(oracle.row_rel_err(y.float().cpu().numpy(), ref).max()))
+            # every output element is within 1e-2 of its row's scale, so the sum of sums is within 1e-2 of the L1 mass
+            worst_cs = max(worst_cs, float((np.abs(cs.cpu().numpy() - cs_ref) / np.maximum(l1, 1e-6)).max()))
+            assert torch.all(y[idx == -1] == 0) and torch.all(cs[idx == -1] == 0)
+        torch.save({"err_y": worst_y, "err_cs": worst_cs, "same": bool(same), "status": _lib.device_status(rank)},
+                   os.path.join(out_dir, f"s{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_sharded_stack_cuda(cuda, tmp_path, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    mp.start_processes(_stack_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True, start_method="spawn")
+    for r in range(world):
+        res = torch.load(os.path.join(str(tmp_path), f"s{r}.pt"))
+        assert res["status"] == 0 and res["same"]
+        assert res["err_y"] <= 1e-2 and res["err_cs"] <= 1e-2, res

@@ -84,3 +84,57 @@ def test_ownership_rule():
     for r in range(4):
         for local, d in enumerate(sharded.shard_ids(10, r, 4)):
             assert int(sharded.owner_of(torch.tensor(d), 4)) == r and int(sharded.local_id_of(torch.tensor(d), 4)) == local
+
+
+def _stack_worker(rank, world, port, case, out_dir):
+    """The sharded linear stack's exchange (one dispatch, one combine for all layers) with a torch
+    statement of the local stack, against the unsharded stack."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from triteia_b200 import sharded, stack
+        from triteia_b200.ops.matmul.sbmm import sbmm_16bit_forloop
+
+        D, T, L = 6, 24, 2
+        linears = (("a", 32, 32), ("b", 32, 48), ("c", 48, 32))
+        g = torch.Generator().manual_seed(1)
+        weights = [[torch.randn(D, k, n, generator=g) for (_, k, n) in linears] for _ in range(L)]
+        mine = sharded.shard_ids(D, rank, world)
+        gr = torch.Generator().manual_seed(200 + rank)
+        xs = {32: torch.randn(T, 32, generator=gr), 48: torch.randn(T, 48, generator=gr)}
+        idx = torch.randint(-1, D, (T,), generator=gr, dtype=torch.int32)
+        if case == "one_owner":
+            idx[:] = 3
+        elif case == "all_base":
+            idx[:] = -1
+
+        def run_stack(ws, x_by_width, ids):
+            cs = torch.zeros(ids.numel())
+            y = torch.zeros(ids.numel(), linears[-1][2])
+            for layer in ws:
+                for (_, k, n), w in zip(linears, layer):
+                    y = sbmm_16bit_forloop(w, x_by_width[k], ids)
+                    cs = cs + y.sum(dim=1)
+            return y, cs
+
+        def local_stack(x_by_width, local_ids):
+            return run_stack([[w[mine] for w in layer] for layer in weights], x_by_width, local_ids)
+
+        y, cs = stack.stack_sharded(xs, idx, local_stack, linears[-1][2])
+        y_ref, cs_ref = run_stack(weights, xs, idx)
+        ok = torch.allclose(y, y_ref, rtol=1e-5, atol=1e-5) and torch.allclose(cs, cs_ref, rtol=1e-4, atol=1e-4)
+        ok = ok and bool(torch.all(y[idx == -1] == 0)) and bool(torch.all(cs[idx == -1] == 0))
+        torch.save({"ok": bool(ok), "max_err": float((y - y_ref).abs().max())}, os.path.join(out_dir, f"s{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("case", ["mixed", "one_owner", "all_base"])
+def test_sharded_stack_world2(tmp_path, case):
+    world = 2
+    mp.start_processes(_stack_worker, args=(world, _free_port(), case, str(tmp_path)), nprocs=world, join=True,
+                       start_method="spawn")
+    for r in range(world):
+        res = torch.load(os.path.join(str(tmp_path), f"s{r}.pt"))
+        assert res["ok"], res

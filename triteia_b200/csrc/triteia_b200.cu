@@ -11,5 +11,6 @@
 #include "delta_gemm_host.cuh"
 #include "shard.cuh"
 #include "unpack.cuh"
+#include "stack.cuh"
 #include "lora.cuh"
 #include "no_alloc.cuh"
