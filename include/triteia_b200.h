@@ -171,6 +171,20 @@ int trb_unpack_2_4(const void* B, const void* meta, const void* s, void* w_out, 
 int trb_row_checksum(const void* y, void* sums, int rows, int prob_m, int accumulate, int dev,
                      void* stream);
 
+/* One pass of a stack of n_linears independent delta linears over grouped rows, issued from C (the
+ * host cost of a launch made from Python exceeds the run time of most of these kernels).  Rows
+ * [class_row0[c], +class_rows[c]) form size class c with its own segment list (class_ids /
+ * class_starts / class_counts, class_segs[c] entries, starts relative to the class's first row); per
+ * linear i every class gets one trb_sbmm_2_4 launch on x_of[i] [rows, k[i]] -> y_of[i] [rows, n[i]],
+ * then y_of[i] is folded into checksum [rows] fp32 (trb_row_checksum, accumulate).  All arrays are
+ * host arrays of device pointers / ints.  No counterpart in the reference. */
+int trb_stack_pass(int n_linears, const void* const* q, const void* const* meta,
+                   const void* const* s, const int* k, const int* n, const void* const* x_of,
+                   void* const* y_of, int n_classes, const int* class_row0, const int* class_rows,
+                   const void* const* class_ids, const void* const* class_starts,
+                   const void* const* class_counts, const int* class_segs, void* checksum, int rows,
+                   int groupsize, int dev, void* stream);
+
 /* BGMV: Y[b, :] += scale * W[indices[b], layer_idx] @ X[b, :], W [M, L, h_out, h_in]
  * contiguous, indices int64 [B].  Replaces bgmv_kernel<feat_in, feat_out, T>
  * (csrc/ops/bgmv_config.h:3-7, csrc/ops/bgmv_impl.cuh:186-207); any h_in, h_out that are

@@ -10,9 +10,10 @@ token's delta id selects the same delta in every linear, id -1 means "no delta" 
 Protocol of one pass (one exchange each way, whatever the number of layers):
   1. every rank sends each of its tokens that has a delta ONCE, as the row [x_4096 | x_11008],
      with its local delta id, to owner(id) = id % world (NCCL all-to-all; counts first);
-  2. the owner groups the received rows by delta once (sort + segment list), then runs every
-     linear of every layer on the grouped rows with the segment-list kernel entry point
-     (no router and no gather per linear) and folds each output into a per-token fp32 checksum;
+  2. the owner groups the received rows once, by segment size class and delta (sort + one segment
+     list per class; a handful of host reads per pass), then runs every linear of every layer on
+     the grouped rows with the segment-list kernel entry point, one launch per size class (no
+     router and no gather per linear), and folds each output into a per-token fp32 checksum;
   3. the last linear's output rows and the checksums travel back and are scattered into token order.
 The linears are independent (each reads the seeded activation of its input width), so the result
 does not depend on the number of ranks.
@@ -50,33 +51,71 @@ class DeltaStackShard:
         self.layers = layers
         self.n_last = layers[-1][-1].n
 
-    def __call__(self, x_by_width, local_ids):
-        from . import _lib
-        from .capi import sbmm_2_4
+    # Segments are handled in size classes, one launch per class and linear, so that a hot delta's
+    # many tokens and a cold delta's single token each get a kernel tiled for them (token tiles of 8
+    # or 16-32 rows on mma.sp, 256 rows on tcgen05) instead of one tile size chosen for the average.
+    CLASS_BOUNDS = (8, 32)
+
+    def _plan(self, local_ids):
+        """Rows ordered by (size class, delta id) and, per class, its row range and segment list."""
         from .ops.matmul.sbmm import _segments
+
+        dev = local_ids.device
+        ids64 = local_ids.to(torch.int64)
+        counts = torch.bincount(ids64)
+        bounds = torch.tensor(self.CLASS_BOUNDS, device=dev)
+        cls_of = torch.bucketize(counts, bounds)                      # 0: <= 8 rows ... 3: > 32 rows
+        big = int(counts.numel()) + 1
+        order = torch.argsort(cls_of[ids64] * big + ids64, stable=True)
+        ids_sorted = local_ids[order].to(torch.int32).contiguous()
+        cls_sorted = cls_of[ids64][order]
+        cls_rows = torch.bincount(cls_sorted, minlength=len(self.CLASS_BOUNDS) + 1).tolist()   # host read (once per pass)
+        classes, at = [], 0
+        for n_rows in cls_rows:
+            if n_rows:
+                uniq, starts, cnts = _segments(ids_sorted[at:at + n_rows])   # sizes its outputs on the host
+                classes.append((at, n_rows, uniq, starts, cnts))
+            at += n_rows
+        return order, classes
+
+    def _static_arrays(self):
+        """Host arrays of the per-linear device pointers and shapes (built once)."""
+        import ctypes
+        from . import _lib
+
+        if getattr(self, "_static", None) is None:
+            lins = [lin for layer in self.layers for lin in layer]
+            vp, ci = ctypes.c_void_p * len(lins), ctypes.c_int * len(lins)
+            self._static = (lins, vp(*[_lib.ptr(l.qweights) for l in lins]), vp(*[_lib.ptr(l.metas) for l in lins]),
+                            vp(*[_lib.ptr(l.scales) for l in lins]), ci(*[l.k for l in lins]), ci(*[l.n for l in lins]))
+        return self._static
+
+    def __call__(self, x_by_width, local_ids):
+        import ctypes
+        from . import _lib
 
         rows = int(local_ids.numel())
         dev = local_ids.device
         if rows == 0:
             return (torch.empty(0, self.n_last, dtype=torch.float16, device=dev),
                     torch.empty(0, dtype=torch.float32, device=dev))
-        order = torch.argsort(local_ids, stable=True)
-        ids_sorted = local_ids[order].to(torch.int32).contiguous()
-        uniq, starts, counts = _segments(ids_sorted)          # the one host read of the pass
+        order, classes = self._plan(local_ids)
         xs = {k: x.index_select(0, order).contiguous() for k, x in x_by_width.items()}
-        ybuf = {}
+        lins, q_arr, m_arr, s_arr, k_arr, n_arr = self._static_arrays()
+        ybuf = {n: torch.empty(rows, n, dtype=torch.float16, device=dev) for n in {l.n for l in lins}}
         checksum = torch.zeros(rows, dtype=torch.float32, device=dev)
-        ws = torch.zeros(1, dtype=torch.int32, device=dev)     # accepted by the ABI, never touched
-        stream = _lib.stream_of(checksum)
-        y = None
-        for layer in self.layers:
-            for lin in layer:
-                y = ybuf.get(lin.n)
-                if y is None:
-                    y = ybuf[lin.n] = torch.empty(rows, lin.n, dtype=torch.float16, device=dev)
-                sbmm_2_4(xs[lin.k], lin.qweights, lin.metas, y, lin.scales, uniq, ws, starts, counts)
-                _lib.check(_lib.lib.trb_row_checksum(_lib.ptr(y), _lib.ptr(checksum), rows, lin.n, 1,
-                                                     _lib.dev_of(y), stream), "row_checksum")
+        vp_l, vp_c, ci_c = ctypes.c_void_p * len(lins), ctypes.c_void_p * len(classes), ctypes.c_int * len(classes)
+        x_arr = vp_l(*[_lib.ptr(xs[l.k]) for l in lins])
+        y_arr = vp_l(*[_lib.ptr(ybuf[l.n]) for l in lins])
+        groupsize = 128 if lins[0].scales.shape[1] > 1 else -1
+        err = _lib.lib.trb_stack_pass(
+            len(lins), q_arr, m_arr, s_arr, k_arr, n_arr, x_arr, y_arr, len(classes),
+            ci_c(*[c[0] for c in classes]), ci_c(*[c[1] for c in classes]),
+            vp_c(*[_lib.ptr(c[2]) for c in classes]), vp_c(*[_lib.ptr(c[3]) for c in classes]),
+            vp_c(*[_lib.ptr(c[4]) for c in classes]), ci_c(*[int(c[2].numel()) for c in classes]),
+            _lib.ptr(checksum), rows, groupsize, _lib.dev_of(checksum), _lib.stream_of(checksum))
+        _lib.check(err, "stack_pass")
+        y = ybuf[self.n_last]
         y_out = torch.empty_like(y)
         y_out[order] = y
         cs_out = torch.empty_like(checksum)
