@@ -13,7 +13,9 @@ triteia/python/ops/utils/generator.py:51).  Only torch-on-CPU reference code run
 the packer (nn/linear.py:79-141), the 2:4 compressor (ops/utils/sparsity.py:167-290),
 `mask_creator` (sparsity.py:99-118), the routing prologue (ops/matmul/sbmm.py:94-123),
 `sbmm_16bit_forloop` (sbmm.py:7-23), `lora_forloop` (ops/matmul/lora.py:4-20) and the
-dispatch rule of `baseline_ldmm` (ops/matmul/ldmm.py:22-46).
+dispatch rule of `baseline_ldmm` (ops/matmul/ldmm.py:22-46), the GPTQ dequantiser
+(utils/quant_utils.py:38-44) and the tensor-parallel chunking of the packer
+(ops/utils/generator.py:126-176).
 
 The fixtures travel with the repository; nothing at test time reads the reference.
 """
@@ -156,6 +158,30 @@ def main():
     np.random.seed(5)
     out["dist_zipf"] = ops.generate_model_distribution("zipf:1.5", 64, 8).numpy()
     gen.torch.tensor = orig_tensor
+
+    # ---- GPTQ-style checkpoint tensors -> dense weight (utils/quant_utils.py:38-44) ----
+    from triteia.python.utils.quant_utils import dequantize_weight
+    g = torch.Generator().manual_seed(40)
+    gq = torch.randint(-2 ** 31, 2 ** 31 - 1, (8, 32), generator=g, dtype=torch.int64).to(torch.int32)
+    gz = torch.full((1, 4), 0x77777777, dtype=torch.int32)
+    gs = (torch.rand(1, 32, generator=g) * 0.01 + 0.001).half()
+    out.update(gptq_qweight=gq.numpy(), gptq_qzeros=gz.numpy(), gptq_scales=gs.numpy(),
+               gptq_dense=dequantize_weight(gq, gz, gs).numpy())
+
+    # ---- tensor-parallel chunking of the packer (ops/utils/generator.py:126-176) ----
+    from triteia.python.ops.utils.generator import torch_weight_to_sparse_marlin
+    torch.manual_seed(41)
+    lev = torch.randint(1, 8, (256, 512)) * (torch.randint(0, 2, (256, 512)) * 2 - 1)
+    keep = mask_creator(torch.randn(512, 256), 2, 4).t()            # 2 of every 4 along the input features
+    tp_scale = (torch.rand(1, 512) * 0.01 + 0.001).half()
+    tp_w = (lev * keep).half() * tp_scale                             # [in, out]
+    out.update(tp_weight=tp_w.numpy(), tp_scale=tp_scale.numpy())
+    for how in ("column", "row"):
+        qs_, ss_, ms_ = torch_weight_to_sparse_marlin(tp_w.clone(), tp_scale.clone(), tp_size=2, chunk_by=how)
+        for i in range(2):
+            out[f"tp_{how}_{i}_q"] = qs_[i].numpy()
+            out[f"tp_{how}_{i}_s"] = ss_[i].numpy()
+            out[f"tp_{how}_{i}_meta"] = ms_[i].numpy()
 
     path = os.path.join(OUT, "reference_vectors.npz")
     np.savez_compressed(path, **out)

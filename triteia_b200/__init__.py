@@ -8,7 +8,7 @@ CPU or PyTorch fallback for the CUDA operators.
 import importlib
 
 __version__ = "0.1.0"
-_LAZY = ("ops", "capi", "nn", "triteia_cuda", "sharded", "_lib", "build")
+_LAZY = ("ops", "capi", "nn", "triteia_cuda", "sharded", "stack", "converters", "configs", "utils", "_lib", "build")
 
 
 def __getattr__(name):
