@@ -61,93 +61,34 @@ extern "C" int trb_row_checksum(const void* y, void* sums, int rows, int prob_m,
 // host cost per launch is a few microseconds (a Python call per launch costs more than most of
 // these kernels run).  Rows are grouped by (segment size class, delta id); every class is a
 // contiguous row range with its own segment list and gets its own launch per linear, so the
-// grouped kernel picks the token tile that fits the class.  The classes of one linear touch
-// disjoint rows: they run side by side, each on its own stream with a share of the SMs (grid cap)
-// in proportion to its estimated work, because a class of a few hot segments cannot fill the GPU
-// (one persistent CTA per SM, an item = one delta's full K for 128-256 columns).  After each
-// linear the streams join and its output is folded into the per-row checksum.  Arrays are host
-// arrays; the pointers in them are device pointers.  x_of[i] / y_of[i]: grouped activations
-// [rows, k[i]] and output buffer [rows, n[i]] of linear i (outputs of the same width may share a
-// buffer: the checksum is taken before the next linear overwrites it).  No counterpart in the
-// reference.
-namespace trb {
-constexpr int kStackSideStreams = 3;
-struct StackStreams {
-  cudaStream_t side[kStackSideStreams];
-  cudaEvent_t fork, join[kStackSideStreams];
-  bool ready;
-};
-// Side streams and events of a device, created on first use (the only resources this entry owns).
-static StackStreams* stack_streams(int dev) {
-  static StackStreams table[64] = {};
-  if (dev < 0 || dev >= 64) return nullptr;
-  StackStreams& t = table[dev];
-  if (!t.ready) {
-    for (int i = 0; i < kStackSideStreams; ++i) {
-      if (cudaStreamCreateWithFlags(&t.side[i], cudaStreamNonBlocking) != cudaSuccess) return nullptr;
-      if (cudaEventCreateWithFlags(&t.join[i], cudaEventDisableTiming) != cudaSuccess) return nullptr;
-    }
-    if (cudaEventCreateWithFlags(&t.fork, cudaEventDisableTiming) != cudaSuccess) return nullptr;
-    t.ready = true;
-  }
-  return &t;
-}
-}  // namespace trb
-
+// grouped kernel picks the token tile that fits the class.  After each linear its output is
+// folded into the per-row checksum.  Arrays are host arrays; the pointers in them are device
+// pointers.  x_of[i] / y_of[i]: grouped activations [rows, k[i]] and output buffer [rows, n[i]]
+// of linear i (outputs of the same width may share a buffer: the checksum is taken before the
+// next linear overwrites it).  No counterpart in the reference.
 extern "C" int trb_stack_pass(int n_linears, const void* const* q, const void* const* meta, const void* const* s,
                               const int* k, const int* n, const void* const* x_of, void* const* y_of,
                               int n_classes, const int* class_row0, const int* class_rows,
                               const void* const* class_ids, const void* const* class_starts,
                               const void* const* class_counts, const int* class_segs, void* checksum, int rows,
                               int groupsize, int dev, void* stream) {
-  using namespace trb;
   if (n_linears <= 0 || rows <= 0) return TRB_OK;
   if (!q || !meta || !s || !k || !n || !x_of || !y_of || !checksum) return TRB_ERR_BAD_ARG;
   if (n_classes < 0 || (n_classes > 0 && (!class_row0 || !class_rows || !class_ids || !class_starts ||
                                           !class_counts || !class_segs)))
     return TRB_ERR_BAD_ARG;
-  if (cudaSetDevice(dev) != cudaSuccess) return TRB_ERR_CUDA;
-  // Classes with work, and their share of the SMs: per segment an 8-token-tile class costs 1, a
-  // 16/32-token-tile class 1.5, a tcgen05 class 4.2 (measured on 4096x4096 and 4096x11008 deltas).
-  int active[1 + kStackSideStreams], n_active = 0;
-  double weight[1 + kStackSideStreams], total = 0.0;
-  for (int c = 0; c < n_classes; ++c) {
+  for (int c = 0; c < n_classes; ++c)
     if (class_row0[c] < 0 || class_rows[c] < 0 || class_row0[c] + class_rows[c] > rows) return TRB_ERR_BAD_ARG;
-    if (class_rows[c] == 0 || class_segs[c] <= 0) continue;
-    if (n_active == 1 + kStackSideStreams) return TRB_ERR_BAD_ARG;   // at most four size classes
-    const int avg = (class_rows[c] + class_segs[c] - 1) / class_segs[c];
-    weight[n_active] = class_segs[c] * (avg <= 8 ? 1.0 : avg <= 32 ? 1.5 : 4.2);
-    total += weight[n_active];
-    active[n_active++] = c;
-  }
-  if (n_active == 0) return TRB_OK;
-  cudaStream_t main_stream = (cudaStream_t)stream;
-  StackStreams* st = n_active > 1 ? stack_streams(dev) : nullptr;
-  if (n_active > 1 && st == nullptr) return TRB_ERR_CUDA;
-  const int sms = sm_count(dev);
-  int share[1 + kStackSideStreams];
-  for (int j = 0; j < n_active; ++j) {
-    int v = n_active == 1 ? sms : (int)(sms * weight[j] / total + 0.5);
-    v = v < 8 ? 8 : v;
-    share[j] = v & ~1;                                     // even: the tcgen05 kernel runs CTA pairs
-  }
   for (int i = 0; i < n_linears; ++i) {
-    if (n_active > 1 && cudaEventRecord(st->fork, main_stream) != cudaSuccess) return TRB_ERR_CUDA;
-    for (int j = n_active - 1; j >= 0; --j) {              // side streams first, the main stream's class last
-      const int c = active[j];
-      cudaStream_t sj = j == 0 ? main_stream : st->side[j - 1];
-      if (j > 0 && cudaStreamWaitEvent(sj, st->fork, 0) != cudaSuccess) return TRB_ERR_CUDA;
+    for (int c = 0; c < n_classes; ++c) {
+      if (class_rows[c] == 0 || class_segs[c] == 0) continue;
       const __half* x = (const __half*)x_of[i] + (size_t)class_row0[c] * k[i];
       __half* y = (__half*)y_of[i] + (size_t)class_row0[c] * n[i];
       const int rc = trb_sbmm_2_4(x, q[i], meta[i], y, s[i], class_ids[c], class_starts[c], class_counts[c], n[i],
-                                  class_rows[c], k[i], class_segs[c], nullptr, groupsize, dev, sj, -1, -1,
-                                  n_active > 1 ? share[j] : -1, 0);
+                                  class_rows[c], k[i], class_segs[c], nullptr, groupsize, dev, stream, -1, -1, -1, 0);
       if (rc != TRB_OK) return rc;
-      if (j > 0 && cudaEventRecord(st->join[j - 1], sj) != cudaSuccess) return TRB_ERR_CUDA;
     }
-    for (int j = 1; j < n_active; ++j)
-      if (cudaStreamWaitEvent(main_stream, st->join[j - 1], 0) != cudaSuccess) return TRB_ERR_CUDA;
-    const int rc = trb_row_checksum(y_of[i], checksum, rows, n[i], 1, dev, main_stream);
+    const int rc = trb_row_checksum(y_of[i], checksum, rows, n[i], 1, dev, stream);
     if (rc != TRB_OK) return rc;
   }
   return TRB_OK;
