@@ -151,7 +151,7 @@ class CpuPath:
 
 
 def cpu_baseline():
-    return CpuPath().timed(passes=200, warmup=3)
+    return CpuPath(num_sample_deltas=16).timed(passes=600, warmup=3)   # about 10 s of host work
 
 
 def run_reference_arm(args):
