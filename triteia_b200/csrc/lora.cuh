@@ -301,22 +301,41 @@ __global__ void __launch_bounds__(128) sgmv_kernel(T* __restrict__ Y, const T* _
     }
     cp_async_wait<0>();
     __syncthreads();
+    // Epilogue through shared memory (the pipeline's buffers are free now): the fp32 tile goes out
+    // as [64 rows][BN columns], then every thread adds 8-column pieces of it into y with one 16-byte
+    // read and one 16-byte write, rounding once (the accumulator fragment layout would touch
+    // 16 bytes per row and instruction).
+    constexpr int OLD = BN + 4;                      // padded row, in floats
+    static_assert(64 * OLD * 4 <= SM::BYTES, "the output tile fits the pipeline's shared memory");
+    float* otile = reinterpret_cast<float*>(sgmv_smem);
 #pragma unroll
     for (int nt = 0; nt < BN / 8; ++nt) {
-      const int col = col_base + nt * 8 + 2 * m;
-      if (col < d_out) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int row = row_base + warp * 16 + g + 8 * h;
-          if (row < r1) {
-            uint32_t* yp = reinterpret_cast<uint32_t*>(Y + (int64_t)row * d_out + col);
-            const float2 old = Cvt<T>::to_f2(*yp);
-            T o2[2] = {Cvt<T>::from_f(old.x + acc[nt][2 * h]), Cvt<T>::from_f(old.y + acc[nt][2 * h + 1])};
-            *yp = *reinterpret_cast<uint32_t*>(o2);
-          }
+      for (int h = 0; h < 2; ++h)
+        *reinterpret_cast<float2*>(otile + (warp * 16 + g + 8 * h) * OLD + nt * 8 + 2 * m) =
+            make_float2(acc[nt][2 * h], acc[nt][2 * h + 1]);
+    }
+    __syncthreads();
+    for (int v = tid; v < 64 * (BN / 8); v += 128) {
+      const int r = v / (BN / 8), c = (v % (BN / 8)) * 8;
+      const int row = row_base + r, col = col_base + c;
+      if (row < r1 && col < d_out) {
+        uint4* yp = reinterpret_cast<uint4*>(Y + (int64_t)row * d_out + col);
+        uint4 old = *yp;
+        const float4 a0 = *reinterpret_cast<const float4*>(otile + r * OLD + c);
+        const float4 a1 = *reinterpret_cast<const float4*>(otile + r * OLD + c + 4);
+        const float add[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+        uint32_t* ow = reinterpret_cast<uint32_t*>(&old);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 o = Cvt<T>::to_f2(ow[e]);
+          T o2[2] = {Cvt<T>::from_f(o.x + add[2 * e]), Cvt<T>::from_f(o.y + add[2 * e + 1])};
+          ow[e] = *reinterpret_cast<uint32_t*>(o2);
         }
+        *yp = old;
       }
     }
+    __syncthreads();                                 // the next tile's loads reuse this memory
   }  // token tiles
 }
 
