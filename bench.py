@@ -469,7 +469,7 @@ def _event_time(fn, steps, warmup):
 
 
 def run_prefill(args):
-    """BASELINE config 5: 32 deltas 5120x13824 (or 13824x5120 with --shape down), group 128, 8192 tokens in
+    """The prefill configuration: 32 deltas 5120x13824 (or 13824x5120 with --shape down), group 128, 8192 tokens in
     16 contiguous segments of 512 (deltas 0..15); optional SGMV rank-64 LoRA on the same segments.
     Tensor-bound: flops are dense-equivalent 2*T*K*N (the reference's convention, bench_sbmm.py:17)."""
     import triteia_b200.ops as ops
@@ -516,7 +516,7 @@ def run_prefill(args):
 
 
 def run_ldmm(args):
-    """BASELINE config 3: fp16 base [11008, 4096] ~N(0, 0.02), 32 per-channel deltas 4096 -> 11008, 32 LoRA
+    """The ldmm configuration: fp16 base [11008, 4096] ~N(0, 0.02), 32 per-channel deltas 4096 -> 11008, 32 LoRA
     adapters of rank 16, 256 decode tokens, ids Zipf(1.2) over the 64 ids through a seeded permutation."""
     import triteia_b200.ops as ops
     from triteia_b200 import _lib
@@ -559,7 +559,7 @@ def run_ldmm(args):
 
 
 def run_stack(args):
-    """BASELINE config 4 (the linear stack): L layers of the seven Llama-2-7B linears, 128 deltas sharded by
+    """The linear-stack configuration: L layers of the seven Llama-2-7B linears, 128 deltas sharded by
     id over the ranks, 512 tokens in all (512 / N per rank), delta id ~ Zipf(1.5); one dispatch and one
     combine per pass.  Strong scaling: the total work is fixed as N grows."""
     import torch.distributed as dist

@@ -166,7 +166,7 @@ int trb_unpack_2_4(const void* B, const void* meta, const void* s, void* w_out, 
 
 /* sums[r] = (accumulate ? sums[r] : 0) + sum over n of y[r, n]: fp32 per-row checksum of an fp16
  * matrix [rows, prob_m] (prob_m % 8 == 0, y 16-byte aligned), fixed summation order.  Used by the
- * sharded linear-stack scenario (BASELINE config "full Llama-2-7B-shaped linear stack") to return
+ * sharded linear-stack scenario (a full Llama-2-7B-shaped stack of independent delta linears) to return
  * one number per token and linear instead of every output row.  No counterpart in the reference. */
 int trb_row_checksum(const void* y, void* sums, int rows, int prob_m, int accumulate, int dev,
                      void* stream);

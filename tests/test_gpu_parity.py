@@ -285,7 +285,7 @@ def test_sbmm_edge_cases(cuda, case):
 
 
 def test_sbmm_decode_config_shape(cuda):
-    """BASELINE sbmm config at reduced delta count: 128 tokens, 4096 x 4096, group 128, 10% base."""
+    """The headline sbmm configuration at reduced delta count: 128 tokens, 4096 x 4096, group 128, 10% base."""
     ops = _ops()
     qs, metas, ss, x, idx, _ = sbmm_inputs(128, 8, 4096, 4096, 128, seed=17, sort=False)
     y = ops.sbmm_4bit_2_4_native(qs, x, metas, ss, idx)
@@ -521,7 +521,7 @@ def test_bmm_reference_shape(cuda):
 
 
 def test_ldmm_full_size_properties(cuda):
-    """BASELINE ldmm configuration at full size (4096 -> 11008, 32 deltas + 32 rank-16 adapters, 256 tokens,
+    """The ldmm benchmark configuration at full size (4096 -> 11008, 32 deltas + 32 rank-16 adapters, 256 tokens,
     Zipf(1.2) ids): agreement with the per-id loop path, doubling the input doubles the output, permuting
     tokens permutes rows; a sample of rows against the oracle."""
     ops = _ops()
@@ -553,7 +553,7 @@ def test_ldmm_full_size_properties(cuda):
 
 
 def test_sbmm_prefill_full_size_properties(cuda):
-    """BASELINE prefill configuration (5120 -> 13824, group 128, 8192 tokens in 16 segments of 512, 16 of 32
+    """The prefill benchmark configuration (5120 -> 13824, group 128, 8192 tokens in 16 segments of 512, 16 of 32
     deltas resident here): the tcgen05 path against the oracle on a sample of rows, linearity, and equality
     with the small-tile kernel on a 24-token slice of the same deltas."""
     ops = _ops()
