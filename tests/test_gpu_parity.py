@@ -572,3 +572,27 @@ def test_sbmm_prefill_full_size_properties(cuda):
     small = torch.cat([torch.arange(0, 8), torch.arange(512, 520), torch.arange(8184, 8192)]).to(cuda)
     ys = ops.sbmm_4bit_2_4_native(qs, x[small].contiguous(), metas, ss, idx[small].contiguous())
     assert oracle.row_rel_err(ys.float().cpu().numpy(), y[small].float().cpu().numpy()).max() <= 2e-3
+
+
+@pytest.mark.parametrize("rows,n", [(1, 8), (37, 256), (200, 11008)])
+def test_row_checksum(cuda, rows, n):
+    """fp32 per-row sums of an fp16 matrix: overwrite, then accumulate; identical from run to run."""
+    from triteia_b200 import _lib
+
+    g = torch.Generator(device="cuda").manual_seed(rows)
+    y = torch.randn(rows, n, generator=g, device="cuda").half()
+    sums = torch.full((rows,), 123.0, device="cuda")
+
+    def call(acc):
+        _lib.check(_lib.lib.trb_row_checksum(_lib.ptr(y), _lib.ptr(sums), rows, n, acc, _lib.dev_of(y),
+                                             _lib.stream_of(y)), "row_checksum")
+    call(0)
+    ref = y.double().sum(dim=1)
+    first = sums.clone()
+    assert torch.allclose(first.double(), ref, rtol=1e-5, atol=1e-3)
+    call(1)
+    assert torch.allclose(sums.double(), 2 * ref, rtol=1e-5, atol=2e-3)
+    call(0)
+    assert torch.equal(sums, first)
+    # bad shapes are refused before any launch
+    assert _lib.lib.trb_row_checksum(_lib.ptr(y), _lib.ptr(sums), rows, n + 1, 0, _lib.dev_of(y), _lib.stream_of(y)) != 0
