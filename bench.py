@@ -395,8 +395,17 @@ def run_gpu_arm(args):
         touched = int(uniq.numel())
     y_k = torch.empty(x_sorted.shape[0], N_OUT, dtype=torch.float16, device=dev)
     ws = torch.zeros(max(touched, 1), N_OUT // 8, dtype=torch.int32, device=dev)
-    from triteia_b200.capi import sbmm_2_4
-    kern = lambda: sbmm_2_4(x_sorted, qs, metas, y_k, ss, uniq, ws, starts, counts) if touched else None
+    # the segment-list entry point with working memory for the tail K split (what the fused step's
+    # grouped kernel runs with); TRB_KSPLIT=0 in the environment turns the split off
+    ks_bytes = _lib.lib.trb_sbmm_ksplit_bytes()
+    ks_buf = torch.zeros(ks_bytes, dtype=torch.uint8, device=dev)
+
+    def kern():
+        if touched:
+            _lib.check(_lib.lib.trb_sbmm_2_4_ksplit(
+                _lib.ptr(x_sorted), _lib.ptr(qs), _lib.ptr(metas), _lib.ptr(y_k), _lib.ptr(ss), _lib.ptr(uniq),
+                _lib.ptr(starts), _lib.ptr(counts), N_OUT, x_sorted.shape[0], K, touched, GROUP, _lib.dev_of(y_k),
+                _lib.stream_of(y_k), _lib.ptr(ks_buf), ks_bytes), "sbmm_2_4_ksplit")
     for _ in range(3):
         kern()
     k_times = time_steps(kern, args.steps, flush)

@@ -94,15 +94,30 @@ int trb_route(const void* indices, int num_tokens, int num_deltas, int tile_toke
               void* tile_start, void* tile_count, void* counters, int dev, void* stream);
 int trb_route_max_tiles(int num_tokens, int num_deltas, int tile_tokens);
 
+/* trb_sbmm_2_4 with working memory for the small-tile kernel's tail K split: when the last round
+ * of work items covers at most half of the SMs, its items are cut along K and the pieces are summed
+ * in a fixed order by whichever piece finishes last.  `ksplit`: trb_sbmm_ksplit_bytes() bytes,
+ * 256-byte aligned, first 512 bytes zero on entry (zero again when the launch has finished);
+ * nullptr = plain trb_sbmm_2_4.  No counterpart in the reference (its K split goes through the
+ * lock workspace, marlin_cuda_kernel_nm.cu). */
+size_t trb_sbmm_ksplit_bytes(void);
+int trb_sbmm_2_4_ksplit(const void* A, const void* B, const void* meta, void* C, const void* s,
+                        const void* indices, const void* starts, const void* counts, int prob_m,
+                        int prob_n, int prob_k, int prob_r, int groupsize, int dev, void* stream,
+                        void* ksplit, size_t ksplit_bytes);
+
 /* Fused indexed delta matmul: y[t] (+)= x[t] @ dequant(delta[indices[t] - index_offset]) for
  * indices[t] - index_offset in [0, num_deltas); other tokens count as "index -1".
  * Router + row gather + grouped kernel on `stream`, no host synchronisation; indices in any
  * order.  accumulate != 0: y[t] += ...  (rows with index -1 untouched); accumulate == 0:
  * rows with index >= 0 are overwritten, rows with index -1 are set to zero.
  * Stands for the body of sbmm_4bit_2_4_native (triteia/python/ops/matmul/sbmm.py:89-142)
- * after its base GEMM.  `scratch` must hold trb_sbmm_indexed_scratch_bytes(T, K, D) bytes
- * (mirrors sgmv_tmp_size, csrc/ops/sgmv.cuh:48-52). */
+ * after its base GEMM.  `scratch` should hold trb_sbmm_indexed_scratch_bytes(T, K, D) bytes
+ * (mirrors sgmv_tmp_size, csrc/ops/sgmv.cuh:48-52) and must hold at least
+ * trb_sbmm_indexed_scratch_min_bytes(T, K, D); the difference (1.2 MB) is the room for the
+ * partial tiles of the small-tile kernel's tail K split, which is left out when it is missing. */
 size_t trb_sbmm_indexed_scratch_bytes(int num_tokens, int prob_k, int num_deltas);
+size_t trb_sbmm_indexed_scratch_min_bytes(int num_tokens, int prob_k, int num_deltas);
 int trb_sbmm_indexed(const void* x, const void* qweights, const void* metas, const void* scales,
                      const void* indices, void* y, int num_tokens, int prob_m, int prob_k,
                      int num_deltas, int index_offset, int groupsize, int accumulate,
@@ -113,7 +128,7 @@ int trb_sbmm_indexed(const void* x, const void* qweights, const void* metas, con
  * contract that bans cudaMalloc after start-up because it stalls the whole device).  The working
  * memory is a fixed array inside the library image: trb_sbmm_indexed_static_capacity() bytes
  * (4 MiB + 64 KiB), held by every GPU that uses the library until the process exits.  A request
- * whose trb_sbmm_indexed_scratch_bytes() exceeds the capacity returns TRB_ERR_SCRATCH and launches
+ * whose trb_sbmm_indexed_scratch_min_bytes() exceeds the capacity returns TRB_ERR_SCRATCH and launches
  * nothing (fits e.g. 256 tokens x K 8192, or 512 tokens x K 4096).  Calls no allocator of any kind.
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that
  * device current); make that first call before any stream capture begins.  All calls on a device

@@ -45,7 +45,19 @@ struct GemmArgs {
   const unsigned char* xchg;
   long long xchg_row_bytes;
   int chunk_rows;
+  // Tail K split (8-token tiles): when the last round of work items covers at most half of the
+  // CTAs, each of its items is cut along K into `parts` pieces taken by neighbouring CTAs.  Every
+  // piece writes its fp32 partial tile to `ksplit_buf` (kKsplitSlots slots of kKsplitSlotFloats),
+  // bumps the item's counter in `ksplit_cnt` (kKsplitItems ints, zero on entry, zero again on
+  // exit) and leaves; the piece that arrives last adds all pieces in a fixed order and runs the
+  // epilogue.  Nobody waits for anybody.  nullptr: no split.
+  float* ksplit_buf;
+  int* ksplit_cnt;
 };
+constexpr int kKsplitItems = 74;              // at most half a grid of tail items is split
+constexpr int kKsplitSlots = 148;             // pieces over all tail items
+constexpr int kKsplitSlotFloats = 256 * 8;    // one 8-token x 256-column fp32 tile
+constexpr size_t kKsplitBufBytes = (size_t)kKsplitSlots * kKsplitSlotFloats * 4;
 
 template <int NB_, int SW_, int KQ_, int KS_, int STAGES_>
 struct GemmCfg {
@@ -92,6 +104,46 @@ struct WorkItem {
   int delta, row0, valid, col0;
   bool ok;
 };
+
+// The u-th unit of work of CTA b: a whole item in the full rounds, a K range of an item in the tail.
+struct WorkUnit {
+  int item, ks0, ks1, part, parts, tail;
+};
+struct TailSplit {
+  int r_full, r_tail, parts, units;   // units = this CTA's number of work units
+};
+__device__ __forceinline__ TailSplit tail_split(int n_items, int k_stages, int grid, int b, bool allowed) {
+  TailSplit t;
+  t.r_full = n_items / grid;
+  t.r_tail = n_items - t.r_full * grid;
+  t.parts = 1;
+  if (allowed && t.r_tail > 0 && 2 * t.r_tail <= grid && t.r_tail <= kKsplitItems) {
+    int s = grid / t.r_tail;
+    s = s > 8 ? 8 : s;
+    s = s > k_stages ? k_stages : s;
+    int p = 1;
+    while (2 * p <= s) p *= 2;
+    while (p > 1 && (k_stages % p != 0 || t.r_tail * p > kKsplitSlots)) p >>= 1;   // equal K ranges, slots for all
+    t.parts = p;
+  }
+  t.units = t.r_full + (b < t.r_tail * t.parts ? 1 : 0);
+  return t;
+}
+__device__ __forceinline__ WorkUnit work_unit(const TailSplit& t, int u, int grid, int b, int k_stages) {
+  WorkUnit w;
+  if (u < t.r_full) {
+    w.item = b + u * grid; w.ks0 = 0; w.ks1 = k_stages; w.part = 0; w.parts = 1; w.tail = 0;
+  } else {
+    w.tail = b / t.parts;
+    w.item = t.r_full * grid + w.tail;
+    w.part = b - w.tail * t.parts;
+    w.parts = t.parts;
+    const int len = k_stages / t.parts;
+    w.ks0 = w.part * len;
+    w.ks1 = w.ks0 + len;
+  }
+  return w;
+}
 
 // Tile t of the batch -> (segment, tile inside the segment); item = tile * n_stripes + stripe.
 template <class Cfg>
@@ -200,6 +252,10 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   const int slabs = a.K / 32;
   const int k_stages = (slabs + KS - 1) / KS;
   const int groups = a.grouped ? a.K / 128 : 1;
+  // Work units of this CTA: whole items in the full rounds, then (maybe) a K range of a tail item.
+  const TailSplit split = tail_split(n_items, k_stages, (int)gridDim.x, (int)blockIdx.x,
+                                     NB == 1 && SW * 512 <= kKsplitSlotFloats && a.ksplit_buf != nullptr &&
+                                         a.y_peers == nullptr);
 
   if (warp == Cfg::CW) {
     // ------------------------------ producer ------------------------------
@@ -213,10 +269,11 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       const uint32_t stage_tx = Cfg::X_BYTES + Cfg::Q_BYTES + Cfg::M_BYTES + (a.grouped ? Cfg::S_BYTES : 0);
       int st = 0;
       uint32_t phase = 0;
-      for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-        const WorkItem w = decode_item<Cfg>(a, prefix, n_seg, n_stripes, item);
+      for (int u = 0; u < split.units; ++u) {
+        const WorkUnit wu = work_unit(split, u, (int)gridDim.x, (int)blockIdx.x, k_stages);
+        const WorkItem w = decode_item<Cfg>(a, prefix, n_seg, n_stripes, wu.item);
         if (!w.ok) continue;
-        for (int ks = 0; ks < k_stages; ++ks) {
+        for (int ks = wu.ks0; ks < wu.ks1; ++ks) {
           mbar_wait(&empty_bar[st], phase ^ 1, dead);
           uint8_t* sbase = smem + st * Cfg::STAGE_BYTES;
           mbar_arrive_expect_tx(&full_bar[st], stage_tx);
@@ -277,11 +334,16 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   bool first_item = true;
   constexpr int JW = 4 / KQ;   // accumulator column pairs (j) that each partner warp finishes
   WorkItem w_next{};
-  if ((int)blockIdx.x < n_items) w_next = decode_item<Cfg>(a, prefix, n_seg, n_stripes, blockIdx.x);
-  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+  if (split.units > 0)
+    w_next = decode_item<Cfg>(a, prefix, n_seg, n_stripes,
+                              work_unit(split, 0, (int)gridDim.x, (int)blockIdx.x, k_stages).item);
+  for (int u = 0; u < split.units; ++u) {
+    const WorkUnit wu = work_unit(split, u, (int)gridDim.x, (int)blockIdx.x, k_stages);
     const WorkItem w = w_next;
     // Descriptor of the next item: its global loads are in flight during this item's K loop.
-    if (item + (int)gridDim.x < n_items) w_next = decode_item<Cfg>(a, prefix, n_seg, n_stripes, item + gridDim.x);
+    if (u + 1 < split.units)
+      w_next = decode_item<Cfg>(a, prefix, n_seg, n_stripes,
+                                work_unit(split, u + 1, (int)gridDim.x, (int)blockIdx.x, k_stages).item);
     if (!w.ok) continue;
     const int nbv = (w.valid + 7) >> 3;
     const bool col_ok = w.col0 + cb * 64 < a.N;
@@ -330,7 +392,7 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 #pragma unroll
         for (int c = 0; c < 4; ++c) acc[j][nb][c] = 0.f;
 
-    for (int ks = 0; ks < k_stages; ++ks) {
+    for (int ks = wu.ks0; ks < wu.ks1; ++ks) {
       mbar_wait(&full_bar[st], phase, dead);
       const uint32_t sb = smem_base + st * Cfg::STAGE_BYTES;
 
@@ -494,6 +556,48 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       }
     }
 
+    // A piece of a K-split item: park the fp32 partial tile, count in; all but the last arriver are
+    // done with the item.  The last arriver replaces its registers with the sum of every piece's
+    // tile in piece order (its own included), so the result does not depend on who came last.
+    if constexpr (NB == 1) {
+      if (wu.parts > 1) {
+        // slot of piece p of tail item t: ((t * parts + p) * 2 + jj) * CT float4s, this thread's at + tid
+        float4* tile = reinterpret_cast<float4*>(a.ksplit_buf) + (size_t)(wu.tail * wu.parts) * (kKsplitSlotFloats / 4) +
+                       (warp * 32 + lane);
+        // (static accumulator indices under a predicate, as in the epilogue: a run-time index would
+        // push the accumulators out of registers)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (j / JW == kq)
+            __stcg(tile + (wu.part * 2 + j % JW) * Cfg::CTHREADS,
+                   make_float4(acc[j][0][0], acc[j][0][1], acc[j][0][2], acc[j][0][3]));
+        // One acq_rel atomic by one thread between two CTA barriers orders every thread's tile
+        // stores before the count (release, cumulative over the barrier) and every thread's tile
+        // loads after it (acquire).  A tail piece is a CTA's last unit: the flag word is used once.
+        named_bar_sync(3, Cfg::CTHREADS);
+        volatile int* flag = dead + 1;
+        if (warp == 0 && lane == 0) {
+          int old;
+          asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(a.ksplit_cnt + wu.tail) : "memory");
+          *flag = old;
+        }
+        named_bar_sync(3, Cfg::CTHREADS);
+        if (*flag != wu.parts - 1) continue;
+        if (warp == 0 && lane == 0) a.ksplit_cnt[wu.tail] = 0;   // back to zero for the next launch
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (j / JW == kq) {
+            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+            for (int p = 0; p < wu.parts; ++p) {
+              const float4 v = __ldcg(tile + (p * 2 + j % JW) * Cfg::CTHREADS);
+              sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+            }
+            acc[j][0][0] = sum.x; acc[j][0][1] = sum.y; acc[j][0][2] = sum.z; acc[j][0][3] = sum.w;
+          }
+        }
+      }
+    }
     if (col_ok) {
       // acc[j][nb][h] is (column colb + j, token nb*8 + 2*m4 + h); acc[j][nb][2 + h] is column colb + 4 + j.
 #pragma unroll

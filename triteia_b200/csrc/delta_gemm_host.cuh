@@ -56,7 +56,11 @@ struct GemmCall {
 };
 
 template <class Cfg>
-static int launch_cfg(const GemmCall& c, const GemmArgs& a) {
+static int launch_cfg(const GemmCall& c, const GemmArgs& a_in) {
+  // TRB_KSPLIT=0 in the environment (read once) turns the tail K split off, for comparison runs.
+  static const bool no_split = [] { const char* e = getenv("TRB_KSPLIT"); return e != nullptr && e[0] == '0'; }();
+  GemmArgs a = a_in;
+  if (no_split) { a.ksplit_buf = nullptr; a.ksplit_cnt = nullptr; }
   const int slabs = a.K / 32;
   const int groups = a.grouped ? a.K / 128 : 1;
   CUtensorMap tx, tq, tm, ts;
@@ -92,7 +96,8 @@ static int launch_cfg(const GemmCall& c, const GemmArgs& a) {
   else if (a.mode == kSegIdentity) max_tiles = a.rows;
   else max_tiles = (long long)a.rows / Cfg::TT + (a.n_seg_ptr ? kMaxSegments : a.n_seg);
   const long long max_items = max_tiles * n_stripes;
-  if (max_items < grid) grid = (int)(max_items > 0 ? max_items : 1);
+  // With the tail K split the idle CTAs of a small launch take pieces of the items: keep the full grid.
+  if (max_items < grid && !(Cfg::NB == 1 && a.ksplit_buf != nullptr)) grid = (int)(max_items > 0 ? max_items : 1);
   cudaLaunchConfig_t lc = {};
   lc.gridDim = dim3(grid);
   lc.blockDim = dim3(Cfg::THREADS);
@@ -244,35 +249,59 @@ extern "C" int trb_mul_2_4(const void* A, const void* B, const void* meta, void*
   return gemm_dispatch(c, a, gemm_tile_tokens(prob_n));
 }
 
-extern "C" int trb_sbmm_2_4(const void* A, const void* B, const void* meta, void* C, const void* s,
-                            const void* indices, const void* starts, const void* counts, int prob_m, int prob_n,
-                            int prob_k, int prob_r, void* workspace, int groupsize, int dev, void* stream,
-                            int thread_k, int thread_m, int sms, int max_par) {
-  (void)workspace; (void)thread_k; (void)thread_m; (void)max_par;
+// trb_sbmm_2_4 with working memory for the small-tile kernel's tail K split: `ksplit` holds
+// trb_sbmm_ksplit_bytes() bytes, 256-byte aligned, whose first 512 bytes are zero on entry (they
+// are zero again when the launch has finished).  Without it (nullptr) this is trb_sbmm_2_4.
+extern "C" size_t trb_sbmm_ksplit_bytes(void) { return 512 + kKsplitBufBytes; }
+
+static int sbmm_segments(const void* A, const void* B, const void* meta, void* C, const void* s, const void* indices,
+                         const void* starts, const void* counts, int prob_m, int prob_n, int prob_k, int prob_r,
+                         int groupsize, int dev, void* stream, int sms, void* ksplit, size_t ksplit_bytes) {
   if (prob_r == 0) return TRB_OK;
   if (prob_r < 0 || !indices || !starts || !counts) return TRB_ERR_BAD_ARG;
   const int rc = check_common(A, B, meta, C, s, prob_m, prob_n, prob_k, groupsize);
   if (rc == -1) return TRB_OK;
   if (rc != TRB_OK) return rc;
   if (prob_r > kMaxSegments) return TRB_ERR_KERN_SHAPE;
+  if (ksplit != nullptr && (((uintptr_t)ksplit & 255) != 0 || ksplit_bytes < trb_sbmm_ksplit_bytes())) return TRB_ERR_SCRATCH;
   GemmArgs a{};
   a.mode = kSegList;
   a.seg_delta = (const int*)indices; a.seg_start = (const int*)starts; a.seg_count = (const int*)counts;
   a.n_seg = prob_r;
   a.rows = prob_n; a.N = prob_m; a.K = prob_k;
-  a.num_deltas = 1 << 30;  // the stacked tensors' leading dimension is not part of this signature
   a.grouped = groupsize == 128;
   a.scales = (const __half*)s;
   a.y = (__half*)C;
+  if (ksplit != nullptr) {
+    a.ksplit_cnt = (int*)ksplit;
+    a.ksplit_buf = (float*)((uint8_t*)ksplit + 512);
+  }
   // The tensor maps need a row bound; the reference signature has no delta count, so the maps
   // cover the largest index space a 32-bit row coordinate allows and the ids are trusted as the
   // reference trusts them.
   const int slabs = prob_k / 32;
-  int max_d = (int)(((1ull << 31) - 1) / (uint64_t)slabs);
+  const int max_d = (int)(((1ull << 31) - 1) / (uint64_t)slabs);
   GemmCall c{A, B, meta, s, max_d, groupsize, dev, sms, (cudaStream_t)stream};
   a.num_deltas = max_d;
   const int avg = (prob_n + prob_r - 1) / prob_r;
   return gemm_dispatch(c, a, gemm_tile_tokens(avg));
+}
+
+extern "C" int trb_sbmm_2_4_ksplit(const void* A, const void* B, const void* meta, void* C, const void* s,
+                                   const void* indices, const void* starts, const void* counts, int prob_m,
+                                   int prob_n, int prob_k, int prob_r, int groupsize, int dev, void* stream,
+                                   void* ksplit, size_t ksplit_bytes) {
+  return sbmm_segments(A, B, meta, C, s, indices, starts, counts, prob_m, prob_n, prob_k, prob_r, groupsize, dev,
+                       stream, -1, ksplit, ksplit_bytes);
+}
+
+extern "C" int trb_sbmm_2_4(const void* A, const void* B, const void* meta, void* C, const void* s,
+                            const void* indices, const void* starts, const void* counts, int prob_m, int prob_n,
+                            int prob_k, int prob_r, void* workspace, int groupsize, int dev, void* stream,
+                            int thread_k, int thread_m, int sms, int max_par) {
+  (void)workspace; (void)thread_k; (void)thread_m; (void)max_par;
+  return sbmm_segments(A, B, meta, C, s, indices, starts, counts, prob_m, prob_n, prob_k, prob_r, groupsize, dev,
+                       stream, sms, nullptr, 0);
 }
 
 extern "C" int trb_bmm_2_4(const void* A, const void* B, const void* meta, void* C, const void* s, int prob_m,
@@ -294,14 +323,30 @@ extern "C" int trb_bmm_2_4(const void* A, const void* B, const void* meta, void*
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-extern "C" size_t trb_sbmm_indexed_scratch_bytes(int num_tokens, int prob_k, int num_deltas) {
-  if (num_tokens <= 0 || prob_k <= 0 || num_deltas <= 0) return 256;
+// Head of the indexed path's scratch: 64 ints of router counters, then the counters of the grouped
+// kernel's tail K split.
+constexpr size_t kCounterBytes = 1024;
+constexpr int kKsplitCntOffset = 64;
+static_assert(kKsplitCntOffset * 4 + kKsplitItems * 4 <= (int)kCounterBytes, "counters fit the scratch head");
+
+// The least scratch the indexed path works with (no tail K split).
+static size_t indexed_scratch_min(int num_tokens, int prob_k, int num_deltas) {
+  if (num_tokens <= 0 || prob_k <= 0 || num_deltas <= 0) return kCounterBytes;
   const size_t tiles = (size_t)trb_route_max_tiles(num_tokens, num_deltas, 8);
-  size_t b = 256;                                          // counters
+  size_t b = kCounterBytes;                                // counters
   b += align_up((size_t)num_tokens * 4, 256);              // perm
   b += 3 * align_up(tiles * 4, 256);                       // tile lists
   b += align_up((size_t)num_tokens * prob_k * 2, 256);     // gathered activations
   return b;
+}
+
+extern "C" size_t trb_sbmm_indexed_scratch_min_bytes(int num_tokens, int prob_k, int num_deltas) {
+  return indexed_scratch_min(num_tokens, prob_k, num_deltas);
+}
+
+// What the caller should provide: the minimum plus the partial-tile slots of the tail K split.
+extern "C" size_t trb_sbmm_indexed_scratch_bytes(int num_tokens, int prob_k, int num_deltas) {
+  return indexed_scratch_min(num_tokens, prob_k, num_deltas) + kKsplitBufBytes;
 }
 
 namespace trb {
@@ -317,7 +362,8 @@ int sbmm_indexed_impl(const void* x, const void* qweights, const void* metas, co
   if (rc == -1) return TRB_OK;
   if (rc != TRB_OK) return rc;
   if (!scratch || ((uintptr_t)scratch & 255)) return TRB_ERR_BAD_ARG;
-  if (scratch_bytes < trb_sbmm_indexed_scratch_bytes(num_tokens, prob_k, num_deltas)) return TRB_ERR_SCRATCH;
+  const size_t min_bytes = indexed_scratch_min(num_tokens, prob_k, num_deltas);
+  if (scratch_bytes < min_bytes) return TRB_ERR_SCRATCH;
   if (cudaSetDevice(dev) != cudaSuccess) return TRB_ERR_CUDA;
 
   const int segs = num_tokens < num_deltas ? num_tokens : num_deltas;
@@ -330,7 +376,9 @@ int sbmm_indexed_impl(const void* x, const void* qweights, const void* metas, co
   const size_t tiles8 = (size_t)trb_route_max_tiles(num_tokens, num_deltas, 8);
 
   uint8_t* p = (uint8_t*)scratch;
-  int* counters = (int*)p; p += 256;
+  int* counters = (int*)p; p += kCounterBytes;
+  // Tail K split of the 8-token-tile kernel: only with room for its partial tiles behind the rest.
+  const bool ksplit = tt == 8 && y_peers == nullptr && scratch_bytes >= min_bytes + kKsplitBufBytes;
   int* perm = (int*)p; p += align_up((size_t)num_tokens * 4, 256);
   int* tile_delta = (int*)p; p += align_up(tiles8 * 4, 256);
   int* tile_start = (int*)p; p += align_up(tiles8 * 4, 256);
@@ -340,7 +388,8 @@ int sbmm_indexed_impl(const void* x, const void* qweights, const void* metas, co
   int r = route_launch_src(src, num_tokens, num_deltas, tt, perm, nullptr, nullptr, nullptr, tile_delta, tile_start,
                            tile_count, counters, nullptr, 0, nullptr, stream);
   if (r != TRB_OK) return r;
-  r = gather_launch(x, perm, counters, x_sorted, y, num_tokens, prob_k, prob_m, mode == 0 ? 1 : 0, stream);
+  r = gather_launch(x, perm, counters, x_sorted, y, num_tokens, prob_k, prob_m, mode == 0 ? 1 : 0, stream,
+                    ksplit ? counters + kKsplitCntOffset : nullptr, kKsplitItems);
   if (r != TRB_OK) return r;
 
   GemmArgs a{};
@@ -358,6 +407,10 @@ int sbmm_indexed_impl(const void* x, const void* qweights, const void* metas, co
   a.xchg = src.chunk_base;
   a.xchg_row_bytes = src.row_bytes;
   a.chunk_rows = chunk_rows;
+  if (ksplit) {
+    a.ksplit_cnt = counters + kKsplitCntOffset;
+    a.ksplit_buf = (float*)((uint8_t*)scratch + min_bytes);
+  }
   GemmCall c{x_sorted, qweights, metas, scales, num_deltas, groupsize, dev, -1, stream};
   return gemm_dispatch(c, a, tt);
 }

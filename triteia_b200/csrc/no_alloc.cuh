@@ -13,7 +13,7 @@
 
 #include "common.cuh"
 
-// Limit: what trb_sbmm_indexed_scratch_bytes(T, K, D) reports must fit in this array
+// Limit: what trb_sbmm_indexed_scratch_min_bytes(T, K, D) reports must fit in this array
 // (e.g. T <= 256 tokens with K <= 8192, or T <= 512 with K <= 4096).  Every GPU that loads the
 // library carries the array from the first use of the library on it until the process exits.
 #define TRB_STATIC_SCRATCH_BYTES (4u * 1024u * 1024u + 64u * 1024u)
@@ -53,13 +53,14 @@ extern "C" int trb_sbmm_indexed_static(const void* x, const void* qweights, cons
   using namespace trb;
   if (num_tokens < 0 || prob_k < 0 || num_deltas <= 0) return TRB_ERR_BAD_ARG;
   // Sizes beyond the array are refused before anything is launched.
-  if (trb_sbmm_indexed_scratch_bytes(num_tokens, prob_k, num_deltas) > (size_t)TRB_STATIC_SCRATCH_BYTES)
+  if (trb_sbmm_indexed_scratch_min_bytes(num_tokens, prob_k, num_deltas) > (size_t)TRB_STATIC_SCRATCH_BYTES)
     return TRB_ERR_SCRATCH;
   void* scratch = nullptr;
   const int rc = static_scratch_address(dev, &scratch);
   if (rc != TRB_OK) return rc;
   // Nothing in the array has to start at zero: the router rewrites the counters, the permutation
-  // and the tile list on every call, and the kernel reads only the rows the tile list names.
+  // and the tile list on every call, the gather kernel zeroes the K-split counters, and the
+  // grouped kernel reads only the rows the tile list names.
   return trb_sbmm_indexed(x, qweights, metas, scales, indices, y, num_tokens, prob_m, prob_k, num_deltas,
                           index_offset, groupsize, accumulate, scratch, TRB_STATIC_SCRATCH_BYTES, dev, stream);
 }

@@ -194,10 +194,14 @@ route_kernel(const RouteSrc src, int T, int D, int W, int TT, int* __restrict__ 
 // x_sorted[p] = x[perm[p]] for every sorted position; optionally zero y rows whose id is -1.
 __global__ void gather_rows_kernel(const uint4* __restrict__ x, const int* __restrict__ perm,
                                    const int* __restrict__ counters, uint4* __restrict__ x_sorted,
-                                   uint4* __restrict__ y, int T, int k_vec, int n_vec, int zero_base_rows) {
+                                   uint4* __restrict__ y, int T, int k_vec, int n_vec, int zero_base_rows,
+                                   int* __restrict__ zero_ints, int n_zero_ints) {
   const int p = blockIdx.x;
   pdl_launch_dependents();
   pdl_wait();                          // perm and counters come from the router launched just before
+  // Counters of the grouped kernel's tail K split: zero at every call (the scratch is the caller's).
+  if (p == 0 && zero_ints != nullptr)
+    for (int i = threadIdx.x; i < n_zero_ints; i += blockDim.x) zero_ints[i] = 0;
   if (p >= T) return;
   const int src = perm[p];
   if (src < 0 || src >= T) return;
@@ -261,7 +265,7 @@ int route_launch(const int* indices, int T, int D, int TT, int id_offset, int* p
 }
 
 int gather_launch(const void* x, const int* perm, const int* counters, void* x_sorted, void* y, int T, int K,
-                  int N, int zero_base_rows, cudaStream_t stream) {
+                  int N, int zero_base_rows, cudaStream_t stream, int* zero_ints = nullptr, int n_zero_ints = 0) {
   if (T == 0) return TRB_OK;
   cudaLaunchConfig_t lc = {};
   lc.gridDim = dim3(T);
@@ -273,7 +277,7 @@ int gather_launch(const void* x, const int* perm, const int* counters, void* x_s
   lc.attrs = at;
   lc.numAttrs = 1;
   return cudaLaunchKernelEx(&lc, gather_rows_kernel, (const uint4*)x, perm, counters, (uint4*)x_sorted, (uint4*)y, T,
-                            K / 8, N / 8, zero_base_rows) == cudaSuccess
+                            K / 8, N / 8, zero_base_rows, zero_ints, n_zero_ints) == cudaSuccess
              ? TRB_OK
              : TRB_ERR_CUDA;
 }
