@@ -477,6 +477,30 @@ def _event_time(fn, steps, warmup):
     return a.elapsed_time(b) / steps
 
 
+def _e2e_time(fn, host_inputs, dev, steps):
+    """Wall-clock ms per step of fn(*device copies of host_inputs) with the copies in from pinned host
+    memory and the copy of the result back inside the timed region (one step in flight)."""
+    pinned = [t.cpu().pin_memory() for t in host_inputs]
+    out_host = None
+
+    def one():
+        nonlocal out_host
+        ins = [t.to(dev, non_blocking=True) for t in pinned]
+        y = fn(*ins)
+        if out_host is None:
+            out_host = torch.empty(y.shape, dtype=y.dtype).pin_memory()
+        out_host.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(2):
+        one()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one()
+    dt = (time.perf_counter() - t0) * 1e3 / steps
+    return dt, int(sum(t.numel() * t.element_size() for t in pinned)), int(out_host.numel() * out_host.element_size())
+
+
 def run_prefill(args):
     """The prefill configuration: 32 deltas 5120x13824 (or 13824x5120 with --shape down), group 128, 8192 tokens in
     16 contiguous segments of 512 (deltas 0..15); optional SGMV rank-64 LoRA on the same segments.
@@ -505,6 +529,8 @@ def run_prefill(args):
     t_step = _event_time(lambda: ops.sbmm_4bit_2_4_native(qs, x, metas, ss, idx), args.steps, max(3, args.warmup))
     t_kern = _event_time(lambda: sbmm_2_4(x, qs, metas, yk, ss, uniq, ws, starts, counts), args.steps, 3)
     t_lora = _event_time(lambda: ops.lora_sgmv(A, B, x, idx), max(1, args.steps // 4), 2)
+    t_e2e, h2d, d2h = _e2e_time(lambda xd, idd: ops.sbmm_4bit_2_4_native(qs, xd, metas, ss, idd), [x, idx], dev,
+                                max(2, args.steps // 4))
     clocks = sampler.stop()
     flops = 2.0 * T * k * n
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -515,6 +541,8 @@ def run_prefill(args):
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": f"sbmm-prefill-32x{k}x{n}-g128-8192tok-16seg", "sgmv_rank64_ms": t_lora,
                        "l2": "inputs larger than L2 (442 MB of packed deltas touched, 84-226 MB of activations)"},
+            "e2e": {"value": T / (t_e2e * 1e-3), "unit": UNIT, "ms_per_step": t_e2e, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "note": "one step in flight; bound by the host link (x in, y out)"},
             "gpu_launches": 3 * args.steps,
             "roofline": {"bound": "tensor", "achieved": ach, "peak": 2 * dense, "unit": "TFLOP/s", "frac": ach / (2 * dense),
                          "peak_source": "2 x measured dense bf16 burst (MEASURED_PEAKS.json has no sparse entry)",
@@ -549,6 +577,8 @@ def run_ldmm(args):
     sampler.start()
     t_step = _event_time(lambda: ops.ldmm(idx, x, A, B, qs, metas, ss, base_weight=base), args.steps, max(3, args.warmup))
     t_base = _event_time(lambda: torch.matmul(x, base.t()), args.steps, 3)
+    t_e2e, h2d, d2h = _e2e_time(lambda idd, xd: ops.ldmm(idd, xd, A, B, qs, metas, ss, base_weight=base), [idx, x], dev,
+                                args.steps)
     clocks = sampler.stop()
     alg = (n * k * 2 + touched_d * (k * n // 4 + k * n // 8 + n * 2) + touched_l * (k * R + R * n) * 2 + T * k * 2 + T * n * 2)
     peak, peak_src = peaks()
@@ -559,6 +589,8 @@ def run_ldmm(args):
             "config": {"workload": "ldmm-256tok-4096x11008-32deltas-32lora-r16-zipf1.2", "deltas_touched": touched_d,
                        "adapters_touched": touched_l, "base_gemm_ms": t_base,
                        "l2": f"inputs larger than L2 ({alg / 1e6:.0f} MB streamed per step)"},
+            "e2e": {"value": T / (t_e2e * 1e-3), "unit": UNIT, "ms_per_step": t_e2e, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "note": "one step in flight"},
             "gpu_launches": 4 * args.steps,
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
                          "peak_source": peak_src, "kernel": "whole step (library base GEMM + LoRA + router + gather + grouped kernel)",
