@@ -596,3 +596,50 @@ def test_row_checksum(cuda, rows, n):
     assert torch.equal(sums, first)
     # bad shapes are refused before any launch
     assert _lib.lib.trb_row_checksum(_lib.ptr(y), _lib.ptr(sums), rows, n + 1, 0, _lib.dev_of(y), _lib.stream_of(y)) != 0
+
+
+@pytest.mark.parametrize("segs,tokens", [(3, 5), (20, 40), (40, 100)])
+def test_segment_list_tail_k_split(cuda, segs, tokens):
+    """trb_sbmm_2_4_ksplit: few work items (every one is a split tail item), a mix, and a launch whose
+    last round is split.  Against the oracle, against the unsplit entry point, twice for bit identity,
+    and the counters are zero again afterwards."""
+    import triteia_b200.ops as ops
+    from triteia_b200 import _lib
+    from triteia_b200.capi import sbmm_2_4
+
+    K, N, g = 1024, 2048, 128
+    qs, metas, ss = ops.random_packed_deltas(segs, K, N, groupsize=g, device=cuda, seed=segs, scale_lo=0.005, scale_hi=0.02)
+    rng = np.random.default_rng(tokens)
+    ids = np.sort(rng.integers(0, segs, tokens)).astype(np.int32)
+    idx = torch.from_numpy(ids).to(cuda)
+    x = torch.randn(tokens, K, device=cuda, generator=torch.Generator(cuda).manual_seed(1)).half()
+    uniq, counts = torch.unique_consecutive(idx, return_counts=True)
+    starts = (torch.cumsum(counts, 0) - counts).int()
+    uniq, counts = uniq.int(), counts.int()
+    nbytes = _lib.lib.trb_sbmm_ksplit_bytes()
+    scratch = torch.zeros(nbytes, dtype=torch.uint8, device=cuda)
+
+    def split_call(y):
+        _lib.check(_lib.lib.trb_sbmm_2_4_ksplit(_lib.ptr(x), _lib.ptr(qs), _lib.ptr(metas), _lib.ptr(y), _lib.ptr(ss),
+                                                _lib.ptr(uniq), _lib.ptr(starts), _lib.ptr(counts), N, tokens, K,
+                                                int(uniq.numel()), g, _lib.dev_of(y), _lib.stream_of(y),
+                                                _lib.ptr(scratch), nbytes), "sbmm_2_4_ksplit")
+    y1 = torch.full((tokens, N), 3.0, dtype=torch.float16, device=cuda)
+    y2 = torch.full((tokens, N), -3.0, dtype=torch.float16, device=cuda)
+    split_call(y1)
+    split_call(y2)
+    y0 = torch.empty(tokens, N, dtype=torch.float16, device=cuda)
+    ws = torch.zeros(int(uniq.numel()), N // 8, dtype=torch.int32, device=cuda)
+    sbmm_2_4(x, qs, metas, y0, ss, uniq, ws, starts, counts)
+    torch.cuda.synchronize()
+    assert torch.equal(y1, y2)
+    assert int(scratch[:512].max()) == 0
+    ref = oracle.sbmm(qs.cpu().numpy(), x.cpu().numpy(), metas.cpu().numpy(), ss.cpu().numpy(), ids)
+    assert oracle.row_rel_err(y1.float().cpu().numpy(), ref).max() <= 1e-2
+    assert oracle.row_rel_err(y1.float().cpu().numpy(), y0.float().cpu().numpy()).max() <= 1e-2
+    # a scratch that is too small or misaligned is refused
+    assert _lib.lib.trb_sbmm_2_4_ksplit(_lib.ptr(x), _lib.ptr(qs), _lib.ptr(metas), _lib.ptr(y1), _lib.ptr(ss),
+                                        _lib.ptr(uniq), _lib.ptr(starts), _lib.ptr(counts), N, tokens, K,
+                                        int(uniq.numel()), g, _lib.dev_of(y1), _lib.stream_of(y1), _lib.ptr(scratch),
+                                        1024) == _lib.ERR_SCRATCH
+    assert _lib.device_status(0) == 0
