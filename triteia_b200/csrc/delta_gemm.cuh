@@ -254,8 +254,7 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   const int groups = a.grouped ? a.K / 128 : 1;
   // Work units of this CTA: whole items in the full rounds, then (maybe) a K range of a tail item.
   const TailSplit split = tail_split(n_items, k_stages, (int)gridDim.x, (int)blockIdx.x,
-                                     NB == 1 && SW * 512 <= kKsplitSlotFloats && a.ksplit_buf != nullptr &&
-                                         a.y_peers == nullptr);
+                                     NB == 1 && SW * 512 <= kKsplitSlotFloats && a.ksplit_buf != nullptr);
 
   if (warp == Cfg::CW) {
     // ------------------------------ producer ------------------------------

@@ -378,7 +378,7 @@ int sbmm_indexed_impl(const void* x, const void* qweights, const void* metas, co
   uint8_t* p = (uint8_t*)scratch;
   int* counters = (int*)p; p += kCounterBytes;
   // Tail K split of the 8-token-tile kernel: only with room for its partial tiles behind the rest.
-  const bool ksplit = tt == 8 && y_peers == nullptr && scratch_bytes >= min_bytes + kKsplitBufBytes;
+  const bool ksplit = tt == 8 && scratch_bytes >= min_bytes + kKsplitBufBytes;
   int* perm = (int*)p; p += align_up((size_t)num_tokens * 4, 256);
   int* tile_delta = (int*)p; p += align_up(tiles8 * 4, 256);
   int* tile_start = (int*)p; p += align_up(tiles8 * 4, 256);

@@ -22,6 +22,7 @@ __global__ void shard_pack_kernel(const uint4* __restrict__ x, const int* __rest
                                   int my_rank, uint4* __restrict__ y_zero, int N, int T, int K, int world, int cap) {
   // Chunk for rank r: in the local send buffer at chunk index r, or (peer mode) straight in rank r's
   // receive buffer at chunk index my_rank, written over NVLink.
+  pdl_wait();   // slot_of and bin_count come from the router launched just before
   const long long row_bytes = (long long)K * 2;
   auto chunk = [&](int r) -> unsigned char* {
     return peers ? peers[r] + (long long)my_rank * (cap + 1) * row_bytes : send + (long long)r * (cap + 1) * row_bytes;
@@ -107,11 +108,20 @@ extern "C" int trb_shard_dispatch(const void* x, const void* indices, int num_to
   int rc = route_launch_src(src, num_tokens, world, 1 << 30, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
                             nullptr, counters, (int*)slot_of, num_tokens, bin_count, stream);
   if (rc != TRB_OK) return rc;
-  shard_pack_kernel<<<num_tokens + world, 128, 0, stream>>>((const uint4*)x, (const int*)indices, (const int*)slot_of,
-                                                           bin_count, (unsigned char*)send_buf,
-                                                           (unsigned char* const*)peer_recv_ptrs, my_rank, (uint4*)y_zero,
-                                                           prob_m, num_tokens, prob_k, world, num_tokens);
-  return cudaGetLastError() == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3(num_tokens + world);
+  lc.blockDim = dim3(128);
+  lc.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // the kernel waits (pdl_wait) before it reads
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = at;
+  lc.numAttrs = 1;
+  return cudaLaunchKernelEx(&lc, shard_pack_kernel, (const uint4*)x, (const int*)indices, (const int*)slot_of,
+                            (const int*)bin_count, (unsigned char*)send_buf, (unsigned char* const*)peer_recv_ptrs,
+                            my_rank, (uint4*)y_zero, prob_m, num_tokens, prob_k, world, num_tokens) == cudaSuccess
+             ? TRB_OK
+             : TRB_ERR_CUDA;
 }
 
 extern "C" int trb_shard_combine(const void* back_buf, const void* slot_of, void* y, int num_tokens, int prob_m,
