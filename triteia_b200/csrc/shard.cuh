@@ -16,10 +16,24 @@ namespace trb {
 
 // One CTA per token: copy its row into its slot of the send buffer and record its local delta id.
 // CTAs T .. T + world - 1 write the per-chunk row counts.
+// inline_plan: small batches skip the router launch; every CTA counts for itself how many earlier
+// tokens go to the same rank (the same stable order the router gives) and writes slot_of.
+__device__ __forceinline__ int block_sum_128(int v, int* sm) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = v;
+  __syncthreads();
+  const int total = sm[0] + sm[1] + sm[2] + sm[3];
+  __syncthreads();
+  return total;
+}
+
 __global__ void shard_pack_kernel(const uint4* __restrict__ x, const int* __restrict__ indices,
-                                  const int* __restrict__ slot_of, const int* __restrict__ bin_count,
+                                  int* __restrict__ slot_of, const int* __restrict__ bin_count,
                                   unsigned char* __restrict__ send, unsigned char* const* __restrict__ peers,
-                                  int my_rank, uint4* __restrict__ y_zero, int N, int T, int K, int world, int cap) {
+                                  int my_rank, uint4* __restrict__ y_zero, int N, int T, int K, int world, int cap,
+                                  int inline_plan) {
+  __shared__ int sm_cnt[4];
   // Chunk for rank r: in the local send buffer at chunk index r, or (peer mode) straight in rank r's
   // receive buffer at chunk index my_rank, written over NVLink.
   pdl_wait();   // slot_of and bin_count come from the router launched just before
@@ -30,13 +44,39 @@ __global__ void shard_pack_kernel(const uint4* __restrict__ x, const int* __rest
   const int b = blockIdx.x;
   if (b >= T) {
     const int r = b - T;
-    if (r < world && threadIdx.x == 0) {
+    if (r >= world) return;
+    int count;
+    if (inline_plan) {
+      int c = 0;
+      for (int t = threadIdx.x; t < T; t += blockDim.x) {
+        const int id = indices[t];
+        c += (id >= 0 && id % world == r) ? 1 : 0;
+      }
+      count = block_sum_128(c, sm_cnt);
+    } else {
+      count = bin_count[r];
+    }
+    if (threadIdx.x == 0) {
       int* ids = reinterpret_cast<int*>(chunk(r) + (long long)cap * row_bytes);
-      ids[cap] = min(bin_count[r], cap);
+      ids[cap] = min(count, cap);
     }
     return;
   }
-  const int slot = slot_of[b];
+  int slot;
+  if (inline_plan) {
+    const int my_id = indices[b];
+    const int my_r = my_id >= 0 ? my_id % world : -1;
+    int c = 0;
+    for (int t = threadIdx.x; t < b; t += blockDim.x) {
+      const int id = indices[t];
+      c += (id >= 0 && id % world == my_r) ? 1 : 0;
+    }
+    const int q = block_sum_128(c, sm_cnt);
+    slot = my_r >= 0 ? my_r * cap + q : -1;
+    if (threadIdx.x == 0) slot_of[b] = slot;
+  } else {
+    slot = slot_of[b];
+  }
   if (slot < 0) {
     // Peer form: nobody will write this token's output row, so it is cleared here.
     if (y_zero)
@@ -105,9 +145,13 @@ extern "C" int trb_shard_dispatch(const void* x, const void* indices, int num_to
   RouteSrc src{};
   src.indices = (const int*)indices;
   src.mod = world;
-  int rc = route_launch_src(src, num_tokens, world, 1 << 30, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
-                            nullptr, counters, (int*)slot_of, num_tokens, bin_count, stream);
-  if (rc != TRB_OK) return rc;
+  // Small batches plan inside the pack kernel (one launch less); large ones go through the router.
+  const int inline_plan = num_tokens <= 1024 ? 1 : 0;
+  if (!inline_plan) {
+    const int rc = route_launch_src(src, num_tokens, world, 1 << 30, nullptr, nullptr, nullptr, nullptr, nullptr,
+                                    nullptr, nullptr, counters, (int*)slot_of, num_tokens, bin_count, stream);
+    if (rc != TRB_OK) return rc;
+  }
   cudaLaunchConfig_t lc = {};
   lc.gridDim = dim3(num_tokens + world);
   lc.blockDim = dim3(128);
@@ -117,9 +161,10 @@ extern "C" int trb_shard_dispatch(const void* x, const void* indices, int num_to
   at[0].val.programmaticStreamSerializationAllowed = 1;
   lc.attrs = at;
   lc.numAttrs = 1;
-  return cudaLaunchKernelEx(&lc, shard_pack_kernel, (const uint4*)x, (const int*)indices, (const int*)slot_of,
+  return cudaLaunchKernelEx(&lc, shard_pack_kernel, (const uint4*)x, (const int*)indices, (int*)slot_of,
                             (const int*)bin_count, (unsigned char*)send_buf, (unsigned char* const*)peer_recv_ptrs,
-                            my_rank, (uint4*)y_zero, prob_m, num_tokens, prob_k, world, num_tokens) == cudaSuccess
+                            my_rank, (uint4*)y_zero, prob_m, num_tokens, prob_k, world, num_tokens,
+                            inline_plan) == cudaSuccess
              ? TRB_OK
              : TRB_ERR_CUDA;
 }
