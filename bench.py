@@ -453,7 +453,7 @@ def run_gpu_arm(args):
                          # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this
                          # launch (profiles/delta_gemm_kernel_sbmm-decode-64x4096x4096-g128.md);
                          # only known for the single-GPU seed (56 deltas touched).
-                         "traffic": 373310976 if (world == 1 and touched == 56) else None},
+                         "traffic": 374398720 if (world == 1 and touched == 56) else None},
             "clocks": clocks, "device_status": status, "wall_s": wall_s,
         }
         if world == 1 and not args.no_cpu_baseline:
