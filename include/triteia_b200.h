@@ -179,6 +179,15 @@ int trb_shard_combine(const void* back_buf, const void* slot_of, void* y, int nu
 int trb_unpack_2_4(const void* B, const void* meta, const void* s, void* w_out, int prob_m,
                    int prob_k, int groupsize, int dev, void* stream);
 
+/* The packer as a kernel: fp16 weight [K, N] (K = prob_k input features, N = prob_m output features;
+ * the two largest magnitudes of every four K positions are kept) and logical scales fp16 [G, N]
+ * (G = 1 or K / 128) -> qweight int32 [K/32, 2N], meta int16 [N, K/16] (physical order), stored
+ * scales fp16 [G, N].  Same result as the reference's host packer
+ * (triteia/python/nn/linear.py:79-141) for weights that are already 2:4 sparse; K % 128 == 0,
+ * N % 256 == 0 as there. */
+int trb_pack_2_4(const void* weight_kn, const void* scales_logical, void* qweight, void* meta,
+                 void* scales_stored, int prob_k, int prob_m, int groupsize, int dev, void* stream);
+
 /* sums[r] = (accumulate ? sums[r] : 0) + sum over n of y[r, n]: fp32 per-row checksum of an fp16
  * matrix [rows, prob_m] (prob_m % 8 == 0, y 16-byte aligned), fixed summation order.  Used by the
  * sharded linear-stack scenario (a full Llama-2-7B-shaped stack of independent delta linears) to return

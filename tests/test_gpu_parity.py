@@ -643,3 +643,30 @@ def test_segment_list_tail_k_split(cuda, segs, tokens):
                                         int(uniq.numel()), g, _lib.dev_of(y1), _lib.stream_of(y1), _lib.ptr(scratch),
                                         1024) == _lib.ERR_SCRATCH
     assert _lib.device_status(0) == 0
+
+
+@pytest.mark.parametrize("k,n,groupsize", [(128, 256, -1), (512, 768, 128), (1024, 512, -1)])
+def test_pack_kernel_bit_exact(cuda, k, n, groupsize):
+    """The packer kernel against the torch packer (itself pinned on the reference's vectors) and the
+    round trip through the on-GPU decoder."""
+    from triteia_b200.ops.utils.sparsity import pack_2_4, pack_2_4_cuda
+    from triteia_b200 import _lib
+
+    g = torch.Generator(device="cuda").manual_seed(k + n)
+    groups = 1 if groupsize == -1 else k // groupsize
+    lev = torch.randint(1, 8, (k, n), generator=g, device=cuda) * (torch.randint(0, 2, (k, n), generator=g, device=cuda) * 2 - 1)
+    keep = torch.rand(k // 4, 4, n, generator=g, device=cuda).argsort(dim=1).argsort(dim=1) < 2
+    scales = (torch.rand(groups, n, generator=g, device=cuda) * 0.01 + 0.001).half()
+    s_rows = scales if groups == 1 else scales.repeat_interleave(k // groups, dim=0)
+    w = ((lev * keep.reshape(k, n)).half() * s_rows).half()
+    q_ref, s_ref, m_ref = pack_2_4(w, scales)
+    q, s, m = pack_2_4_cuda(w, scales)
+    torch.cuda.synchronize()
+    assert torch.equal(q, q_ref) and torch.equal(m, m_ref) and torch.equal(s, s_ref)
+    out = torch.empty(k, n, dtype=torch.float16, device=cuda)
+    _lib.check(_lib.lib.trb_unpack_2_4(_lib.ptr(q), _lib.ptr(m), _lib.ptr(s), _lib.ptr(out), n, k, groupsize, 0,
+                                       _lib.stream_of(out)), "unpack")
+    torch.cuda.synchronize()
+    assert torch.equal(out, w)
+    assert _lib.lib.trb_pack_2_4(_lib.ptr(w), _lib.ptr(scales), _lib.ptr(q), _lib.ptr(m), _lib.ptr(s), k + 1, n, groupsize, 0,
+                                 _lib.stream_of(w)) == _lib.ERR_PROB_SHAPE

@@ -38,6 +38,7 @@ SIGNATURES = {
     "trb_shard_compute": (_i, [_vp] * 5 + [_i] * 6 + [_vp, _i, _vp, _sz, _i, _vp]),
     "trb_shard_combine": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "trb_unpack_2_4": (_i, [_vp] * 4 + [_i] * 4 + [_vp]),
+    "trb_pack_2_4": (_i, [_vp] * 5 + [_i] * 4 + [_vp]),
     "trb_row_checksum": (_i, [_vp] * 2 + [_i] * 4 + [_vp]),
     "trb_stack_pass": (_i, [_i] + [_vp] * 7 + [_i] + [_vp] * 7 + [_i] * 3 + [_vp]),
     "trb_bgmv": (_i, [_vp] * 4 + [_i] * 5 + [_f, _i, _i, _vp]),

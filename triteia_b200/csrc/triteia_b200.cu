@@ -11,6 +11,7 @@
 #include "delta_gemm_host.cuh"
 #include "shard.cuh"
 #include "unpack.cuh"
+#include "pack.cuh"
 #include "stack.cuh"
 #include "lora.cuh"
 #include "no_alloc.cuh"

@@ -121,3 +121,27 @@ def pack_2_4(weight_kn: torch.Tensor, scales: torch.Tensor):
     codes_nk = (mask * codes.t()).contiguous()
     comp, meta = compress_2_4(codes_nk)
     return pack_codes(comp), store_scales(scales.to(torch.float16)), meta
+
+
+def pack_2_4_cuda(weight_kn: torch.Tensor, scales: torch.Tensor):
+    """pack_2_4 as one CUDA kernel (trb_pack_2_4): fp16 weight [K, N] and logical scales fp16 [G, N]
+    on a GPU -> (qweight, stored scales, meta).  Identical to pack_2_4 for weights that are already
+    2:4 sparse along K (otherwise equal magnitudes inside a group of four may be pruned differently:
+    torch's argsort leaves the order of ties open, the kernel keeps the higher index)."""
+    from ... import _lib
+
+    if not weight_kn.is_cuda or weight_kn.dtype != torch.float16 or scales.dtype != torch.float16:
+        raise RuntimeError("pack_2_4_cuda needs fp16 CUDA tensors")
+    k, n = weight_kn.shape
+    g = scales.shape[0]
+    if g != 1 and k // g != 128:
+        raise ValueError("group size must be -1 (one row of scales) or 128")
+    weight_kn, scales = weight_kn.contiguous(), scales.contiguous()
+    dev = weight_kn.device
+    q = torch.empty(k // 32, 2 * n, dtype=torch.int32, device=dev)
+    meta = torch.empty(n, k // 16, dtype=torch.int16, device=dev)
+    s_out = torch.empty(g, n, dtype=torch.float16, device=dev)
+    _lib.check(_lib.lib.trb_pack_2_4(_lib.ptr(weight_kn), _lib.ptr(scales), _lib.ptr(q), _lib.ptr(meta), _lib.ptr(s_out),
+                                     k, n, -1 if g == 1 else 128, _lib.dev_of(weight_kn), _lib.stream_of(weight_kn)),
+               "pack_2_4")
+    return q, s_out, meta
