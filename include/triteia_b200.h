@@ -188,6 +188,23 @@ int trb_unpack_2_4(const void* B, const void* meta, const void* s, void* w_out, 
 int trb_pack_2_4(const void* weight_kn, const void* scales_logical, void* qweight, void* meta,
                  void* scales_stored, int prob_k, int prob_m, int groupsize, int dev, void* stream);
 
+/* Element-wise neighbours of the linears, as the reference's extension offers them.
+ * trb_gelu_quick: out = x * sigmoid(1.702 x) over numel elements (numel % 8 == 0, 16-byte aligned);
+ *   replaces vllm::gelu_quick (csrc/ops/activations.cu:203-207).
+ * trb_silu_and_mul: out[t, :d] = silu(in[t, :d]) * in[t, d:2d] (d % 8 == 0); replaces silu_and_mul
+ *   (activations.cu:68-72).
+ * trb_rotary_embedding: in-place GPT-NeoX (is_neox) or GPT-J rotation of the first rot_dim elements
+ *   of every head; positions int64 [T], cos_sin_cache [max_position, rot_dim], strides in elements,
+ *   key may be NULL; cache_offsets int64 [T] or NULL (the batched form).  Replaces
+ *   rotary_embedding / batched_rotary_embedding (csrc/ops/pos_encoding_kernels.cu:118-213).
+ * dtype: TRB_F16 or TRB_BF16. */
+int trb_gelu_quick(void* out, const void* in, long long numel, int dtype, int dev, void* stream);
+int trb_silu_and_mul(void* out, const void* in, int num_tokens, int d, int dtype, int dev, void* stream);
+int trb_rotary_embedding(const void* positions, void* query, void* key, const void* cos_sin_cache,
+                         const void* cache_offsets, int num_tokens, int rot_dim, long long query_stride,
+                         long long key_stride, int num_heads, int num_kv_heads, int head_size,
+                         int is_neox, int dtype, int dev, void* stream);
+
 /* sums[r] = (accumulate ? sums[r] : 0) + sum over n of y[r, n]: fp32 per-row checksum of an fp16
  * matrix [rows, prob_m] (prob_m % 8 == 0, y 16-byte aligned), fixed summation order.  Used by the
  * sharded linear-stack scenario (a full Llama-2-7B-shaped stack of independent delta linears) to return

@@ -670,3 +670,50 @@ def test_pack_kernel_bit_exact(cuda, k, n, groupsize):
     assert torch.equal(out, w)
     assert _lib.lib.trb_pack_2_4(_lib.ptr(w), _lib.ptr(scales), _lib.ptr(q), _lib.ptr(m), _lib.ptr(s), k + 1, n, groupsize, 0,
                                  _lib.stream_of(w)) == _lib.ERR_PROB_SHAPE
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_elementwise_neighbours(cuda, dtype):
+    """gelu_quick, silu_and_mul and rotary_embedding (both styles, plain and batched) against fp32
+    torch statements of the same formulas; tolerance = a few roundings of the 16-bit type."""
+    from triteia_b200 import triteia_cuda as tc
+    from triteia_b200.capi import QuickGELU, rotary_embedding, batched_rotary_embedding
+
+    g = torch.Generator(device="cuda").manual_seed(3)
+    tol = dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=4e-3, atol=4e-3)
+    x = torch.randn(37, 11008, generator=g, device=cuda).to(dtype)
+    y = QuickGELU()(x)
+    assert torch.allclose(y.float(), x.float() * torch.sigmoid(1.702 * x.float()), **tol)
+    gu = torch.randn(37, 2 * 1024, generator=g, device=cuda).to(dtype)
+    out = torch.empty(37, 1024, dtype=dtype, device=cuda)
+    tc.silu_and_mul(out, gu)
+    ref = torch.nn.functional.silu(gu[:, :1024].float()) * gu[:, 1024:].float()
+    assert torch.allclose(out.float(), ref, **tol)
+
+    T, H, KVH, hs, rot, maxpos = 19, 8, 2, 64, 32, 100
+    cache = torch.randn(2 * maxpos, rot, generator=g, device=cuda).clamp(-1, 1).to(dtype)
+    pos = torch.randint(0, maxpos, (T,), generator=g, device=cuda, dtype=torch.int64)
+    offs = torch.randint(0, 2, (T,), generator=g, device=cuda, dtype=torch.int64) * maxpos
+
+    def ref_rot(t, rows, neox):
+        t = t.float().reshape(T, -1, hs).clone()
+        cos, sin = cache[rows, : rot // 2].float()[:, None, :], cache[rows, rot // 2:].float()[:, None, :]
+        if neox:
+            a, b = t[..., : rot // 2].clone(), t[..., rot // 2: rot].clone()
+            t[..., : rot // 2], t[..., rot // 2: rot] = a * cos - b * sin, b * cos + a * sin
+        else:
+            a, b = t[..., 0:rot:2].clone(), t[..., 1:rot:2].clone()
+            t[..., 0:rot:2], t[..., 1:rot:2] = a * cos - b * sin, b * cos + a * sin
+        return t.reshape(T, -1)
+
+    for neox in (True, False):
+        q0 = torch.randn(T, H * hs, generator=g, device=cuda).to(dtype)
+        k0 = torch.randn(T, KVH * hs, generator=g, device=cuda).to(dtype)
+        q, k = q0.clone(), k0.clone()
+        rotary_embedding(pos, q, k, hs, cache, neox)
+        assert torch.allclose(q.float(), ref_rot(q0, pos, neox), **tol) and torch.allclose(k.float(), ref_rot(k0, pos, neox), **tol)
+        q, k = q0.clone(), k0.clone()
+        batched_rotary_embedding(pos, q, k, hs, cache, neox, rot, offs)
+        assert torch.allclose(q.float(), ref_rot(q0, pos + offs, neox), **tol)
+        assert torch.allclose(k.float(), ref_rot(k0, pos + offs, neox), **tol)
+        assert torch.equal(q[:, rot:hs], q0[:, rot:hs])          # beyond rot_dim nothing moves

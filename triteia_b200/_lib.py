@@ -39,6 +39,9 @@ SIGNATURES = {
     "trb_shard_combine": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "trb_unpack_2_4": (_i, [_vp] * 4 + [_i] * 4 + [_vp]),
     "trb_pack_2_4": (_i, [_vp] * 5 + [_i] * 4 + [_vp]),
+    "trb_gelu_quick": (_i, [_vp, _vp, ctypes.c_longlong, _i, _i, _vp]),
+    "trb_silu_and_mul": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),
+    "trb_rotary_embedding": (_i, [_vp] * 5 + [_i, _i, ctypes.c_longlong, ctypes.c_longlong] + [_i] * 6 + [_vp]),
     "trb_row_checksum": (_i, [_vp] * 2 + [_i] * 4 + [_vp]),
     "trb_stack_pass": (_i, [_i] + [_vp] * 7 + [_i] + [_vp] * 7 + [_i] * 3 + [_vp]),
     "trb_bgmv": (_i, [_vp] * 4 + [_i] * 5 + [_f, _i, _i, _vp]),

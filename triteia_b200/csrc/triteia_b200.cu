@@ -14,4 +14,5 @@
 #include "pack.cuh"
 #include "stack.cuh"
 #include "lora.cuh"
+#include "elementwise.cuh"
 #include "no_alloc.cuh"

@@ -131,3 +131,51 @@ def sgmv_cutlass(y, x, w_ptr, s, tmp, layer_idx):
     if err == _lib.ERR_KERN_SHAPE:
         raise RuntimeError(f"No suitable kernel. dtype={x.dtype}")
     _lib.check(err, "sgmv_cutlass")
+
+
+def gelu_quick(out, input):
+    """out = input * sigmoid(1.702 * input) (the pybind module's gelu_quick, ops.cpp:363)."""
+    _check_input(out, "out")
+    _check_input(input, "input")
+    if out.shape != input.shape or out.dtype != input.dtype:
+        raise RuntimeError("gelu_quick: out and input must have the same shape and dtype")
+    _lib.check(lib.trb_gelu_quick(ptr(out), ptr(input), input.numel(), _lib.dtype_tag(input.dtype), dev_of(input),
+                                  stream_of(input)), "gelu_quick")
+
+
+def silu_and_mul(out, input):
+    """out[..., :d] = silu(input[..., :d]) * input[..., d:] (declared at ops.cpp:335)."""
+    _check_input(out, "out")
+    _check_input(input, "input")
+    d = input.size(-1) // 2
+    if input.size(-1) != 2 * d or out.size(-1) != d or out.numel() * 2 != input.numel():
+        raise RuntimeError("silu_and_mul: input must be [..., 2 * d] and out [..., d]")
+    _lib.check(lib.trb_silu_and_mul(ptr(out), ptr(input), input.numel() // (2 * d) if d else 0, d,
+                                    _lib.dtype_tag(input.dtype), dev_of(input), stream_of(input)), "silu_and_mul")
+
+
+def _rotary(positions, query, key, head_size, cos_sin_cache, is_neox, rot_dim, offsets):
+    for t, n in ((positions, "positions"), (query, "query"), (key, "key"), (cos_sin_cache, "cos_sin_cache")):
+        _check_input(t, n)
+    if positions.dtype != torch.int64:
+        raise RuntimeError("positions must be an int64 tensor")
+    num_tokens = query.numel() // query.size(-1)
+    num_heads, num_kv_heads = query.size(-1) // head_size, key.size(-1) // head_size
+    _lib.check(lib.trb_rotary_embedding(ptr(positions), ptr(query), ptr(key), ptr(cos_sin_cache), ptr(offsets),
+                                        num_tokens, rot_dim, query.stride(-2), key.stride(-2), num_heads, num_kv_heads,
+                                        head_size, int(bool(is_neox)), _lib.dtype_tag(query.dtype), dev_of(query),
+                                        stream_of(query)), "rotary_embedding")
+
+
+def rotary_embedding(positions, query, key, head_size, cos_sin_cache, is_neox):
+    """In place; query [..., num_heads * head_size], key [..., num_kv_heads * head_size],
+    cos_sin_cache [max_position, rot_dim] (pos_encoding_kernels.cu:118-160)."""
+    _rotary(positions, query, key, head_size, cos_sin_cache, is_neox, cos_sin_cache.size(1), None)
+
+
+def batched_rotary_embedding(positions, query, key, head_size, cos_sin_cache, is_neox, rot_dim, cos_sin_cache_offsets):
+    """rotary_embedding with a per-token row offset into the cache (pos_encoding_kernels.cu:166-213)."""
+    _check_input(cos_sin_cache_offsets, "cos_sin_cache_offsets")
+    if cos_sin_cache_offsets.dtype != torch.int64:
+        raise RuntimeError("cos_sin_cache_offsets must be an int64 tensor")
+    _rotary(positions, query, key, head_size, cos_sin_cache, is_neox, rot_dim, cos_sin_cache_offsets)
