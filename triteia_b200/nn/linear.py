@@ -36,6 +36,9 @@ class sparse_low_precision_linear(nn.Module):
             raise ValueError("Only `torch.half` weights are supported.")
         if not trans:
             raise ValueError("only the 2:4 (trans=True) layout is supported")
+        # The torch packer, on whatever device the tensors are: where a group of four holds fewer than
+        # two non-zeros its choice of the stored zero follows torch's sort, as the reference's does;
+        # pack_2_4_cuda (one kernel) encodes the same weights but may pick another zero.
         q, s, meta = pack_2_4(weight, scales)
         self.qweight.copy_(q)
         self.scale.copy_(s)

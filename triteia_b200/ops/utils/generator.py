@@ -84,11 +84,13 @@ def fp16_to_sparse(weights, scale, device="cuda"):
 
 
 @torch.no_grad()
-def torch_weight_to_sparse_marlin(weight, scale, tp_size=1, chunk_by="column"):
+def torch_weight_to_sparse_marlin(weight, scale, tp_size=1, chunk_by="column", use_kernel=False):
     """weight [in, out], scale [1, out] -> per tensor-parallel chunk lists (qweights, scales, metas).
 
     "column" splits the output features (each chunk keeps its slice of the scales), "row"
-    splits the input features (every chunk keeps all scales).
+    splits the input features (every chunk keeps all scales).  use_kernel: pack CUDA fp16 chunks
+    with the packer kernel (same weights; a group of four with fewer than two non-zeros may store a
+    different one of its zeros than the torch packer does).
     """
     assert chunk_by in ["column", "row"], "chunk_by must be either 'column' or 'row'"
     assert weight.dim() == 2, "weight must be a 2D tensor"
@@ -102,7 +104,7 @@ def torch_weight_to_sparse_marlin(weight, scale, tp_size=1, chunk_by="column"):
         else:
             lo, hi = i * weight.size(0) // tp_size, (i + 1) * weight.size(0) // tp_size
             w_i, s_i = weight[lo:hi, :], scale
-        if w_i.is_cuda and w_i.dtype == torch.float16 and s_i.dtype == torch.float16:
+        if use_kernel and w_i.is_cuda and w_i.dtype == torch.float16 and s_i.dtype == torch.float16:
             q, s, meta = pack_2_4_cuda(w_i.contiguous(), s_i.contiguous())     # one kernel instead of ~20 torch ops
         else:
             q, s, meta = pack_2_4(w_i.contiguous(), s_i.contiguous())

@@ -125,9 +125,11 @@ def pack_2_4(weight_kn: torch.Tensor, scales: torch.Tensor):
 
 def pack_2_4_cuda(weight_kn: torch.Tensor, scales: torch.Tensor):
     """pack_2_4 as one CUDA kernel (trb_pack_2_4): fp16 weight [K, N] and logical scales fp16 [G, N]
-    on a GPU -> (qweight, stored scales, meta).  Identical to pack_2_4 for weights that are already
-    2:4 sparse along K (otherwise equal magnitudes inside a group of four may be pruned differently:
-    torch's argsort leaves the order of ties open, the kernel keeps the higher index)."""
+    on a GPU -> (qweight, stored scales, meta).  Identical to pack_2_4 when every group of four K
+    positions holds exactly two non-zeros of distinct or equal magnitude; with ties between a kept
+    and a pruned element (fewer than two non-zeros, or more than two equal magnitudes) torch's
+    argsort leaves the choice open and the kernel keeps the higher index: the packed tensors then
+    decode to the same weights but need not be the same bits."""
     from ... import _lib
 
     if not weight_kn.is_cuda or weight_kn.dtype != torch.float16 or scales.dtype != torch.float16:
