@@ -117,3 +117,45 @@ def dequantize(qweight, meta, s):
     g = sl.shape[0]
     per_row = np.repeat(sl, k // g, axis=0)  # [K, N]
     return (lev.astype(np.float16) * per_row).astype(np.float16)
+
+
+def column_blocks(qweight, meta, s, blk0, nblk):
+    """The packed tensors of output columns [64 * blk0, 64 * (blk0 + nblk)) of one delta.
+
+    A 64-column block is self-contained in every packed tensor: 128 consecutive words of each
+    qweight row, rows 64b..64b+63 of the metadata (physically [K/32][N][2] int16, reordered only
+    inside 64-row groups), 64 consecutive scale columns (the stored order permutes inside 8-column
+    blocks).  The result decodes with `dequantize` to the same values as columns 64*blk0.. of the
+    whole delta, at 1/(N/64/nblk) of the cost: full-size parity checks use it on sampled rows.
+    Takes numpy arrays or tensors (only slicing and reshape are used before the copy to numpy).
+    """
+    q = qweight[:, 128 * blk0:128 * (blk0 + nblk)]
+    n, kc = meta.shape
+    m = meta.reshape(kc // 2, n, 2)[:, 64 * blk0:64 * (blk0 + nblk), :].reshape(64 * nblk, kc)
+    sc = s[:, 64 * blk0:64 * (blk0 + nblk)]
+    return to_numpy(q), to_numpy(m), to_numpy(sc)
+
+
+def to_numpy(a):
+    """numpy view or copy of an array-like; device tensors (anything with .detach) come through the host."""
+    if hasattr(a, "detach"):
+        a = a.detach().cpu().numpy()
+    return np.ascontiguousarray(a)
+
+
+VALID_META_NIBBLES = np.array([0b0100, 0b1000, 0b1100, 0b1001, 0b1101, 0b1110], dtype=np.uint16)
+
+
+def random_packed(k, n, groupsize=-1, seed=0, scale_lo=0.001, scale_hi=0.01):
+    """A valid packed delta drawn directly in the wire format (numpy only): every code word is
+    valid as it is, a metadata nibble is valid when its first position (low 2 bits) is below its
+    second (high 2 bits), and the physical metadata order is a permutation, so any arrangement of
+    valid nibbles decodes.  Levels come out uniform in [-8, 7].  Used by the CPU timing legs, which
+    must not load the product library."""
+    rng = np.random.default_rng(seed)
+    q = rng.integers(0, 1 << 32, size=(k // 32, 2 * n), dtype=np.uint64).astype(np.uint32).view(np.int32)
+    nib = VALID_META_NIBBLES[rng.integers(0, 6, size=(n, k // 16, 4))]
+    m = (nib[..., 0] | (nib[..., 1] << 4) | (nib[..., 2] << 8) | (nib[..., 3] << 12)).astype(np.uint16).view(np.int16)
+    g = 1 if groupsize == -1 else k // groupsize
+    s = rng.uniform(scale_lo, scale_hi, size=(g, n)).astype(np.float16)
+    return q, m, s

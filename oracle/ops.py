@@ -78,6 +78,40 @@ def sbmm(qweights, xs, metas, ss, indices, base_weight=None):
     return y
 
 
+def sbmm_rows(qweights, xs, metas, ss, indices, rows, blk0=0, nblk=2, base_weight=None):
+    """`sbmm` restricted to the token rows `rows` and output columns [64*blk0, 64*(blk0+nblk)):
+    returns fp32 [len(rows), 64*nblk].  Full-size checks decode only these column blocks."""
+    from .delta_format import column_blocks, to_numpy
+
+    rows = np.asarray(rows)
+    xs32 = _f32(to_numpy(xs)[rows])
+    idx = to_numpy(indices)[rows]
+    c0, c1 = 64 * blk0, 64 * (blk0 + nblk)
+    y = (xs32 @ _f32(to_numpy(base_weight[c0:c1])).T if base_weight is not None
+         else np.zeros((len(rows), c1 - c0), np.float32))
+    for d in np.unique(idx):
+        if d < 0:
+            continue
+        w = _f32(dequantize(*column_blocks(qweights[d], metas[d], ss[d], blk0, nblk)))
+        m = idx == d
+        y[m] += xs32[m] @ w
+    return y
+
+
+def sbmm_dense_f32(weights, x, rows_of):
+    """The reference's torch check path on dequantised weights (sbmm_16bit_forloop,
+    triteia/python/ops/matmul/sbmm.py:7-23) in fp32 on host tensors: for every delta d,
+    y[rows_of[d]] += x[rows_of[d]] @ weights[d].  torch tensors in, torch tensor out; this is what
+    the CPU timing legs of the benchmark run (all host threads, through torch.matmul)."""
+    import torch
+
+    y = torch.zeros(x.shape[0], weights[0].shape[1])
+    for d, r in enumerate(rows_of):
+        if len(r):
+            y[r] += x[r] @ weights[d]
+    return y
+
+
 def lora(weights_a, weights_b, x, indices, base_weight=None, scale=1.0):
     """y[t] = x[t] @ base.T + scale * (x[t] @ A[idx[t]]) @ B[idx[t]]; A [M,H1,r], B [M,r,H2]."""
     x32 = _f32(x)

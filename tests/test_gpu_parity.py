@@ -717,3 +717,51 @@ def test_elementwise_neighbours(cuda, dtype):
         assert torch.allclose(q.float(), ref_rot(q0, pos + offs, neox), **tol)
         assert torch.allclose(k.float(), ref_rot(k0, pos + offs, neox), **tol)
         assert torch.equal(q[:, rot:hs], q0[:, rot:hs])          # beyond rot_dim nothing moves
+
+
+# ------------------------------------------------------------------ overlapping calls, full-size oracle comparisons
+def _sampled_rows(idx_np, per_id=1, seed=0):
+    rng = np.random.default_rng(seed)
+    rows = []
+    for d in np.unique(idx_np):
+        cand = np.flatnonzero(idx_np == d)
+        rows.extend(int(r) for r in rng.choice(cand, size=min(per_id, len(cand)), replace=False))
+    return sorted(rows)
+
+
+def test_sbmm_two_streams_do_not_share_scratch(cuda):
+    """Two different batches in flight on two streams: the op keeps its working memory per stream
+    (the reference allocates its workspace per call), so both results must match the oracle."""
+    ops = _ops()
+    qs, metas, ss, xa, ia, _ = sbmm_inputs(128, 16, 1024, 2048, 128, seed=41, sort=False)
+    _, _, _, xb, ib, _ = sbmm_inputs(128, 16, 1024, 2048, 128, seed=42, sort=False)
+    ib = torch.roll(ib, 7)
+    sa, sb = torch.cuda.Stream(), torch.cuda.Stream()
+    torch.cuda.synchronize()
+    outs = {}
+    for rep in range(20):                      # interleaved launches, no synchronisation in between
+        with torch.cuda.stream(sa):
+            outs["a"] = ops.sbmm_4bit_2_4_native(qs, xa, metas, ss, ia)
+        with torch.cuda.stream(sb):
+            outs["b"] = ops.sbmm_4bit_2_4_native(qs, xb, metas, ss, ib)
+    torch.cuda.synchronize()
+    check(outs["a"], sbmm_ref(qs, metas, ss, xa, ia, None))
+    check(outs["b"], sbmm_ref(qs, metas, ss, xb, ib, None))
+    assert _lib().device_status(0) == 0
+
+
+def test_sbmm_decode_full_size_against_oracle(cuda):
+    """The headline configuration at its full size (64 deltas, 128 tokens, group 128, unsorted, tail K
+    split active): one sampled row of every distinct id x 128 columns against the oracle, and rows
+    with id -1 exactly zero."""
+    ops = _ops()
+    qs, metas, ss, x, idx, _ = sbmm_inputs(128, 64, 4096, 4096, 128, seed=23, sort=False)
+    y = ops.sbmm_4bit_2_4_native(qs, x, metas, ss, idx)
+    idx_np = idx.cpu().numpy()
+    rows = _sampled_rows(idx_np, per_id=1, seed=1)
+    for blk0 in (0, 31, 62):
+        ref = oracle.sbmm_rows(qs, x, metas, ss, idx_np, rows, blk0=blk0, nblk=2)
+        got = y[rows][:, 64 * blk0:64 * blk0 + 128].float().cpu().numpy()
+        err = oracle.row_rel_err(got, ref)
+        assert err.max() <= ROW_TOL, f"columns {64 * blk0}: row rel err {err.max():.4g}"
+    assert torch.all(y[idx == -1] == 0)

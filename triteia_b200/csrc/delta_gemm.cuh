@@ -366,7 +366,7 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             const int pr = r / a.chunk_rows, pq = r - pr * a.chunk_rows;
             const int* ids = reinterpret_cast<const int*>(a.xchg + ((long long)pr * a.chunk_rows + a.chunk_rows - 1) * a.xchg_row_bytes);
             const int trow = ids[a.chunk_rows + pq];
-            r = (trow >= 0 && trow < (1 << 20)) ? ((pr << 20) | trow) : -1;
+            r = (trow >= 0 && trow < a.chunk_rows - 1) ? ((pr << 20) | trow) : -1;   // a peer's output has chunk_rows - 1 rows
           }
         }
         orow[nb][h] = r;

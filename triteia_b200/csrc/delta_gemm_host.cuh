@@ -439,6 +439,8 @@ extern "C" int trb_shard_compute(const void* recv_buf, const void* qweights, con
                                  size_t scratch_bytes, int dev, void* stream_v) {
   (void)my_rank;
   if (world < 1 || cap < 1 || !recv_buf || (!y_work && !peer_out_ptrs)) return TRB_ERR_BAD_ARG;
+  // The id row of a chunk holds cap ids and the row count (plain form), plus cap token rows (peer form).
+  if ((long long)(cap + 1) * 4 > (long long)prob_k * 2) return TRB_ERR_PROB_SHAPE;
   if (peer_out_ptrs && ((long long)(2 * cap + 2) * 4 > (long long)prob_k * 2 || cap >= (1 << 20))) return TRB_ERR_PROB_SHAPE;
   const long long rows = (long long)world * (cap + 1);
   if (rows > 65536) return TRB_ERR_PROB_SHAPE;
