@@ -253,6 +253,29 @@ int trb_lora_indexed(void* y, const void* x, const void* wa, const void* wb, con
                      int index_is_64bit, int batch, int h1, int h2, int rank, int num_adapters,
                      float scale, int dtype, int dev, void* stream);
 
+/* Base product with the LoRA expand in the same accumulator:
+ *   y[T, N] (+)= x[T, K] @ base_weight[N, K]^T  +  lora_v[T, lora_k] @ lora_b[lora_k, N]
+ * on the tcgen05 tensor cores (fp32 accumulation in tensor memory, y written once).  Stands for the
+ * library GEMM `x @ base_weight.t()` that opens every operator of the reference
+ * (triteia/python/ops/matmul/sbmm.py:90-93, ldmm.py:72-76, lora.py:5-9) and, with lora_k > 0, for
+ * the expand half of its BGMV pair (triteia/csrc/ops/bgmv_impl.cuh:141-183): lora_b is the
+ * adapters' [M, r, N] tensor seen as [M * r, N] and lora_v comes from trb_lora_shrink_rows.
+ * lora_k = 0 (lora_v, lora_b NULL): base product only.  accumulate != 0: y += instead of y =.
+ * K % 64 == 0, N % 8 == 0, lora_k % 8 == 0; dtype TRB_F16 or TRB_BF16 for all tensors. */
+int trb_base_gemm(const void* x, const void* base_weight, void* y, int num_tokens, int prob_m, int prob_k,
+                  const void* lora_v, const void* lora_b, int lora_k, int accumulate, int dtype, int dev,
+                  void* stream);
+
+/* Shrink half of the indexed LoRA, written as the operand of trb_base_gemm: row b of v[B, v_cols]
+ * (fp16) becomes zero except columns [id * rank, (id + 1) * rank) = scale * x[b] @ A[id], with
+ * A [M, h1, rank] fp16 and id = indices[b] (int32, or int64 when index_is_64bit); ids outside
+ * [0, num_adapters) leave a zero row.  v_cols >= num_adapters * rank, v_cols % 8 == 0.
+ * Stands for the shrink launch of add_lora_bgmv (triteia/python/capi/punica.py:61-66,
+ * triteia/csrc/ops/bgmv_impl.cuh:15-137). */
+int trb_lora_shrink_rows(void* v, const void* x, const void* wa, const void* indices, int index_is_64bit,
+                         int batch, int h1, int rank, int num_adapters, int v_cols, float scale, int dev,
+                         void* stream);
+
 /* SGMV: y[s[i]:s[i+1]] += x[s[i]:s[i+1]] @ w[i][layer_idx], w[i] -> [L, d_in, d_out] row-major,
  * w: device array of num_problems device pointers, s int32 [num_problems + 1].
  * Replaces sgmv<T> (csrc/ops/sgmv.h:6-9, csrc/ops/sgmv.cuh:61-174).  `tmp` is accepted for call

@@ -765,3 +765,42 @@ def test_sbmm_decode_full_size_against_oracle(cuda):
         err = oracle.row_rel_err(got, ref)
         assert err.max() <= ROW_TOL, f"columns {64 * blk0}: row rel err {err.max():.4g}"
     assert torch.all(y[idx == -1] == 0)
+
+
+# ------------------------------------------------------------------ base product on the library's own kernel
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("T,K,N", [(1, 128, 256), (40, 256, 512), (256, 4096, 1024), (300, 512, 11008), (700, 1024, 384)])
+def test_base_gemm(cuda, T, K, N, dtype):
+    """y = x @ W^T against an fp32 torch statement of the same product (the reference calls torch.matmul
+    here: sbmm.py:90-93); fp16 / bf16 rounding of the output bounds the error."""
+    from triteia_b200.ops.matmul._base import base_gemm
+    g = torch.Generator(cuda).manual_seed(T + K + N)
+    x = torch.randn(T, K, device=cuda, generator=g).to(dtype)
+    w = (torch.randn(N, K, device=cuda, generator=g) * 0.05).to(dtype)
+    y = base_gemm(x, w)
+    ref = (x.float() @ w.float().t()).cpu().numpy()
+    err = oracle.row_rel_err(y.float().cpu().numpy(), ref)
+    assert err.max() <= (ROW_TOL if dtype == torch.float16 else 2e-2), f"row rel err {err.max():.4g}"
+    y2 = base_gemm(x, w, out=y.clone(), accumulate=True)
+    err2 = oracle.row_rel_err(y2.float().cpu().numpy(), 2 * ref)
+    assert err2.max() <= 2e-2
+    assert _lib().device_status(0) == 0
+
+
+@pytest.mark.parametrize("M,rank", [(3, 8), (5, 16), (32, 16), (4, 64)])
+def test_base_gemm_with_lora_expand(cuda, M, rank):
+    """Base product and LoRA expand in one accumulator: shrink rows + trb_base_gemm against the oracle's
+    lora statement (lora_forloop semantics, lora.py:4-20), ids outside [0, M) get the base only."""
+    from triteia_b200.ops.matmul._base import base_gemm, lora_shrink_rows
+    T, K, N = 100, 512, 768
+    A, B, x, idx = lora_inputs(T, M, K, N, rank, seed=3 * M + rank)
+    idx[::7] = -1
+    idx[3::11] = M + 2                      # an id of the delta range: no adapter
+    w = (torch.randn(N, K, device=cuda, generator=torch.Generator(cuda).manual_seed(5)) * 0.05).half()
+    v = lora_shrink_rows(x, A, idx)
+    y = base_gemm(x, w, lora_v=v, lora_b=B.view(M * rank, N))
+    idx_np = idx.cpu().numpy().copy()
+    idx_np[idx_np >= M] = -1
+    ref = oracle.lora(A.cpu().numpy(), B.cpu().numpy(), x.cpu().numpy(), idx_np, base_weight=w.cpu().numpy())
+    check(y, ref, mean_tol=None)
+    assert _lib().device_status(0) == 0

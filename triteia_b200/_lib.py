@@ -47,6 +47,8 @@ SIGNATURES = {
     "trb_bgmv": (_i, [_vp] * 4 + [_i] * 5 + [_f, _i, _i, _vp]),
     "trb_lora_bgmv_fused": (_i, [_vp] * 5 + [_i] * 6 + [_f, _i, _i, _vp]),
     "trb_lora_indexed": (_i, [_vp] * 5 + [_i] * 6 + [_f, _i, _i, _vp]),
+    "trb_base_gemm": (_i, [_vp] * 3 + [_i] * 3 + [_vp, _vp] + [_i] * 4 + [_vp]),
+    "trb_lora_shrink_rows": (_i, [_vp] * 4 + [_i] * 6 + [_f, _i, _vp]),
     "trb_sgmv_tmp_size": (_sz, [_i]),
     "trb_sgmv": (_i, [_vp] * 5 + [_i] * 6 + [_vp]),
 }

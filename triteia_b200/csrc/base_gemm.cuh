@@ -1,0 +1,441 @@
+// Dense fp16 base GEMM of the path, y[T, N] (+)= x[T, K] * W_base[N, K]^T, with the LoRA expand folded
+// into the same accumulator: y += V[T, Kv] * B[Kv, N], where V holds every token's rank-r shrink
+// result in the column block of its adapter (zero elsewhere) and B is the adapters' expand matrices
+// stacked along K (the natural [M, r, N] tensor seen as [M * r, N]).
+//
+// The reference runs the base product as torch.matmul (a library GEMM) and then adds the LoRA and
+// delta parts in separate passes over y (triteia/python/ops/matmul/ldmm.py:72-76, 86-107;
+// sbmm.py:90-93; lora.py:5-9).  Here one kernel on the fifth-generation tensor cores produces
+// base + LoRA in one TMEM accumulator and writes y once:
+//   tcgen05.mma.kind::f16, D[M = 128 output features, N = token tile] in tensor memory (two
+//   accumulators, so the epilogue of one work item overlaps the MMAs of the next);
+//   A operand = W_base rows [128 x 64 K] as they lie in memory (K-major, TMA with 128-byte swizzle),
+//   for the LoRA chunks = B rows [64 Kv x 128 features] as they lie in memory (MN-major operand);
+//   B operand = x (or V) rows [token tile x 64 K], K-major;
+//   warp 0: TMA producer (one thread), warp 1: MMA issuer (one thread) and TMEM owner,
+//   warps 2-5: epilogue (tcgen05.ld, fp16 convert, 32 x 32 transposes through shared memory,
+//   16-byte stores).  Every wait is bounded.
+#pragma once
+
+#include "tc_common.cuh"
+
+namespace trb {
+
+struct BaseCfg {
+  static constexpr int KC = 64;             // K per pipeline stage (one 128-byte swizzle atom of fp16)
+  static constexpr int STAGES = 4;
+  static constexpr int EPI_WARPS = 4;
+  static constexpr int THREADS = (2 + EPI_WARPS) * 32;
+  static constexpr int MAX_TT = 256;        // largest token tile (UMMA N)
+  static constexpr int A_BYTES = 128 * KC * 2;           // 16 KiB
+  static constexpr int B_BYTES = MAX_TT * KC * 2;        // 32 KiB (a smaller token tile uses the front)
+  static constexpr int A_OFF = 0;
+  static constexpr int B_OFF = A_BYTES;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;  // 48 KiB, a multiple of 1 KiB
+  static constexpr int XPOSE_OFF = STAGES * STAGE_BYTES;                  // [EPI_WARPS][32 tokens][32 features] halves
+  static constexpr int BAR_OFF = XPOSE_OFF + EPI_WARPS * 2048;
+  static constexpr int NUM_BARS = 2 * STAGES + 4;
+  static constexpr int SMEM_BYTES = BAR_OFF + NUM_BARS * 8 + 16;
+  static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;
+  static constexpr uint32_t TMEM_COLS = 512;
+};
+static_assert(BaseCfg::STAGE_BYTES % 1024 == 0, "stages keep the 1 KiB alignment of the swizzle atoms");
+
+struct BaseArgs {
+  int T, N, K;        // tokens, output features, input features (K % 64 == 0)
+  int kv;             // K extent of the LoRA part (0: none); columns of V and rows of B
+  int tt;             // token tile: 32, 64, 128 or 256
+  __half* y;          // fp16 or bf16 by `bf16`
+  int accumulate;     // y += result instead of y = result
+  int bf16;           // operands and output are bfloat16
+};
+
+// MN-major operand, 128-byte swizzle: a row of the tile is one K index and holds 64 consecutive
+// M (feature) elements = 128 bytes; 8 K rows form a 1 KiB group (stride offset), the next 64
+// features start `lbo` bytes further (leading offset).
+__device__ __forceinline__ uint64_t tc_smem_desc_mn(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// kind::f16 with a run-time instruction descriptor (token tile and operand majorness vary).
+__device__ __forceinline__ void tc_mma_f16_idesc(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(BaseCfg::THREADS, 1)
+base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
+                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_b,
+                 const BaseArgs a) {
+  using Cfg = BaseCfg;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::BAR_OFF);   // TMA data of a stage landed
+  uint64_t* empty_bar = full_bar + STAGES;                                 // MMAs of a stage retired
+  uint64_t* accready_bar = empty_bar + STAGES;                             // [2] accumulator complete
+  uint64_t* accfree_bar = accready_bar + 2;                                // [2] accumulator drained
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accfree_bar + 2);
+  volatile int* dead = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&accready_bar[b], 1);
+      mbar_init(&accfree_bar[b], Cfg::EPI_WARPS);
+    }
+    *dead = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(Cfg::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  pdl_launch_dependents();
+  pdl_wait();   // x and V may come from the kernels launched just before
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int n_stripes = (a.N + 127) / 128;
+  const int n_tiles = (a.T + a.tt - 1) / a.tt;
+  const int n_items = n_tiles * n_stripes;            // item = tile * n_stripes + stripe
+  const int kw = a.K / Cfg::KC;                        // chunks of the base product
+  const int kl = (a.kv + Cfg::KC - 1) / Cfg::KC;       // chunks of the LoRA expand
+  const int k_chunks = kw + kl;
+  const uint32_t smem_base = smem_u32(smem);
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      prefetch_tmap(&tm_x);
+      prefetch_tmap(&tm_w);
+      if (kl > 0) {
+        prefetch_tmap(&tm_v);
+        prefetch_tmap(&tm_b);
+      }
+      const uint64_t pol_w = policy_evict_first();
+      const uint64_t pol_x = policy_evict_last();
+      const uint32_t stage_tx = Cfg::A_BYTES + a.tt * Cfg::KC * 2;
+      int st = 0;
+      uint32_t phase = 0;
+      for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+        const int tile = item / n_stripes, stripe = item - tile * n_stripes;
+        const int row0 = tile * a.tt, col0 = stripe * 128;
+        for (int kc = 0; kc < k_chunks; ++kc) {
+          mbar_wait(&empty_bar[st], phase ^ 1, dead);
+          uint8_t* sbase = smem + st * Cfg::STAGE_BYTES;
+          mbar_arrive_expect_tx(&full_bar[st], stage_tx);
+          if (kc < kw) {
+            tma_load_2d_hint(sbase + Cfg::A_OFF, &tm_w, kc * Cfg::KC, col0, &full_bar[st], pol_w);
+            tma_load_2d_hint(sbase + Cfg::B_OFF, &tm_x, kc * Cfg::KC, row0, &full_bar[st], pol_x);
+          } else {
+            const int j = kc - kw;
+            // two boxes of [64 K rows x 64 features]: features col0.. and col0 + 64..
+            tma_load_2d_hint(sbase + Cfg::A_OFF, &tm_b, col0, j * Cfg::KC, &full_bar[st], pol_x);
+            tma_load_2d_hint(sbase + Cfg::A_OFF + 8192, &tm_b, col0 + 64, j * Cfg::KC, &full_bar[st], pol_x);
+            tma_load_2d_hint(sbase + Cfg::B_OFF, &tm_v, j * Cfg::KC, row0, &full_bar[st], pol_x);
+          }
+          if (++st == STAGES) { st = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      // D fp32, A and B fp16; N = token tile, M = 128; bit 15: A is MN-major (the LoRA chunks)
+      const uint32_t fmt = a.bf16 ? 1u : 0u;           // operand format field: 0 = fp16, 1 = bf16
+      const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (((uint32_t)a.tt >> 3) << 17) | ((128u >> 4) << 24);
+      const uint32_t idesc_mn = idesc | (1u << 15);
+      int st = 0;
+      uint32_t phase = 0;
+      uint32_t use[2] = {0, 0};
+      int local = 0;
+      for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+        const int buf = local & 1;
+        mbar_wait(&accfree_bar[buf], (use[buf] & 1) ^ 1, dead);
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * Cfg::MAX_TT;
+        for (int kc = 0; kc < k_chunks; ++kc) {
+          mbar_wait(&full_bar[st], phase, dead);
+          tc_fence_after();
+          const uint32_t sb = smem_base + st * Cfg::STAGE_BYTES;
+          const uint64_t bdesc = tc_smem_desc(sb + Cfg::B_OFF);
+          if (kc < kw) {
+            const uint64_t adesc = tc_smem_desc(sb + Cfg::A_OFF);
+#pragma unroll
+            for (int k = 0; k < Cfg::KC / 16; ++k)   // +32 bytes of K per instruction = +2 in the address field
+              tc_mma_f16_idesc(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kc > 0 || k > 0) ? 1u : 0u);
+          } else {
+#pragma unroll
+            for (int k = 0; k < Cfg::KC / 16; ++k) {  // 16 K rows of 128 bytes per instruction
+              const uint64_t adesc = tc_smem_desc_mn(sb + Cfg::A_OFF + k * 2048, 8192, 1024);   // 64-feature halves 8 KiB apart, 8-row K groups 1 KiB apart
+              tc_mma_f16_idesc(d_tmem, adesc, bdesc + 2 * k, idesc_mn, (kc > 0 || k > 0) ? 1u : 0u);
+            }
+          }
+          tc_commit(&empty_bar[st]);
+          if (++st == STAGES) { st = 0; phase ^= 1; }
+        }
+        tc_commit(&accready_bar[buf]);
+        ++use[buf];
+        ++local;
+      }
+    }
+  } else {
+    // ------------------------------ epilogue warps ------------------------------
+    const int ew = warp - 2;
+    const int quad = warp & 3;                        // TMEM lanes this warp may touch: 32 * quad .. + 31
+    uint32_t use[2] = {0, 0};
+    int local = 0;
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+      const int tile = item / n_stripes, stripe = item - tile * n_stripes;
+      const int row0 = tile * a.tt, col0 = stripe * 128;
+      const int valid = min(a.tt, a.T - row0);
+      const int buf = local & 1;
+      if (ew == 0) {                                  // one warp polls, the others park on the hardware barrier
+        uint32_t polls = 0;
+        while (!mbar_try_wait(&accready_bar[buf], use[buf] & 1)) {
+          __nanosleep(64);
+          if ((polls & 15u) == 0 && *dead) break;
+          if (++polls > kMaxPolls) {
+            *dead = 1;
+            atomicExch(&g_device_status, TRB_ERR_TIMEOUT);
+            break;
+          }
+        }
+      }
+      named_bar_sync(4, Cfg::EPI_WARPS * 32);
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * Cfg::MAX_TT;
+      const int nbatch = (valid + 31) >> 5;
+      for (int b = 0; b < nbatch; ++b) {
+        uint32_t v[32];
+        tc_ld32(taddr + b * 32, v);
+        tc_wait_ld();
+        if (b == nbatch - 1) {                        // the accumulator is in registers: hand the buffer back
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&accfree_bar[buf]);
+        }
+        __half* patch = reinterpret_cast<__half*>(smem + Cfg::XPOSE_OFF + ew * 2048);
+        if (a.bf16) {
+          __nv_bfloat16* pb = reinterpret_cast<__nv_bfloat16*>(patch);
+#pragma unroll
+          for (int c = 0; c < 32; ++c) pb[c * 32 + lane] = __float2bfloat16_rn(__uint_as_float(v[c]));
+        } else {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) patch[c * 32 + lane] = __float2half_rn(__uint_as_float(v[c]));
+        }
+        __syncwarp();
+        const int f8 = (lane & 3) * 8;                // feature offset of this lane's 16-byte piece
+        const int nb = col0 + quad * 32 + f8;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int c = i * 8 + (lane >> 2);          // token of the batch
+          const int t = b * 32 + c;
+          if (t < valid && nb < a.N) {
+            uint4 o = *reinterpret_cast<const uint4*>(patch + c * 32 + f8);
+            uint4* yp = reinterpret_cast<uint4*>(a.y + (size_t)(row0 + t) * a.N + nb);
+            if (a.accumulate) {
+              const uint4 old = *yp;
+              if (a.bf16) {
+                __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+                const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 p = __bfloat1622float2(oh[e]), q = __bfloat1622float2(ph[e]);
+                  oh[e] = __floats2bfloat162_rn(p.x + q.x, p.y + q.y);
+                }
+              } else {
+                __half2* oh = reinterpret_cast<__half2*>(&o);
+                const __half2* ph = reinterpret_cast<const __half2*>(&old);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 p = __half22float2(oh[e]), q = __half22float2(ph[e]);
+                  oh[e] = __floats2half2_rn(p.x + q.x, p.y + q.y);
+                }
+              }
+            }
+            *yp = o;
+          }
+        }
+        __syncwarp();
+      }
+      ++use[buf];
+      ++local;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::TMEM_COLS) : "memory");
+  }
+}
+
+// V[t, :] = 0 except columns [id * rank, (id + 1) * rank) = scale * x[t] @ A[id], for id = indices[t]
+// in [0, num_adapters); the row stays zero for any other id.  One CTA per token, A [M, h1, rank] in
+// its natural layout.  This is the shrink half of the reference's BGMV pair
+// (triteia/csrc/ops/bgmv_impl.cuh:15-137) writing straight into the operand of the expand above.
+template <class IdxT>
+__global__ void __launch_bounds__(256) lora_shrink_rows_kernel(__half* __restrict__ V, const __half* __restrict__ X,
+                                                               const __half* __restrict__ A,
+                                                               const IdxT* __restrict__ indices, int h1, int rank,
+                                                               int num_adapters, int v_cols, float scale) {
+  __shared__ float part[8][64];
+  const int b = blockIdx.x;
+  pdl_launch_dependents();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  uint4* vrow = reinterpret_cast<uint4*>(V + (int64_t)b * v_cols);
+  const long long idx = (long long)indices[b];
+  const bool has = idx >= 0 && idx < num_adapters;
+  const int lo8 = has ? (int)idx * rank / 8 : -1, hi8 = has ? lo8 + rank / 8 : -1;
+  for (int i = tid; i < v_cols / 8; i += 256)
+    if (i < lo8 || i >= hi8) vrow[i] = make_uint4(0, 0, 0, 0);
+  if (!has) return;
+  const __half* am = A + idx * (int64_t)h1 * rank;
+  const __half* x = X + (int64_t)b * h1;
+  float acc[64];
+#pragma unroll
+  for (int j = 0; j < 64; ++j) acc[j] = 0.f;
+  const int rv = rank / 8;
+  for (int k = tid; k < h1; k += 256) {
+    const float xk = __half2float(x[k]);
+    const uint4* row = reinterpret_cast<const uint4*>(am + (int64_t)k * rank);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (i < rv) {
+        const uint4 wv = row[i];
+        const uint32_t* pw = reinterpret_cast<const uint32_t*>(&wv);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&pw[e]));
+          acc[i * 8 + 2 * e] = fmaf(xk, f.x, acc[i * 8 + 2 * e]);
+          acc[i * 8 + 2 * e + 1] = fmaf(xk, f.y, acc[i * 8 + 2 * e + 1]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 64; ++j) {
+    if (j < rank) {
+      const float s = warp_sum(acc[j]);
+      if (lane == 0) part[warp][j] = s;
+    }
+  }
+  __syncthreads();
+  if (tid < rank) {
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) s += part[w][tid];
+    V[(int64_t)b * v_cols + idx * rank + tid] = __float2half_rn(s * scale);
+  }
+}
+
+static_assert(BaseCfg::SMEM_ALLOC <= 232448, "shared memory budget of one sm_100 CTA");
+
+static int base_gemm_launch(const void* x, const void* w, void* y, int T, int N, int K, const void* v, const void* b,
+                            int kv, int accumulate, int bf16, int dev, cudaStream_t stream) {
+  BaseArgs a{};
+  a.T = T; a.N = N; a.K = K; a.kv = kv;
+  a.tt = T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+  a.y = (__half*)y;
+  a.accumulate = accumulate;
+  a.bf16 = bf16;
+  const CUtensorMapDataType dt = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUtensorMap tx, tw, tv, tb;
+  if (!make_map_2d(&tx, dt, 2, x, (uint64_t)T, (uint64_t)K, a.tt, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return TRB_ERR_CUDA;
+  if (!make_map_2d(&tw, dt, 2, w, (uint64_t)N, (uint64_t)K, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return TRB_ERR_CUDA;
+  if (kv > 0) {
+    if (!make_map_2d(&tv, dt, 2, v, (uint64_t)T, (uint64_t)kv, a.tt, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return TRB_ERR_CUDA;
+    if (!make_map_2d(&tb, dt, 2, b, (uint64_t)kv, (uint64_t)N, 64, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return TRB_ERR_CUDA;
+  } else {
+    tv = tx;   // never dereferenced
+    tb = tw;
+  }
+  static std::mutex mu;
+  static bool attr_set[64] = {};
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+      if (cudaFuncSetAttribute(base_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BaseCfg::SMEM_ALLOC) !=
+          cudaSuccess)
+        return TRB_ERR_CUDA;
+      attr_set[dev] = true;
+    }
+  }
+  const long long items = (long long)((T + a.tt - 1) / a.tt) * ((N + 127) / 128);
+  int grid = sm_count(dev);
+  if (items < grid) grid = (int)items;
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3(grid);
+  lc.blockDim = dim3(BaseCfg::THREADS);
+  lc.dynamicSmemBytes = BaseCfg::SMEM_ALLOC;
+  lc.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // the kernel waits (pdl_wait) before it reads
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = at;
+  lc.numAttrs = 1;
+  return cudaLaunchKernelEx(&lc, base_gemm_kernel, tx, tw, tv, tb, a) == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
+}
+
+}  // namespace trb
+
+extern "C" int trb_base_gemm(const void* x, const void* base_weight, void* y, int num_tokens, int prob_m, int prob_k,
+                             const void* lora_v, const void* lora_b, int lora_k, int accumulate, int dtype, int dev,
+                             void* stream) {
+  using namespace trb;
+  if (num_tokens < 0 || prob_m < 0 || prob_k < 0 || lora_k < 0) return TRB_ERR_BAD_ARG;
+  if (num_tokens == 0 || prob_m == 0) return TRB_OK;
+  if (!x || !base_weight || !y || (lora_k > 0 && (!lora_v || !lora_b))) return TRB_ERR_BAD_ARG;
+  if (prob_k == 0 || prob_k % 64 != 0 || prob_m % 8 != 0 || lora_k % 8 != 0) return TRB_ERR_PROB_SHAPE;
+  if (dtype != TRB_F16 && dtype != TRB_BF16) return TRB_ERR_KERN_SHAPE;
+  const uintptr_t bits = (uintptr_t)x | (uintptr_t)base_weight | (uintptr_t)y | (uintptr_t)lora_v | (uintptr_t)lora_b;
+  if (bits & 15) return TRB_ERR_BAD_ARG;
+  if (cudaSetDevice(dev) != cudaSuccess) return TRB_ERR_CUDA;
+  return base_gemm_launch(x, base_weight, y, num_tokens, prob_m, prob_k, lora_v, lora_b, lora_k, accumulate ? 1 : 0,
+                          dtype == TRB_BF16, dev, (cudaStream_t)stream);
+}
+
+extern "C" int trb_lora_shrink_rows(void* v, const void* x, const void* wa, const void* indices, int index_is_64bit,
+                                    int batch, int h1, int rank, int num_adapters, int v_cols, float scale, int dev,
+                                    void* stream) {
+  using namespace trb;
+  if (batch == 0) return TRB_OK;
+  if (batch < 0 || num_adapters <= 0 || !v || !x || !wa || !indices) return TRB_ERR_BAD_ARG;
+  if (rank <= 0 || rank > 64 || rank % 8 != 0 || h1 <= 0 || v_cols % 8 != 0 || (long long)num_adapters * rank > v_cols)
+    return TRB_ERR_KERN_SHAPE;
+  if (((uintptr_t)v | (uintptr_t)wa) & 15) return TRB_ERR_BAD_ARG;
+  if (cudaSetDevice(dev) != cudaSuccess) return TRB_ERR_CUDA;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (index_is_64bit)
+    lora_shrink_rows_kernel<int64_t><<<batch, 256, 0, st>>>((__half*)v, (const __half*)x, (const __half*)wa,
+                                                            (const int64_t*)indices, h1, rank, num_adapters, v_cols, scale);
+  else
+    lora_shrink_rows_kernel<int32_t><<<batch, 256, 0, st>>>((__half*)v, (const __half*)x, (const __half*)wa,
+                                                            (const int32_t*)indices, h1, rank, num_adapters, v_cols, scale);
+  return cudaGetLastError() == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
+}

@@ -57,10 +57,7 @@ struct GemmCall {
 
 template <class Cfg>
 static int launch_cfg(const GemmCall& c, const GemmArgs& a_in) {
-  // TRB_KSPLIT=0 in the environment (read once) turns the tail K split off, for comparison runs.
-  static const bool no_split = [] { const char* e = getenv("TRB_KSPLIT"); return e != nullptr && e[0] == '0'; }();
-  GemmArgs a = a_in;
-  if (no_split) { a.ksplit_buf = nullptr; a.ksplit_cnt = nullptr; }
+  const GemmArgs& a = a_in;
   const int slabs = a.K / 32;
   const int groups = a.grouped ? a.K / 128 : 1;
   CUtensorMap tx, tq, tm, ts;
@@ -111,8 +108,7 @@ static int launch_cfg(const GemmCall& c, const GemmArgs& a_in) {
   return cudaLaunchKernelEx(&lc, delta_gemm_kernel<Cfg>, tx, tq, tm, ts, a) == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
 }
 
-// Prefill-sized tiles: the tcgen05 / TMEM kernels (sparse instruction by default; the dense-expanding
-// kernel is kept selectable with TRB_TC_DENSE=1 in the environment for comparison).
+// Prefill-sized tiles: the sparse tcgen05 / TMEM kernel.
 template <class Cfg, class Kernel>
 static int launch_tc_impl(Kernel kernel, const GemmCall& c, const GemmArgs& a) {
   const int slabs = a.K / 32;
@@ -169,21 +165,11 @@ static int launch_tc_impl(Kernel kernel, const GemmCall& c, const GemmArgs& a) {
   return cudaLaunchKernelEx(&lc, kernel, tx, tq, tm, ts, a) == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
 }
 static int launch_tc(const GemmCall& c, const GemmArgs& a) {
-  static const bool dense = [] {
-    const char* e = getenv("TRB_TC_DENSE");
-    return e != nullptr && e[0] == '1';
-  }();
-  static const bool single = [] {
-    const char* e = getenv("TRB_TC_PAIR");
-    return e != nullptr && e[0] == '0';
-  }();
-  if (dense) return launch_tc_impl<TcCfg>(delta_gemm_tc_kernel, c, a);
   // The sparse kernel writes y in 16-byte pieces of 8 output features.
   if ((reinterpret_cast<uintptr_t>(a.y) & 15) != 0 || (a.N & 7) != 0) return TRB_ERR_KERN_SHAPE;
-  if (single) return launch_tc_impl<TcSpCfg>(delta_gemm_tcsp_kernel<false>, c, a);
   return launch_tc_impl<TcSpPairCfg>(delta_gemm_tcsp_kernel<true>, c, a);
 }
-static_assert(TcCfg::SMEM_ALLOC <= 232448 && TcSpCfg::SMEM_ALLOC <= 232448 && TcSpPairCfg::SMEM_ALLOC <= 232448, "shared memory budget of one sm_100 CTA");
+static_assert(TcSpPairCfg::SMEM_ALLOC <= 232448, "shared memory budget of one sm_100 CTA");
 
 using CfgT8 = GemmCfg<1, 2, 4, 16, 6>;
 // Wide outputs: 256-column items, two warps per column block.  Half as many work items, so half the

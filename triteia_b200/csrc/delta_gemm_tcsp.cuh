@@ -3,15 +3,15 @@
 // STORED halves of the 2:4 weights in shared memory (16 per row and instruction), 2:4 metadata in
 // tensor memory, fp32 accumulator in tensor memory.
 //
-// Two forms of one kernel template:
-//   PAIR (default)  two CTAs of a cluster issue one tcgen05.mma.sp.cta_group::2 per instruction:
+// Forms of the kernel template:
+//   PAIR (shipped)  two CTAs of a cluster issue one tcgen05.mma.sp.cta_group::2 per instruction:
 //                   M = 256 output features (128 per CTA: each CTA decodes its own stripe and holds its
 //                   own accumulator and metadata) x N = 256 tokens (each CTA stages 128 of them).  The
 //                   leader CTA's MMA thread issues for both; every decode warp of both CTAs arrives on
 //                   the leader's barrier; tcgen05.commit with a CTA mask hands stages back to both.
 //                   Half the activation bytes per SM and flop: the kernel is bound by what one SM can
 //                   pull through TMA and shared memory, not by the tensor pipe.
-//   single CTA      M = 128 x N = 256 per CTA (kept selectable for comparison).
+//   single CTA      M = 128 x N = 256 per CTA (PAIR = false; not instantiated in the library).
 //
 // Per 64-K chunk and per CTA:
 //   producer warps  TMA, one thread each: the activation tile [tokens x 64 K] (128-byte swizzle, the B
@@ -32,7 +32,7 @@
 // Every wait is bounded; both CTAs of a pair meet at a cluster barrier before either leaves.
 #pragma once
 
-#include "delta_gemm_tc.cuh"
+#include "tc_common.cuh"
 
 namespace trb {
 

@@ -6,7 +6,7 @@
 #include "common.cuh"
 #include "route.cuh"
 #include "delta_gemm.cuh"
-#include "delta_gemm_tc.cuh"
+#include "tc_common.cuh"
 #include "delta_gemm_tcsp.cuh"
 #include "delta_gemm_host.cuh"
 #include "shard.cuh"
@@ -14,5 +14,6 @@
 #include "pack.cuh"
 #include "stack.cuh"
 #include "lora.cuh"
+#include "base_gemm.cuh"
 #include "elementwise.cuh"
 #include "no_alloc.cuh"

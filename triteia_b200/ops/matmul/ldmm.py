@@ -6,14 +6,9 @@ Index space (ldmm.py:54-59 of the reference): [0, M) = LoRA adapter, [M, M + D) 
 """
 import torch
 
+from ._base import base_gemm, base_or_zeros as _base, lora_shrink_rows
 from .lora import lora_forloop, lora_indexed
 from .sbmm import sbmm_4bit_2_4_forloop, sbmm_indexed
-
-
-def _base(x_, base_weight, n_out):
-    if base_weight is not None:
-        return torch.matmul(x_, base_weight.t())
-    return torch.zeros(x_.shape[0], n_out, dtype=x_.dtype, device=x_.device)
 
 
 def baseline_ldmm(indices, x, LwA, LwB, DeltaW, metas, ss, base_weight=None, debug=False):
@@ -31,17 +26,25 @@ def baseline_ldmm(indices, x, LwA, LwB, DeltaW, metas, ss, base_weight=None, deb
 
 
 def ldmm(indices, x, LwA, LwB, DeltaW, metas, ss, base_weight=None, debug=False):
-    """Two launches after the base GEMM, no host synchronisation, no masks: the indexed LoRA
-    kernel skips ids outside [0, M) and the router of the delta kernel skips ids outside
-    [M, M + D), both reading the one index vector.  The delta tokens may be in any order."""
+    """No library GEMM, no host synchronisation, no masks.  With a base weight: the LoRA shrink
+    writes every token's rank-r vector into the column block of its adapter, and ONE tensor-core
+    kernel produces base + LoRA in one accumulator (the expand is extra K of the same product) and
+    writes y once; the delta kernel then adds its rows.  Without a base weight the indexed LoRA
+    kernel runs alone.  Both parts read the one index vector: the LoRA side skips ids outside
+    [0, M), the router of the delta kernel skips ids outside [M, M + D).  Any token order."""
     x_ = x.to(torch.float16)
     if not x_.is_contiguous():
         x_ = x_.contiguous()
-    y = _base(x_, base_weight, LwB.shape[2])
     M = LwA.shape[0]
     idx = indices if indices.dtype == torch.int32 else indices.to(torch.int32)
-    if M > 0:
-        lora_indexed(y, x_, LwA.to(torch.float16).contiguous(), LwB.to(torch.float16).contiguous(), idx)
+    if base_weight is not None and M > 0:
+        A16, B16 = LwA.to(torch.float16).contiguous(), LwB.to(torch.float16).contiguous()
+        v = lora_shrink_rows(x_, A16, idx)
+        y = base_gemm(x_, base_weight.to(torch.float16), lora_v=v, lora_b=B16.view(M * B16.shape[1], B16.shape[2]))
+    else:
+        y = _base(x_, base_weight, LwB.shape[2])
+        if M > 0:
+            lora_indexed(y, x_, LwA.to(torch.float16).contiguous(), LwB.to(torch.float16).contiguous(), idx)
     if DeltaW is not None and DeltaW.shape[0] > 0:
         sbmm_indexed(x_, DeltaW, metas, ss, idx, y=y, index_offset=M)
     return y.to(x.dtype)

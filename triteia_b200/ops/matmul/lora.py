@@ -5,12 +5,13 @@ import torch
 from ... import _lib
 from ..._lib import lib, ptr, stream_of, dev_of
 from ...capi import add_lora_sgmv_cutlass
+from ._base import base_or_zeros
 
 
 def _base(x, base_weight, n_out):
-    if base_weight is not None:
-        return torch.matmul(x, base_weight.t())
-    return torch.zeros(x.shape[0], n_out, dtype=x.dtype, device=x.device)
+    if base_weight is not None and not x.is_cuda:
+        return torch.matmul(x, base_weight.t())        # lora_forloop also serves as a host-side check path
+    return base_or_zeros(x, base_weight, n_out)
 
 
 def lora_forloop(weights_A, weights_B, x, indices, base_weight=None):

@@ -11,13 +11,14 @@ import torch
 from ... import _lib
 from ..._lib import lib, ptr, stream_of, dev_of
 from ...capi import mul_2_4, sbmm_2_4, sbmm_2_4_multilaunch
+from ._base import base_gemm, base_or_zeros
 from ._scratch import scratch
 
 
 def _base(xs, base_weight, n_out):
-    if base_weight is not None:
-        return torch.matmul(xs, base_weight.t())
-    return torch.zeros(xs.shape[0], n_out, dtype=xs.dtype, device=xs.device)
+    if base_weight is not None and not xs.is_cuda:
+        return torch.matmul(xs, base_weight.t())       # sbmm_16bit_forloop also serves as a host-side check path
+    return base_or_zeros(xs, base_weight, n_out)
 
 
 def sbmm_16bit_forloop(weights, xs, indices, base_weight=None):
@@ -88,7 +89,7 @@ def sbmm_4bit_2_4_native(qweights, xs, metas, ss, indices, base_weight=None):
     if not xs.is_contiguous():
         xs = xs.contiguous()
     if base_weight is not None:
-        y = torch.matmul(xs, base_weight.t())
+        y = base_gemm(xs, base_weight)
         return sbmm_indexed(xs, qweights, metas, ss, indices, y=y)
     return sbmm_indexed(xs, qweights, metas, ss, indices)
 
