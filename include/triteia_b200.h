@@ -215,16 +215,21 @@ int trb_row_checksum(const void* y, void* sums, int rows, int prob_m, int accumu
 /* One pass of a stack of n_linears independent delta linears over grouped rows, issued from C (the
  * host cost of a launch made from Python exceeds the run time of most of these kernels).  Rows
  * [class_row0[c], +class_rows[c]) form size class c with its own segment list (class_ids /
- * class_starts / class_counts, class_segs[c] entries, starts relative to the class's first row); per
- * linear i every class gets one trb_sbmm_2_4 launch on x_of[i] [rows, k[i]] -> y_of[i] [rows, n[i]],
- * then y_of[i] is folded into checksum [rows] fp32 (trb_row_checksum, accumulate).  All arrays are
+ * class_starts / class_counts, class_segs[c] entries, starts relative to the class's first row) and
+ * its kernel: class_tile[c] = 32 (segments of up to 64 rows: the mma.sp kernel, tiles of 8, 16 or 32
+ * rows chosen per segment) or 256 (longer segments: the tcgen05 kernel).  Per linear i every class
+ * gets one segment-list launch on x_of[i] [rows, k[i]] -> y_of[i] [rows, n[i]], then y_of[i] is
+ * folded into checksum [rows] fp32 (trb_row_checksum, accumulate).  ksplit: NULL, or
+ * trb_sbmm_ksplit_bytes() bytes of working memory (256-byte aligned, first 512 bytes zero on entry
+ * and again on exit) that lets under-filled launches cut their work items along K.  All arrays are
  * host arrays of device pointers / ints.  No counterpart in the reference. */
 int trb_stack_pass(int n_linears, const void* const* q, const void* const* meta,
                    const void* const* s, const int* k, const int* n, const void* const* x_of,
                    void* const* y_of, int n_classes, const int* class_row0, const int* class_rows,
                    const void* const* class_ids, const void* const* class_starts,
-                   const void* const* class_counts, const int* class_segs, void* checksum, int rows,
-                   int groupsize, int dev, void* stream);
+                   const void* const* class_counts, const int* class_segs, const int* class_tile,
+                   void* checksum, int rows, int groupsize, void* ksplit, size_t ksplit_bytes, int dev,
+                   void* stream);
 
 /* BGMV: Y[b, :] += scale * W[indices[b], layer_idx] @ X[b, :], W [M, L, h_out, h_in]
  * contiguous, indices int64 [B].  Replaces bgmv_kernel<feat_in, feat_out, T>

@@ -804,3 +804,60 @@ def test_base_gemm_with_lora_expand(cuda, M, rank):
     ref = oracle.lora(A.cpu().numpy(), B.cpu().numpy(), x.cpu().numpy(), idx_np, base_weight=w.cpu().numpy())
     check(y, ref, mean_tol=None)
     assert _lib().device_status(0) == 0
+
+
+# ------------------------------------------------------------------ tiles chosen per segment, long lists
+def test_sbmm_zipf_batch_mixed_tiles(cuda):
+    """A Zipf(1.5) batch of 512 tokens over 64 deltas through the one-call path: the hot deltas
+    (hundreds of rows) go to the tcgen05 kernel, mid-sized ones to 16- and 32-token tiles, the tail to
+    8-token tiles, all inside one call.  Every row against the oracle; run twice, bit-identical."""
+    ops = _ops()
+    T, D, K, N = 512, 64, 512, 768
+    qs, metas, ss = packed(N, K, 128, seed=51, num=D)
+    rng = np.random.default_rng(51)
+    p = np.arange(1, D + 1, dtype=np.float64) ** -1.5
+    idx_np = rng.choice(D, T, p=p / p.sum()).astype(np.int32)
+    idx_np[rng.choice(T, 20, replace=False)] = -1
+    counts = np.bincount(idx_np[idx_np >= 0], minlength=D)
+    assert counts.max() > 64 and ((counts > 8) & (counts <= 32)).any() and ((counts > 0) & (counts <= 8)).any()
+    x = torch.randn(T, K, dtype=torch.float16, device=cuda, generator=torch.Generator(cuda).manual_seed(51))
+    idx = torch.from_numpy(idx_np).to(cuda)
+    y = ops.sbmm_4bit_2_4_native(qs, x, metas, ss, idx)
+    check(y, sbmm_ref(qs, metas, ss, x, idx, None))
+    assert torch.all(y[idx == -1] == 0)
+    assert torch.equal(y, ops.sbmm_4bit_2_4_native(qs, x, metas, ss, idx))
+    assert _lib().device_status(0) == 0
+
+
+@pytest.mark.parametrize("count", [33, 48, 64, 65, 100])
+def test_sbmm_segment_sizes_around_the_class_bounds(cuda, count):
+    """One delta with `count` rows among singletons: 33-64 rows run as two 32-token tiles on mma.sp,
+    65 and more as one tile of the tcgen05 kernel."""
+    ops = _ops()
+    D, K, N = 6, 256, 512
+    qs, metas, ss = packed(N, K, -1, seed=60 + count, num=D)
+    idx_np = np.concatenate([np.full(count, 2), np.arange(D), [-1, -1]]).astype(np.int32)
+    np.random.default_rng(count).shuffle(idx_np)
+    T = idx_np.size
+    x = torch.randn(T, K, dtype=torch.float16, device=cuda, generator=torch.Generator(cuda).manual_seed(count))
+    idx = torch.from_numpy(idx_np).to(cuda)
+    y = ops.sbmm_4bit_2_4_native(qs, x, metas, ss, idx)
+    check(y, sbmm_ref(qs, metas, ss, x, idx, None))
+
+
+def test_sbmm_more_than_1024_segments(cuda):
+    """2048 tokens over 1500 deltas in one call (more tiles than one launch's shared-memory table
+    held before), and the same batch through the segment-list entry point, which splits lists of
+    more than 1024 segments over several launches."""
+    ops = _ops()
+    T, D, K, N = 2048, 1500, 128, 256
+    qs, metas, ss = packed(N, K, -1, seed=71, num=D)
+    rng = np.random.default_rng(71)
+    idx_np = np.sort(rng.integers(-1, D, T)).astype(np.int32)
+    x = torch.randn(T, K, dtype=torch.float16, device=cuda, generator=torch.Generator(cuda).manual_seed(71))
+    idx = torch.from_numpy(idx_np).to(cuda)
+    ref = sbmm_ref(qs, metas, ss, x, idx, None)
+    assert len(np.unique(idx_np[idx_np >= 0])) > 1024
+    check(ops.sbmm_4bit_2_4_native(qs, x, metas, ss, idx), ref)
+    check(ops.sbmm_4bit_2_4_segments(qs, x, metas, ss, idx), ref)
+    assert _lib().device_status(0) == 0

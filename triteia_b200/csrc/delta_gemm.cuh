@@ -20,7 +20,11 @@ namespace trb {
 
 constexpr int kMaxSegments = 1024;
 
-enum SegMode { kSegList = 0, kSegSingle = 1, kSegIdentity = 2 };
+// kSegList: segments of any length (tiles counted per segment through a prefix table in shared memory,
+// at most kMaxSegments segments per launch); kSegSingle: one segment = all rows, delta 0;
+// kSegIdentity: row r is its own segment with delta r; kSegTiles: the lists hold ready-made tiles
+// (at most Cfg::TT rows each, as the router writes them), no limit on their number.
+enum SegMode { kSegList = 0, kSegSingle = 1, kSegIdentity = 2, kSegTiles = 3 };
 
 struct GemmArgs {
   const int* seg_delta;   // [n_seg] delta id per segment (kSegList)
@@ -61,7 +65,8 @@ constexpr size_t kKsplitBufBytes = (size_t)kKsplitSlots * kKsplitSlotFloats * 4;
 
 template <int NB_, int SW_, int KQ_, int KS_, int STAGES_>
 struct GemmCfg {
-  static constexpr int NB = NB_;          // token blocks of 8 per tile
+  static constexpr int NB = NB_;          // token blocks of 8 in the largest tile; a tile's class (1, 2 or 4
+                                          // blocks) follows from its row count, item by item
   static constexpr int SW = SW_;          // 64-column blocks per stripe
   static constexpr int KQ = KQ_;          // warps sharing one column block (split over slabs)
   static constexpr int KS = KS_;          // 32-K slabs per pipeline stage
@@ -70,6 +75,7 @@ struct GemmCfg {
   static constexpr int CTHREADS = CW * 32;
   static constexpr int THREADS = CTHREADS + 32;     // + one producer warp
   static_assert(CW == 8, "8 consumer warps");
+  static_assert(NB == 1 || NB == 2 || NB == 4, "tile classes are 1, 2 and 4 token blocks");
   static_assert(KQ == 1 || KQ == 2 || KQ == 4, "the K split must divide the four j's of a fragment");
   static_assert(KS % 4 == 0 && KS % KQ == 0 && KS % 2 == 0, "stage must hold whole scale groups");
   static_assert((KS / KQ) <= 4 && 4 % (KS / KQ) == 0 && KS <= 32, "a warp's slabs of a stage share one scale group");
@@ -91,7 +97,8 @@ struct GemmCfg {
   static constexpr int S_OFF = M_OFF + M_BYTES;
   static constexpr int STAGE_BYTES = (S_OFF + S_BYTES + 1023) / 1024 * 1024;
   static constexpr int RED_BUFS = KQ - 1;                     // partner-warp reduction buffers
-  static constexpr int RED_BUF_FLOATS = 16 * NB * SW * 32;
+  static constexpr int NBH = NB < 2 ? NB : 2;                 // token blocks exchanged per round
+  static constexpr int RED_BUF_FLOATS = 16 * NBH * SW * 32;
   static constexpr int RED_FLOATS = RED_BUFS * RED_BUF_FLOATS;
   static constexpr int RED_OFF = STAGES * STAGE_BYTES;
   static constexpr int PREFIX_OFF = RED_OFF + RED_FLOATS * 4;
@@ -156,7 +163,7 @@ __device__ __forceinline__ WorkItem decode_item(const GemmArgs& a, const int* pr
   if (a.mode == kSegSingle) {
     seg = 0;
     tin = tile;
-  } else if (a.mode == kSegIdentity) {
+  } else if (a.mode == kSegIdentity || a.mode == kSegTiles) {
     seg = tile;
     tin = 0;
   } else {
@@ -186,12 +193,19 @@ __device__ __forceinline__ WorkItem decode_item(const GemmArgs& a, const int* pr
   return w;
 }
 
+// Token blocks of the class that serves a tile of `valid` rows.
+__device__ __forceinline__ int tile_class(int valid) { return valid <= 8 ? 1 : (valid <= 16 ? 2 : 4); }
+
+template <int V> using IntTag = std::integral_constant<int, V>;
+
+// tm_x1 / tm_x2 / tm_x4: the activation matrix with boxes of 8, 16 and 32 rows (one per tile class).
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
-delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_q,
+delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ CUtensorMap tm_x2,
+                  const __grid_constant__ CUtensorMap tm_x4, const __grid_constant__ CUtensorMap tm_q,
                   const __grid_constant__ CUtensorMap tm_m, const __grid_constant__ CUtensorMap tm_s,
                   const GemmArgs a) {
-  constexpr int NB = Cfg::NB, SW = Cfg::SW, KQ = Cfg::KQ, KS = Cfg::KS, STAGES = Cfg::STAGES;
+  constexpr int NBMAX = Cfg::NB, SW = Cfg::SW, KQ = Cfg::KQ, KS = Cfg::KS, STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* red = reinterpret_cast<float*>(smem + Cfg::RED_OFF);
@@ -212,10 +226,11 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     *dead = 0;
     fence_mbar_init();
   }
+  pdl_launch_dependents();
   pdl_wait();   // everything below reads what the kernels launched before this one wrote
 
   int n_seg = a.n_seg_ptr ? *a.n_seg_ptr : a.n_seg;
-  n_seg = max(0, min(n_seg, kMaxSegments));
+  n_seg = max(0, min(n_seg, a.mode == kSegTiles ? a.n_seg : kMaxSegments));
 
   // Tiles-per-segment prefix sums (list mode).  Warp 0 scans 32 segments per step.
   int total_tiles;
@@ -244,7 +259,7 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     total_tiles = prefix[n_seg];
   } else {
     __syncthreads();
-    total_tiles = a.mode == kSegSingle ? (a.rows + Cfg::TT - 1) / Cfg::TT : a.rows;
+    total_tiles = a.mode == kSegTiles ? n_seg : (a.mode == kSegSingle ? (a.rows + Cfg::TT - 1) / Cfg::TT : a.rows);
   }
 
   const int n_stripes = (a.N + SW * 64 - 1) / (SW * 64);
@@ -254,31 +269,47 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   const int groups = a.grouped ? a.K / 128 : 1;
   // Work units of this CTA: whole items in the full rounds, then (maybe) a K range of a tail item.
   const TailSplit split = tail_split(n_items, k_stages, (int)gridDim.x, (int)blockIdx.x,
-                                     NB == 1 && SW * 512 <= kKsplitSlotFloats && a.ksplit_buf != nullptr);
+                                     SW * 512 <= kKsplitSlotFloats && a.ksplit_buf != nullptr);
+  // Only 8-token tiles are cut along K (the partial-tile slots hold 8 tokens): a larger tile of the
+  // tail is done whole by the CTA that holds its piece 0.  Returns false when this CTA has nothing to do.
+  auto settle_unit = [&](WorkUnit& wu, const WorkItem& w) -> bool {
+    if (!w.ok) return false;
+    if (wu.parts > 1 && tile_class(w.valid) != 1) {
+      if (wu.part != 0) return false;
+      wu.ks0 = 0; wu.ks1 = k_stages; wu.parts = 1;
+    }
+    return true;
+  };
 
   if (warp == Cfg::CW) {
     // ------------------------------ producer ------------------------------
     if (lane == 0) {
-      prefetch_tmap(&tm_x);
+      prefetch_tmap(&tm_x1);
+      if (NBMAX >= 2) prefetch_tmap(&tm_x2);
+      if (NBMAX >= 4) prefetch_tmap(&tm_x4);
       prefetch_tmap(&tm_q);
       prefetch_tmap(&tm_m);
       if (a.grouped) prefetch_tmap(&tm_s);
       const uint64_t pol_w = policy_evict_first();
       const uint64_t pol_x = policy_evict_last();
-      const uint32_t stage_tx = Cfg::X_BYTES + Cfg::Q_BYTES + Cfg::M_BYTES + (a.grouped ? Cfg::S_BYTES : 0);
+      const uint32_t weight_tx = Cfg::Q_BYTES + Cfg::M_BYTES + (a.grouped ? Cfg::S_BYTES : 0);
       int st = 0;
       uint32_t phase = 0;
       for (int u = 0; u < split.units; ++u) {
-        const WorkUnit wu = work_unit(split, u, (int)gridDim.x, (int)blockIdx.x, k_stages);
+        WorkUnit wu = work_unit(split, u, (int)gridDim.x, (int)blockIdx.x, k_stages);
         const WorkItem w = decode_item<Cfg>(a, prefix, n_seg, n_stripes, wu.item);
-        if (!w.ok) continue;
+        if (!settle_unit(wu, w)) continue;
+        const int cls = NBMAX == 1 ? 1 : tile_class(w.valid);
+        const CUtensorMap* tmx = cls == 1 ? &tm_x1 : (cls == 2 ? &tm_x2 : &tm_x4);
+        const uint32_t box_bytes = (uint32_t)cls * 1024u;          // 8 * cls rows of 128 bytes
+        const uint32_t stage_tx = Cfg::NXBOX * box_bytes + weight_tx;
         for (int ks = wu.ks0; ks < wu.ks1; ++ks) {
           mbar_wait(&empty_bar[st], phase ^ 1, dead);
           uint8_t* sbase = smem + st * Cfg::STAGE_BYTES;
           mbar_arrive_expect_tx(&full_bar[st], stage_tx);
 #pragma unroll
           for (int b = 0; b < Cfg::NXBOX; ++b)
-            tma_load_2d_hint(sbase + Cfg::X_OFF + b * Cfg::X_BOX_BYTES, &tm_x, ks * KS * 32 + b * 64, w.row0,
+            tma_load_2d_hint(sbase + Cfg::X_OFF + b * box_bytes, tmx, ks * KS * 32 + b * 64, w.row0,
                              &full_bar[st], pol_x);
           const int wrow = w.delta * slabs + ks * KS;
 #pragma unroll
@@ -307,43 +338,36 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   const int g8 = lane >> 2;   // quad index: MMA row group / token inside a block of 8
   const int m4 = lane & 3;
   constexpr int SPW = KS / KQ;  // slabs per warp per stage
-  // A warp's slabs of one stage lie inside one scale group, so their integer-level products are
-  // accumulated on their own and scaled once per stage in fp32 (small token tiles); large token
-  // tiles scale every weight in fp16 instead, which costs less than scaling many accumulators.
-  constexpr bool kPostScale = (NB <= 2);
-  constexpr bool kBulkLoad = (NB == 1);   // larger tiles would spill: they load slab by slab
   const int box = cb / Cfg::QB, within = cb % Cfg::QB;
   // Per-lane byte offsets inside a stage, fixed for the whole kernel.
   const uint32_t q_off = Cfg::Q_OFF + box * (KS * Cfg::QB * 512) + within * 512 + lane * 16 + kq * SPW * (Cfg::QB * 512);
   const uint32_t m_off = Cfg::M_OFF + box * (KS * Cfg::QB * 256) + within * 256 + lane * 4 + kq * SPW * (Cfg::QB * 256);
   const uint32_t s_off = Cfg::S_OFF + (cb / Cfg::SB) * Cfg::S_BOX_BYTES + ((kq * SPW) / 4) * (Cfg::SB * 128) +
                          (cb % Cfg::SB) * 128 + g8 * 16;
-  // ldmatrix row address of slab i of this warp: 16-byte chunk 4*slab + lane/8 of the stage's K
-  // range lives in activation box chunk/8 at swizzled chunk position (chunk%8) ^ (row%8).
-  uint32_t x_off[SPW];
-#pragma unroll
-  for (int i = 0; i < SPW; ++i) {
-    const int chunk = (kq * SPW + i) * 4 + (lane >> 3);
-    x_off[i] = Cfg::X_OFF + (chunk >> 3) * Cfg::X_BOX_BYTES + (lane & 7) * 128 + ((((chunk & 7) ^ (lane & 7))) << 4);
-  }
   const uint32_t smem_base = smem_u32(smem);
 
   int st = 0;
   uint32_t phase = 0;
   bool first_item = true;
   constexpr int JW = 4 / KQ;   // accumulator column pairs (j) that each partner warp finishes
-  WorkItem w_next{};
-  if (split.units > 0)
-    w_next = decode_item<Cfg>(a, prefix, n_seg, n_stripes,
-                              work_unit(split, 0, (int)gridDim.x, (int)blockIdx.x, k_stages).item);
-  for (int u = 0; u < split.units; ++u) {
-    const WorkUnit wu = work_unit(split, u, (int)gridDim.x, (int)blockIdx.x, k_stages);
-    const WorkItem w = w_next;
-    // Descriptor of the next item: its global loads are in flight during this item's K loop.
-    if (u + 1 < split.units)
-      w_next = decode_item<Cfg>(a, prefix, n_seg, n_stripes,
-                                work_unit(split, u + 1, (int)gridDim.x, (int)blockIdx.x, k_stages).item);
-    if (!w.ok) continue;
+
+  // One work unit with a tile of NB token blocks (the tile's class).
+  auto run_unit = [&](auto nb_tag, const WorkUnit& wu, const WorkItem& w) {
+    constexpr int NB = decltype(nb_tag)::value;
+    // A warp's slabs of one stage lie inside one scale group, so their integer-level products are
+    // accumulated on their own and scaled once per stage in fp32 (small token tiles); large token
+    // tiles scale every weight in fp16 instead, which costs less than scaling many accumulators.
+    constexpr bool kPostScale = (NB <= 2);
+    constexpr bool kBulkLoad = (NB == 1);   // larger tiles would spill: they load slab by slab
+    constexpr uint32_t XBOX = NB * 1024;    // bytes of one 64-K activation box of this class
+    // ldmatrix row address of slab i of this warp: 16-byte chunk 4*slab + lane/8 of the stage's K
+    // range lives in activation box chunk/8 at swizzled chunk position (chunk%8) ^ (row%8).
+    uint32_t x_off[SPW];
+#pragma unroll
+    for (int i = 0; i < SPW; ++i) {
+      const int chunk = (kq * SPW + i) * 4 + (lane >> 3);
+      x_off[i] = Cfg::X_OFF + (chunk >> 3) * XBOX + (lane & 7) * 128 + ((((chunk & 7) ^ (lane & 7))) << 4);
+    }
     const int nbv = (w.valid + 7) >> 3;
     const bool col_ok = w.col0 + cb * 64 < a.N;
 
@@ -468,7 +492,9 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
           for (int i = 0; i < SPW; ++i)
             if (FULL || ks * KS + kq * SPW + i < slabs) compute_slab(i, q4[i], e0[i], e1[i], bf[i]);
         } else {
-#pragma unroll
+          // 32-token tiles keep 64 accumulators per lane: their slabs run one after the other.
+          constexpr int kSlabUnroll = NB >= 4 ? 1 : SPW;
+#pragma unroll kSlabUnroll
           for (int i = 0; i < SPW; ++i) {
             if (FULL || ks * KS + kq * SPW + i < slabs) {
               const uint4 q4 = lds128(sb + q_off + i * (Cfg::QB * 512));
@@ -520,36 +546,41 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     // Partner warps (same column block) own identical fragments.  Each of them finishes the j's
     // [kq*JW, (kq+1)*JW): it hands its partial sums of the other j's to their owners through shared
     // memory, adds the partners' partials to its own in a fixed order, and writes its columns.
-    // Barrier 2 (before the stores) keeps an item's partials until every reader of the previous
-    // item is done; barrier 1 separates stores from loads.
+    // The exchange runs in rounds of at most two token blocks (the buffer holds that much).
+    // Barrier 2 (before the stores) keeps a round's partials until every reader of the previous
+    // round is done; barrier 1 separates stores from loads.
     if constexpr (KQ > 1) {
       constexpr int CT = Cfg::CTHREADS;
       constexpr int LANES = SW * 32;
-      if (!first_item) named_bar_sync(2, CT);
-      first_item = false;
+      constexpr int NBH = NB < 2 ? NB : 2;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int owner = j / JW;
-        if (owner != kq) {
-          const int slot = kq < owner ? kq : kq - 1;
-          float* dst = red + (((owner * (KQ - 1) + slot) * JW + (j % JW)) * NB * 4) * LANES + cb * 32 + lane;
+      for (int h0 = 0; h0 < NB; h0 += NBH) {
+        if (!first_item) named_bar_sync(2, CT);
+        first_item = false;
 #pragma unroll
-          for (int nb = 0; nb < NB; ++nb)
+        for (int j = 0; j < 4; ++j) {
+          const int owner = j / JW;
+          if (owner != kq) {
+            const int slot = kq < owner ? kq : kq - 1;
+            float* dst = red + (((owner * (KQ - 1) + slot) * JW + (j % JW)) * NBH * 4) * LANES + cb * 32 + lane;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) dst[(nb * 4 + c) * LANES] = acc[j][nb][c];
+            for (int nb = 0; nb < NBH; ++nb)
+#pragma unroll
+              for (int c = 0; c < 4; ++c) dst[(nb * 4 + c) * LANES] = acc[j][h0 + nb][c];
+          }
         }
-      }
-      named_bar_sync(1, CT);
+        named_bar_sync(1, CT);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (j / JW == kq) {
+        for (int j = 0; j < 4; ++j) {
+          if (j / JW == kq) {
 #pragma unroll
-          for (int slot = 0; slot < KQ - 1; ++slot) {
-            const float* src = red + (((kq * (KQ - 1) + slot) * JW + (j % JW)) * NB * 4) * LANES + cb * 32 + lane;
+            for (int slot = 0; slot < KQ - 1; ++slot) {
+              const float* src = red + (((kq * (KQ - 1) + slot) * JW + (j % JW)) * NBH * 4) * LANES + cb * 32 + lane;
 #pragma unroll
-            for (int nb = 0; nb < NB; ++nb)
+              for (int nb = 0; nb < NBH; ++nb)
 #pragma unroll
-              for (int c = 0; c < 4; ++c) acc[j][nb][c] += src[(nb * 4 + c) * LANES];
+                for (int c = 0; c < 4; ++c) acc[j][h0 + nb][c] += src[(nb * 4 + c) * LANES];
+            }
           }
         }
       }
@@ -581,7 +612,7 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
           *flag = old;
         }
         named_bar_sync(3, Cfg::CTHREADS);
-        if (*flag != wu.parts - 1) continue;
+        if (*flag != wu.parts - 1) return;
         if (warp == 0 && lane == 0) a.ksplit_cnt[wu.tail] = 0;   // back to zero for the next launch
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -628,6 +659,28 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         }
       }
     }
+  };
+
+  WorkItem w_next{};
+  if (split.units > 0)
+    w_next = decode_item<Cfg>(a, prefix, n_seg, n_stripes,
+                              work_unit(split, 0, (int)gridDim.x, (int)blockIdx.x, k_stages).item);
+  for (int u = 0; u < split.units; ++u) {
+    WorkUnit wu = work_unit(split, u, (int)gridDim.x, (int)blockIdx.x, k_stages);
+    const WorkItem w = w_next;
+    // Descriptor of the next item: its global loads are in flight during this item's K loop.
+    if (u + 1 < split.units)
+      w_next = decode_item<Cfg>(a, prefix, n_seg, n_stripes,
+                                work_unit(split, u + 1, (int)gridDim.x, (int)blockIdx.x, k_stages).item);
+    if (!settle_unit(wu, w)) continue;
+    const int cls = NBMAX == 1 ? 1 : tile_class(w.valid);
+    if constexpr (NBMAX >= 4) {
+      if (cls == 4) { run_unit(IntTag<4>{}, wu, w); continue; }
+    }
+    if constexpr (NBMAX >= 2) {
+      if (cls == 2) { run_unit(IntTag<2>{}, wu, w); continue; }
+    }
+    run_unit(IntTag<1>{}, wu, w);
   }
 }
 

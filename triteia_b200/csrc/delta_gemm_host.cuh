@@ -5,6 +5,7 @@
 #include "delta_gemm.cuh"
 
 #include <cudaTypedefs.h>
+#include <atomic>
 #include <mutex>
 
 namespace trb {
@@ -36,14 +37,24 @@ static bool make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int esize, con
 }
 
 static int sm_count(int dev) {
-  static int cached[64] = {};
+  static std::atomic<int> cached[64];
   if (dev < 0 || dev >= 64) return 148;
-  if (cached[dev] == 0) {
-    int v = 0;
+  int v = cached[dev].load(std::memory_order_relaxed);
+  if (v == 0) {
     if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
-    cached[dev] = v;
+    cached[dev].store(v, std::memory_order_relaxed);
   }
-  return cached[dev];
+  return v;
+}
+
+// cudaFuncSetAttribute(max dynamic shared memory) once per device and kernel; safe from any host thread.
+template <class Kernel>
+static bool ensure_smem_attr(Kernel kernel, int dev, int bytes, std::atomic<bool>* done /* [64] */) {
+  if (dev < 0 || dev >= 64) return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
+  if (done[dev].load(std::memory_order_acquire)) return true;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
+  done[dev].store(true, std::memory_order_release);
+  return true;
 }
 
 struct GemmCall {
@@ -56,14 +67,17 @@ struct GemmCall {
 };
 
 template <class Cfg>
-static int launch_cfg(const GemmCall& c, const GemmArgs& a_in) {
-  const GemmArgs& a = a_in;
+static int launch_cfg(const GemmCall& c, const GemmArgs& a) {
   const int slabs = a.K / 32;
   const int groups = a.grouped ? a.K / 128 : 1;
-  CUtensorMap tx, tq, tm, ts;
-  if (!make_map_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, c.x, (uint64_t)a.rows, (uint64_t)a.K, Cfg::TT, 64,
-                   CU_TENSOR_MAP_SWIZZLE_128B))
-    return TRB_ERR_CUDA;
+  CUtensorMap tx[3], tq, tm, ts;
+  for (int i = 0; i < 3; ++i) {   // one activation map per tile class: boxes of 8, 16 and 32 rows
+    const int rows = 8 << i;
+    if (rows > Cfg::TT) { tx[i] = tx[i - 1]; continue; }   // never dereferenced
+    if (!make_map_2d(&tx[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, c.x, (uint64_t)a.rows, (uint64_t)a.K, rows, 64,
+                     CU_TENSOR_MAP_SWIZZLE_128B))
+      return TRB_ERR_CUDA;
+  }
   if (!make_map_2d(&tq, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, c.q, (uint64_t)c.num_deltas * slabs, 2ull * a.N, Cfg::KS,
                    Cfg::QB * 128, CU_TENSOR_MAP_SWIZZLE_NONE))
     return TRB_ERR_CUDA;
@@ -77,13 +91,8 @@ static int launch_cfg(const GemmCall& c, const GemmArgs& a_in) {
   } else {
     ts = tm;  // never dereferenced
   }
-  static bool attr_set[64] = {};
-  if (c.dev >= 0 && c.dev < 64 && !attr_set[c.dev]) {
-    if (cudaFuncSetAttribute(delta_gemm_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             Cfg::SMEM_ALLOC) != cudaSuccess)
-      return TRB_ERR_CUDA;
-    attr_set[c.dev] = true;
-  }
+  static std::atomic<bool> attr_set[64];
+  if (!ensure_smem_attr(delta_gemm_kernel<Cfg>, c.dev, Cfg::SMEM_ALLOC, attr_set)) return TRB_ERR_CUDA;
   int grid = sm_count(c.dev);
   if (c.sms > 0 && c.sms < grid) grid = c.sms;
   // Upper bound on work items known on the host: never launch more CTAs than that.
@@ -91,10 +100,11 @@ static int launch_cfg(const GemmCall& c, const GemmArgs& a_in) {
   long long max_tiles;
   if (a.mode == kSegSingle) max_tiles = (a.rows + Cfg::TT - 1) / Cfg::TT;
   else if (a.mode == kSegIdentity) max_tiles = a.rows;
-  else max_tiles = (long long)a.rows / Cfg::TT + (a.n_seg_ptr ? kMaxSegments : a.n_seg);
+  else if (a.mode == kSegTiles) max_tiles = a.n_seg;
+  else max_tiles = (long long)a.rows / Cfg::TT + a.n_seg;
   const long long max_items = max_tiles * n_stripes;
   // With the tail K split the idle CTAs of a small launch take pieces of the items: keep the full grid.
-  if (max_items < grid && !(Cfg::NB == 1 && a.ksplit_buf != nullptr)) grid = (int)(max_items > 0 ? max_items : 1);
+  if (max_items < grid && a.ksplit_buf == nullptr) grid = (int)(max_items > 0 ? max_items : 1);
   cudaLaunchConfig_t lc = {};
   lc.gridDim = dim3(grid);
   lc.blockDim = dim3(Cfg::THREADS);
@@ -105,7 +115,8 @@ static int launch_cfg(const GemmCall& c, const GemmArgs& a_in) {
   at[0].val.programmaticStreamSerializationAllowed = 1;
   lc.attrs = at;
   lc.numAttrs = 1;
-  return cudaLaunchKernelEx(&lc, delta_gemm_kernel<Cfg>, tx, tq, tm, ts, a) == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
+  return cudaLaunchKernelEx(&lc, delta_gemm_kernel<Cfg>, tx[0], tx[1], tx[2], tq, tm, ts, a) == cudaSuccess ? TRB_OK
+                                                                                                             : TRB_ERR_CUDA;
 }
 
 // Prefill-sized tiles: the sparse tcgen05 / TMEM kernel.
@@ -130,12 +141,8 @@ static int launch_tc_impl(Kernel kernel, const GemmCall& c, const GemmArgs& a) {
   } else {
     ts = tm;  // never dereferenced
   }
-  static bool attr_set[64] = {};   // one per instantiation of this template, that is per kernel
-  if (c.dev >= 0 && c.dev < 64 && !attr_set[c.dev]) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_ALLOC) != cudaSuccess)
-      return TRB_ERR_CUDA;
-    attr_set[c.dev] = true;
-  }
+  static std::atomic<bool> attr_set[64];   // one per instantiation of this template, that is per kernel
+  if (!ensure_smem_attr(kernel, c.dev, Cfg::SMEM_ALLOC, attr_set)) return TRB_ERR_CUDA;
   constexpr int ctas = Cfg::CTAS;
   int grid = sm_count(c.dev);
   if (c.sms > 0 && c.sms < grid) grid = c.sms;
@@ -145,7 +152,8 @@ static int launch_tc_impl(Kernel kernel, const GemmCall& c, const GemmArgs& a) {
   long long max_tiles;
   if (a.mode == kSegSingle) max_tiles = (a.rows + Cfg::TT - 1) / Cfg::TT;
   else if (a.mode == kSegIdentity) max_tiles = a.rows;
-  else max_tiles = (long long)a.rows / Cfg::TT + (a.n_seg_ptr ? kMaxSegments : a.n_seg);
+  else if (a.mode == kSegTiles) max_tiles = a.n_seg;
+  else max_tiles = (long long)a.rows / Cfg::TT + a.n_seg;
   const long long max_items = max_tiles * n_stripes;
   if (max_items < grid) grid = (int)(max_items > 0 ? max_items : 1);
   cudaLaunchConfig_t lc = {};
@@ -171,23 +179,18 @@ static int launch_tc(const GemmCall& c, const GemmArgs& a) {
 }
 static_assert(TcSpPairCfg::SMEM_ALLOC <= 232448, "shared memory budget of one sm_100 CTA");
 
-using CfgT8 = GemmCfg<1, 2, 4, 16, 6>;
-// Wide outputs: 256-column items, two warps per column block.  Half as many work items, so half the
-// per-item cost (descriptor search, partial-sum exchange, epilogue) per byte streamed.
-using CfgT8W = GemmCfg<1, 4, 2, 8, 7>;
-using CfgT16 = GemmCfg<2, 2, 4, 16, 4>;
-using CfgT32 = GemmCfg<4, 2, 4, 8, 5>;
-using CfgT64 = GemmCfg<8, 4, 2, 4, 5>;
-static_assert(CfgT8W::SMEM_ALLOC <= 232448 && CfgT8::SMEM_ALLOC <= 232448 && CfgT16::SMEM_ALLOC <= 232448 && CfgT32::SMEM_ALLOC <= 232448 &&
-                  CfgT64::SMEM_ALLOC <= 232448,
-              "shared memory budget of one sm_100 CTA");
+// Two geometries of the mma.sp kernel, both with tiles of up to 32 tokens whose class (8, 16 or 32
+// tokens) is chosen item by item.  Wide outputs: 256-column items, two warps per column block
+// (half as many work items, so half the per-item cost per byte streamed); otherwise 128-column
+// items, four warps per column block.
+using CfgWide = GemmCfg<4, 4, 2, 8, 5>;
+using CfgNarrow = GemmCfg<4, 2, 4, 8, 6>;
+static_assert(CfgWide::SMEM_ALLOC <= 232448 && CfgNarrow::SMEM_ALLOC <= 232448, "shared memory budget of one sm_100 CTA");
+constexpr int kSmallTile = 32;     // largest token tile of the mma.sp kernel
+constexpr int kBigTile = 256;      // token tile of the tcgen05 kernel
+constexpr int kSmallSegMax = 64;   // the router sends segments of more tokens than this to the tcgen05 kernel
 
-int gemm_tile_tokens(int tokens_per_segment) {
-  if (tokens_per_segment <= 8) return 8;
-  if (tokens_per_segment <= 16) return 16;
-  if (tokens_per_segment <= 32) return 32;
-  return 256;   // tcgen05 kernel
-}
+int gemm_tile_tokens(int tokens_per_segment) { return tokens_per_segment <= kSmallTile ? kSmallTile : kBigTile; }
 
 static int check_common(const void* A, const void* B, const void* meta, void* C, const void* s, int N, int T, int K,
                         int groupsize) {
@@ -205,11 +208,8 @@ int gemm_dispatch(const GemmCall& c, const GemmArgs& a, int tile_tokens) {
   cudaError_t e = cudaSetDevice(c.dev);
   if (e != cudaSuccess) return TRB_ERR_CUDA;
   switch (tile_tokens) {
-    case 8: return (a.N % 256 == 0 && a.N >= 2048) ? launch_cfg<CfgT8W>(c, a) : launch_cfg<CfgT8>(c, a);
-    case 16: return launch_cfg<CfgT16>(c, a);
-    case 32: return launch_cfg<CfgT32>(c, a);
-    case 64: return launch_cfg<CfgT64>(c, a);
-    case 256: return a.y_peers ? TRB_ERR_KERN_SHAPE : launch_tc(c, a);
+    case kSmallTile: return (a.N % 256 == 0 && a.N >= 2048) ? launch_cfg<CfgWide>(c, a) : launch_cfg<CfgNarrow>(c, a);
+    case kBigTile: return a.y_peers ? TRB_ERR_KERN_SHAPE : launch_tc(c, a);
     default: return TRB_ERR_KERN_SHAPE;
   }
 }
@@ -240,28 +240,23 @@ extern "C" int trb_mul_2_4(const void* A, const void* B, const void* meta, void*
 // are zero again when the launch has finished).  Without it (nullptr) this is trb_sbmm_2_4.
 extern "C" size_t trb_sbmm_ksplit_bytes(void) { return 512 + kKsplitBufBytes; }
 
+// tile_tokens: 0 = choose from the average segment length; kSmallTile / kBigTile = forced.
 static int sbmm_segments(const void* A, const void* B, const void* meta, void* C, const void* s, const void* indices,
                          const void* starts, const void* counts, int prob_m, int prob_n, int prob_k, int prob_r,
-                         int groupsize, int dev, void* stream, int sms, void* ksplit, size_t ksplit_bytes) {
+                         int groupsize, int dev, void* stream, int sms, void* ksplit, size_t ksplit_bytes,
+                         int tile_tokens = 0) {
   if (prob_r == 0) return TRB_OK;
   if (prob_r < 0 || !indices || !starts || !counts) return TRB_ERR_BAD_ARG;
   const int rc = check_common(A, B, meta, C, s, prob_m, prob_n, prob_k, groupsize);
   if (rc == -1) return TRB_OK;
   if (rc != TRB_OK) return rc;
-  if (prob_r > kMaxSegments) return TRB_ERR_KERN_SHAPE;
   if (ksplit != nullptr && (((uintptr_t)ksplit & 255) != 0 || ksplit_bytes < trb_sbmm_ksplit_bytes())) return TRB_ERR_SCRATCH;
   GemmArgs a{};
   a.mode = kSegList;
-  a.seg_delta = (const int*)indices; a.seg_start = (const int*)starts; a.seg_count = (const int*)counts;
-  a.n_seg = prob_r;
   a.rows = prob_n; a.N = prob_m; a.K = prob_k;
   a.grouped = groupsize == 128;
   a.scales = (const __half*)s;
   a.y = (__half*)C;
-  if (ksplit != nullptr) {
-    a.ksplit_cnt = (int*)ksplit;
-    a.ksplit_buf = (float*)((uint8_t*)ksplit + 512);
-  }
   // The tensor maps need a row bound; the reference signature has no delta count, so the maps
   // cover the largest index space a 32-bit row coordinate allows and the ids are trusted as the
   // reference trusts them.
@@ -270,7 +265,21 @@ static int sbmm_segments(const void* A, const void* B, const void* meta, void* C
   GemmCall c{A, B, meta, s, max_d, groupsize, dev, sms, (cudaStream_t)stream};
   a.num_deltas = max_d;
   const int avg = (prob_n + prob_r - 1) / prob_r;
-  return gemm_dispatch(c, a, gemm_tile_tokens(avg));
+  const int tt = tile_tokens != 0 ? tile_tokens : gemm_tile_tokens(avg);
+  // A launch takes at most kMaxSegments segments (its prefix table lives in shared memory): longer
+  // lists go out in several launches, which write disjoint rows.  The tail K split needs the whole
+  // list in one launch (its counters are per launch).
+  for (int r0 = 0; r0 < prob_r; r0 += kMaxSegments) {
+    a.seg_delta = (const int*)indices + r0; a.seg_start = (const int*)starts + r0; a.seg_count = (const int*)counts + r0;
+    a.n_seg = prob_r - r0 < kMaxSegments ? prob_r - r0 : kMaxSegments;
+    if (ksplit != nullptr && prob_r <= kMaxSegments) {
+      a.ksplit_cnt = (int*)ksplit;
+      a.ksplit_buf = (float*)((uint8_t*)ksplit + 512);
+    }
+    const int r = gemm_dispatch(c, a, tt);
+    if (r != TRB_OK) return r;
+  }
+  return TRB_OK;
 }
 
 extern "C" int trb_sbmm_2_4_ksplit(const void* A, const void* B, const void* meta, void* C, const void* s,
@@ -304,7 +313,7 @@ extern "C" int trb_bmm_2_4(const void* A, const void* B, const void* meta, void*
   a.scales = (const __half*)s;
   a.y = (__half*)C;
   GemmCall c{A, B, meta, s, prob_n, groupsize, dev, sms, (cudaStream_t)stream};
-  return gemm_dispatch(c, a, 8);
+  return gemm_dispatch(c, a, kSmallTile);
 }
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -315,14 +324,23 @@ constexpr size_t kCounterBytes = 1024;
 constexpr int kKsplitCntOffset = 64;
 static_assert(kKsplitCntOffset * 4 + kKsplitItems * 4 <= (int)kCounterBytes, "counters fit the scratch head");
 
+// Capacity of the two tile lists the router fills: tiles of at most kSmallTile tokens for segments of
+// at most kSmallSegMax tokens, tiles of kBigTile tokens for the longer ones.
+static size_t small_tile_capacity(int num_tokens, int num_deltas) {
+  return (size_t)trb_route_max_tiles(num_tokens, num_deltas, 8);
+}
+static size_t big_tile_capacity(int num_tokens) {
+  return (size_t)(num_tokens / kBigTile + num_tokens / (kSmallSegMax + 1) + 1);
+}
+
 // The least scratch the indexed path works with (no tail K split).
 static size_t indexed_scratch_min(int num_tokens, int prob_k, int num_deltas) {
   if (num_tokens <= 0 || prob_k <= 0 || num_deltas <= 0) return kCounterBytes;
-  const size_t tiles = (size_t)trb_route_max_tiles(num_tokens, num_deltas, 8);
-  size_t b = kCounterBytes;                                // counters
-  b += align_up((size_t)num_tokens * 4, 256);              // perm
-  b += 3 * align_up(tiles * 4, 256);                       // tile lists
-  b += align_up((size_t)num_tokens * prob_k * 2, 256);     // gathered activations
+  size_t b = kCounterBytes;                                                      // counters
+  b += align_up((size_t)num_tokens * 4, 256);                                    // perm
+  b += 3 * align_up(small_tile_capacity(num_tokens, num_deltas) * 4, 256);       // tile list, small segments
+  b += 3 * align_up(big_tile_capacity(num_tokens) * 4, 256);                     // tile list, large segments
+  b += align_up((size_t)num_tokens * prob_k * 2, 256);                           // gathered activations
   return b;
 }
 
@@ -336,12 +354,17 @@ extern "C" size_t trb_sbmm_indexed_scratch_bytes(int num_tokens, int prob_k, int
 }
 
 namespace trb {
-// Router + row gather + grouped kernel.  `src` says where the ids come from; num_tokens counts the
+// Router + row gather + grouped kernels.  `src` says where the ids come from; num_tokens counts the
 // rows of x and y.  mode: 0 = overwrite rows that have a delta and zero the others, 1 = accumulate,
-// 2 = overwrite rows that have a delta and leave the others untouched.  tile_tokens: 0 = choose.
+// 2 = overwrite rows that have a delta and leave the others untouched.
+// The router cuts every segment into tiles that fit its own token count (the reference chooses its
+// tile per delta the same way, triteia/csrc/ops/triteia_nm_sbmm.cu:756-762): segments of up to
+// kSmallSegMax tokens go to the mma.sp kernel in tiles of 8, 16 or 32 tokens, longer ones to the
+// tcgen05 kernel in tiles of 256.  Both lists are consumed without the host knowing their lengths;
+// a launch whose list is empty ends at once.
 int sbmm_indexed_impl(const void* x, const void* qweights, const void* metas, const void* scales, const RouteSrc& src,
                       void* y, int num_tokens, int prob_m, int prob_k, int num_deltas, int groupsize, int mode,
-                      int tile_tokens, void* scratch, size_t scratch_bytes, int dev, cudaStream_t stream,
+                      void* scratch, size_t scratch_bytes, int dev, cudaStream_t stream,
                       const void* y_peers = nullptr, int chunk_rows = 0) {
   if (num_deltas <= 0) return TRB_ERR_BAD_ARG;
   const int rc = check_common(x, qweights, metas, y, scales, prob_m, num_tokens, prob_k, groupsize);
@@ -352,43 +375,54 @@ int sbmm_indexed_impl(const void* x, const void* qweights, const void* metas, co
   if (scratch_bytes < min_bytes) return TRB_ERR_SCRATCH;
   if (cudaSetDevice(dev) != cudaSuccess) return TRB_ERR_CUDA;
 
-  const int segs = num_tokens < num_deltas ? num_tokens : num_deltas;
-  int tt = tile_tokens;
-  if (tt == 0) tt = gemm_tile_tokens((num_tokens + segs - 1) / segs);
-  if (y_peers && tt > 64) tt = 64;   // the peer-store epilogue exists in the mma.sp kernel only
-  if (tt != 8 && tt != 16 && tt != 32 && tt != 64 && tt != 256) return TRB_ERR_KERN_SHAPE;
-  const int max_tiles = trb_route_max_tiles(num_tokens, num_deltas, tt);
-  if (max_tiles > kMaxSegments) return TRB_ERR_KERN_SHAPE;
-  const size_t tiles8 = (size_t)trb_route_max_tiles(num_tokens, num_deltas, 8);
+  // The peer-store epilogue exists in the mma.sp kernel only; the tcgen05 kernel writes 16-byte pieces.
+  const bool use_big = y_peers == nullptr && num_tokens > kSmallSegMax && (prob_m & 7) == 0;
+  const size_t cap_small = small_tile_capacity(num_tokens, num_deltas), cap_big = big_tile_capacity(num_tokens);
 
   uint8_t* p = (uint8_t*)scratch;
   int* counters = (int*)p; p += kCounterBytes;
-  // Tail K split of the 8-token-tile kernel: only with room for its partial tiles behind the rest.
-  const bool ksplit = tt == 8 && scratch_bytes >= min_bytes + kKsplitBufBytes;
+  // Tail K split of the mma.sp kernel: only with room for its partial tiles behind the rest.
+  const bool ksplit = scratch_bytes >= min_bytes + kKsplitBufBytes;
   int* perm = (int*)p; p += align_up((size_t)num_tokens * 4, 256);
-  int* tile_delta = (int*)p; p += align_up(tiles8 * 4, 256);
-  int* tile_start = (int*)p; p += align_up(tiles8 * 4, 256);
-  int* tile_count = (int*)p; p += align_up(tiles8 * 4, 256);
+  int* tile_delta = (int*)p; p += align_up(cap_small * 4, 256);
+  int* tile_start = (int*)p; p += align_up(cap_small * 4, 256);
+  int* tile_count = (int*)p; p += align_up(cap_small * 4, 256);
+  RouteBig big{};
+  big.small_max = kSmallSegMax;
+  big.tt_big = kBigTile;
+  big.tile_delta = (int*)p; p += align_up(cap_big * 4, 256);
+  big.tile_start = (int*)p; p += align_up(cap_big * 4, 256);
+  big.tile_count = (int*)p; p += align_up(cap_big * 4, 256);
   void* x_sorted = p;
 
-  int r = route_launch_src(src, num_tokens, num_deltas, tt, perm, nullptr, nullptr, nullptr, tile_delta, tile_start,
-                           tile_count, counters, nullptr, 0, nullptr, stream);
+  int r = route_launch_src(src, num_tokens, num_deltas, kSmallTile, perm, nullptr, nullptr, nullptr, tile_delta,
+                           tile_start, tile_count, counters, nullptr, 0, nullptr, stream, use_big ? &big : nullptr);
   if (r != TRB_OK) return r;
   r = gather_launch(x, perm, counters, x_sorted, y, num_tokens, prob_k, prob_m, mode == 0 ? 1 : 0, stream,
                     ksplit ? counters + kKsplitCntOffset : nullptr, kKsplitItems);
   if (r != TRB_OK) return r;
 
   GemmArgs a{};
-  a.mode = kSegList;
-  a.seg_delta = tile_delta; a.seg_start = tile_start; a.seg_count = tile_count;
-  a.n_seg_ptr = counters + 1;
-  a.n_seg = max_tiles;
+  a.mode = kSegTiles;
   a.rows = num_tokens; a.N = prob_m; a.K = prob_k; a.num_deltas = num_deltas;
   a.grouped = groupsize == 128;
   a.scales = (const __half*)scales;
   a.y = (__half*)y;
   a.row_map = perm;
   a.accumulate = mode == 1;
+  GemmCall c{x_sorted, qweights, metas, scales, num_deltas, groupsize, dev, -1, stream};
+  if (use_big) {
+    // First the large segments (an empty list is the common case at decode sizes: its CTAs are
+    // resident before the gather ends and leave at once), then the small ones.
+    a.seg_delta = big.tile_delta; a.seg_start = big.tile_start; a.seg_count = big.tile_count;
+    a.n_seg_ptr = counters + 4;
+    a.n_seg = (int)cap_big;
+    r = gemm_dispatch(c, a, kBigTile);
+    if (r != TRB_OK) return r;
+  }
+  a.seg_delta = tile_delta; a.seg_start = tile_start; a.seg_count = tile_count;
+  a.n_seg_ptr = counters + 1;
+  a.n_seg = (int)cap_small;
   a.y_peers = (__half* const*)y_peers;
   a.xchg = src.chunk_base;
   a.xchg_row_bytes = src.row_bytes;
@@ -397,8 +431,7 @@ int sbmm_indexed_impl(const void* x, const void* qweights, const void* metas, co
     a.ksplit_cnt = counters + kKsplitCntOffset;
     a.ksplit_buf = (float*)((uint8_t*)scratch + min_bytes);
   }
-  GemmCall c{x_sorted, qweights, metas, scales, num_deltas, groupsize, dev, -1, stream};
-  return gemm_dispatch(c, a, tt);
+  return gemm_dispatch(c, a, kSmallTile);
 }
 }  // namespace trb
 
@@ -411,7 +444,7 @@ extern "C" int trb_sbmm_indexed(const void* x, const void* qweights, const void*
   src.indices = (const int*)indices;
   src.id_offset = index_offset;
   return sbmm_indexed_impl(x, qweights, metas, scales, src, y, num_tokens, prob_m, prob_k, num_deltas, groupsize,
-                           accumulate ? 1 : 0, 0, scratch, scratch_bytes, dev, (cudaStream_t)stream_v);
+                           accumulate ? 1 : 0, scratch, scratch_bytes, dev, (cudaStream_t)stream_v);
 }
 
 // Owner-side step of the sharded path: the received exchange buffer (world chunks of cap + 1 rows of K
@@ -434,11 +467,8 @@ extern "C" int trb_shard_compute(const void* recv_buf, const void* qweights, con
   src.chunk_base = (const unsigned char*)recv_buf;
   src.cap = cap;
   src.row_bytes = (long long)prob_k * 2;
-  // Tile size from the tokens a rank expects (cap per rank on average), not from the padded row count.
-  const int segs = cap < num_local_deltas ? cap : num_local_deltas;
-  const int tt = gemm_tile_tokens((cap + segs - 1) / (segs > 0 ? segs : 1));
   return sbmm_indexed_impl(recv_buf, qweights, metas, scales, src, y_work ? y_work : (void*)recv_buf, (int)rows, prob_m, prob_k, num_local_deltas,
-                           groupsize, 2, tt, scratch, scratch_bytes, dev, (cudaStream_t)stream_v, peer_out_ptrs, cap + 1);
+                           groupsize, 2, scratch, scratch_bytes, dev, (cudaStream_t)stream_v, peer_out_ptrs, cap + 1);
 }
 
 extern "C" int trb_route(const void* indices, int num_tokens, int num_deltas, int tile_tokens, int index_offset,

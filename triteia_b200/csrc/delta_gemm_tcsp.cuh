@@ -222,7 +222,7 @@ delta_gemm_tcsp_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
   }
   pdl_wait();   // everything below reads what the kernels launched before this one wrote
   n_seg = a.n_seg_ptr ? *a.n_seg_ptr : a.n_seg;
-  n_seg = max(0, min(n_seg, kMaxSegments));
+  n_seg = max(0, min(n_seg, a.mode == kSegTiles ? a.n_seg : kMaxSegments));
   int total_tiles;
   if (a.mode == kSegList) {
     if (warp == 0) {
@@ -251,7 +251,7 @@ delta_gemm_tcsp_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
   if constexpr (PAIR) cluster_sync_all();     // both CTAs' barriers exist before any remote arrive
   tc_fence_after();
   if (a.mode == kSegList) total_tiles = prefix[n_seg];
-  else total_tiles = a.mode == kSegSingle ? (a.rows + Cfg::TT - 1) / Cfg::TT : a.rows;
+  else total_tiles = a.mode == kSegTiles ? n_seg : (a.mode == kSegSingle ? (a.rows + Cfg::TT - 1) / Cfg::TT : a.rows);
   const uint32_t tmem_base = *tmem_slot;
 
   const int n_stripes = (a.N + Cfg::SW * 64 - 1) / (Cfg::SW * 64);

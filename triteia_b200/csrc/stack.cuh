@@ -61,7 +61,10 @@ extern "C" int trb_row_checksum(const void* y, void* sums, int rows, int prob_m,
 // host cost per launch is a few microseconds (a Python call per launch costs more than most of
 // these kernels run).  Rows are grouped by (segment size class, delta id); every class is a
 // contiguous row range with its own segment list and gets its own launch per linear, so the
-// grouped kernel picks the token tile that fits the class.  After each linear its output is
+// grouped kernel that fits the class runs (class_tile[c]: 32 = the mma.sp kernel with tiles of 8, 16
+// or 32 tokens chosen per segment, 256 = the tcgen05 kernel).  `ksplit` (optional): working memory
+// of trb_sbmm_ksplit_bytes() bytes for the tail K split of small launches, first 512 bytes zero on
+// entry (and again on exit).  After each linear its output is
 // folded into the per-row checksum.  Arrays are host arrays; the pointers in them are device
 // pointers.  x_of[i] / y_of[i]: grouped activations [rows, k[i]] and output buffer [rows, n[i]]
 // of linear i (outputs of the same width may share a buffer: the checksum is taken before the
@@ -70,12 +73,13 @@ extern "C" int trb_stack_pass(int n_linears, const void* const* q, const void* c
                               const int* k, const int* n, const void* const* x_of, void* const* y_of,
                               int n_classes, const int* class_row0, const int* class_rows,
                               const void* const* class_ids, const void* const* class_starts,
-                              const void* const* class_counts, const int* class_segs, void* checksum, int rows,
-                              int groupsize, int dev, void* stream) {
+                              const void* const* class_counts, const int* class_segs, const int* class_tile,
+                              void* checksum, int rows, int groupsize, void* ksplit, size_t ksplit_bytes, int dev,
+                              void* stream) {
   if (n_linears <= 0 || rows <= 0) return TRB_OK;
   if (!q || !meta || !s || !k || !n || !x_of || !y_of || !checksum) return TRB_ERR_BAD_ARG;
   if (n_classes < 0 || (n_classes > 0 && (!class_row0 || !class_rows || !class_ids || !class_starts ||
-                                          !class_counts || !class_segs)))
+                                          !class_counts || !class_segs || !class_tile)))
     return TRB_ERR_BAD_ARG;
   for (int c = 0; c < n_classes; ++c)
     if (class_row0[c] < 0 || class_rows[c] < 0 || class_row0[c] + class_rows[c] > rows) return TRB_ERR_BAD_ARG;
@@ -84,8 +88,11 @@ extern "C" int trb_stack_pass(int n_linears, const void* const* q, const void* c
       if (class_rows[c] == 0 || class_segs[c] == 0) continue;
       const __half* x = (const __half*)x_of[i] + (size_t)class_row0[c] * k[i];
       __half* y = (__half*)y_of[i] + (size_t)class_row0[c] * n[i];
-      const int rc = trb_sbmm_2_4(x, q[i], meta[i], y, s[i], class_ids[c], class_starts[c], class_counts[c], n[i],
-                                  class_rows[c], k[i], class_segs[c], nullptr, groupsize, dev, stream, -1, -1, -1, 0);
+      if (class_tile[c] != trb::kSmallTile && class_tile[c] != trb::kBigTile) return TRB_ERR_BAD_ARG;
+      const bool small = class_tile[c] == trb::kSmallTile;
+      const int rc = sbmm_segments(x, q[i], meta[i], y, s[i], class_ids[c], class_starts[c], class_counts[c], n[i],
+                                   class_rows[c], k[i], class_segs[c], groupsize, dev, stream, -1,
+                                   small ? ksplit : nullptr, small ? ksplit_bytes : 0, class_tile[c]);
       if (rc != TRB_OK) return rc;
     }
     const int rc = trb_row_checksum(y_of[i], checksum, rows, n[i], 1, dev, stream);

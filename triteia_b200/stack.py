@@ -51,10 +51,11 @@ class DeltaStackShard:
         self.layers = layers
         self.n_last = layers[-1][-1].n
 
-    # Segments are handled in size classes, one launch per class and linear, so that a hot delta's
-    # many tokens and a cold delta's single token each get a kernel tiled for them (token tiles of 8
-    # or 16-32 rows on mma.sp, 256 rows on tcgen05) instead of one tile size chosen for the average.
-    CLASS_BOUNDS = (8, 32)
+    # Segments are handled in two size classes, one launch per class and linear: segments of up to 64
+    # rows go to the mma.sp kernel (which tiles every segment by its own length: 8, 16 or 32 rows),
+    # longer ones to the tcgen05 kernel (256-row tiles).
+    CLASS_BOUNDS = (64,)
+    CLASS_TILES = (32, 256)
 
     def _plan(self, local_ids):
         """Rows ordered by (size class, delta id) and, per class, its row range and segment list."""
@@ -71,12 +72,20 @@ class DeltaStackShard:
         cls_sorted = cls_of[ids64][order]
         cls_rows = torch.bincount(cls_sorted, minlength=len(self.CLASS_BOUNDS) + 1).tolist()   # host read (once per pass)
         classes, at = [], 0
-        for n_rows in cls_rows:
+        for ci, n_rows in enumerate(cls_rows):
             if n_rows:
                 uniq, starts, cnts = _segments(ids_sorted[at:at + n_rows])   # sizes its outputs on the host
-                classes.append((at, n_rows, uniq, starts, cnts))
+                classes.append((at, n_rows, uniq, starts, cnts, self.CLASS_TILES[ci]))
             at += n_rows
         return order, classes
+
+    def _ksplit(self, dev):
+        """Working memory of the grouped kernel's tail K split (zero on entry, left zero by every launch)."""
+        from . import _lib
+
+        if getattr(self, "_ksplit_buf", None) is None or self._ksplit_buf.device != dev:
+            self._ksplit_buf = torch.zeros(_lib.lib.trb_sbmm_ksplit_bytes(), dtype=torch.uint8, device=dev)
+        return self._ksplit_buf
 
     def _static_arrays(self):
         """Host arrays of the per-linear device pointers and shapes (built once)."""
@@ -113,7 +122,8 @@ class DeltaStackShard:
             ci_c(*[c[0] for c in classes]), ci_c(*[c[1] for c in classes]),
             vp_c(*[_lib.ptr(c[2]) for c in classes]), vp_c(*[_lib.ptr(c[3]) for c in classes]),
             vp_c(*[_lib.ptr(c[4]) for c in classes]), ci_c(*[int(c[2].numel()) for c in classes]),
-            _lib.ptr(checksum), rows, groupsize, _lib.dev_of(checksum), _lib.stream_of(checksum))
+            ci_c(*[c[5] for c in classes]), _lib.ptr(checksum), rows, groupsize, _lib.ptr(self._ksplit(dev)),
+            _lib.lib.trb_sbmm_ksplit_bytes(), _lib.dev_of(checksum), _lib.stream_of(checksum))
         _lib.check(err, "stack_pass")
         y = ybuf[self.n_last]
         y_out = torch.empty_like(y)
