@@ -63,10 +63,11 @@ constexpr int kKsplitSlots = 148;             // pieces over all tail items
 constexpr int kKsplitSlotFloats = 256 * 8;    // one 8-token x 256-column fp32 tile
 constexpr size_t kKsplitBufBytes = (size_t)kKsplitSlots * kKsplitSlotFloats * 4;
 
-template <int NB_, int SW_, int KQ_, int KS_, int STAGES_>
+template <int NB_, int SW_, int KQ_, int KS_, int STAGES_, int MINNB_ = 1>
 struct GemmCfg {
   static constexpr int NB = NB_;          // token blocks of 8 in the largest tile; a tile's class (1, 2 or 4
                                           // blocks) follows from its row count, item by item
+  static constexpr int MINNB = MINNB_;    // smallest class compiled in: shorter tiles run as this class
   static constexpr int SW = SW_;          // 64-column blocks per stripe
   static constexpr int KQ = KQ_;          // warps sharing one column block (split over slabs)
   static constexpr int KS = KS_;          // 32-K slabs per pipeline stage
@@ -193,10 +194,356 @@ __device__ __forceinline__ WorkItem decode_item(const GemmArgs& a, const int* pr
   return w;
 }
 
-// Token blocks of the class that serves a tile of `valid` rows.
-__device__ __forceinline__ int tile_class(int valid) { return valid <= 8 ? 1 : (valid <= 16 ? 2 : 4); }
+// Token blocks of the class that serves a tile of `valid` rows in a kernel whose classes span [lo, hi].
+__device__ __forceinline__ int tile_class(int valid, int lo, int hi) {
+  const int c = valid <= 8 ? 1 : (valid <= 16 ? 2 : 4);
+  return c < lo ? lo : (c > hi ? hi : c);
+}
 
 template <int V> using IntTag = std::integral_constant<int, V>;
+
+// Where a consumer warp stands in the stage ring, carried from one work unit to the next.
+struct PipeState {
+  int st;
+  uint32_t phase;
+  bool first_item;
+};
+
+// One work unit of a consumer warp with a tile of NB token blocks (the tile's class).
+template <class Cfg, int NB>
+__device__ __forceinline__ PipeState run_unit_body(const GemmArgs& a, uint8_t* smem, PipeState ps, const WorkUnit wu,
+                                                   const WorkItem w) {
+  constexpr int SW = Cfg::SW, KQ = Cfg::KQ, KS = Cfg::KS, STAGES = Cfg::STAGES;
+  float* red = reinterpret_cast<float*>(smem + Cfg::RED_OFF);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::BAR_OFF);
+  uint64_t* empty_bar = full_bar + STAGES;
+  volatile int* dead = reinterpret_cast<volatile int*>(empty_bar + STAGES);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int slabs = a.K / 32;
+  const int cb = warp / KQ;   // column block of the stripe
+  const int kq = warp % KQ;   // which share of each stage's slabs
+  const int g8 = lane >> 2;   // quad index: MMA row group / token inside a block of 8
+  const int m4 = lane & 3;
+  constexpr int SPW = KS / KQ;  // slabs per warp per stage
+  const int box = cb / Cfg::QB, within = cb % Cfg::QB;
+  // Per-lane byte offsets inside a stage.
+  const uint32_t q_off = Cfg::Q_OFF + box * (KS * Cfg::QB * 512) + within * 512 + lane * 16 + kq * SPW * (Cfg::QB * 512);
+  const uint32_t m_off = Cfg::M_OFF + box * (KS * Cfg::QB * 256) + within * 256 + lane * 4 + kq * SPW * (Cfg::QB * 256);
+  const uint32_t s_off = Cfg::S_OFF + (cb / Cfg::SB) * Cfg::S_BOX_BYTES + ((kq * SPW) / 4) * (Cfg::SB * 128) +
+                         (cb % Cfg::SB) * 128 + g8 * 16;
+  const uint32_t smem_base = smem_u32(smem);
+  int st = ps.st;
+  uint32_t phase = ps.phase;
+  bool first_item = ps.first_item;
+  constexpr int JW = 4 / KQ;   // accumulator column pairs (j) that each partner warp finishes
+  // A warp's slabs of one stage lie inside one scale group, so their integer-level products are
+  // accumulated on their own and scaled once per stage in fp32 (small token tiles); large token
+  // tiles scale every weight in fp16 instead, which costs less than scaling many accumulators.
+  constexpr bool kPostScale = (NB <= 2);
+  constexpr bool kBulkLoad = (NB == 1);   // larger tiles would spill: they load slab by slab
+  constexpr uint32_t XBOX = NB * 1024;    // bytes of one 64-K activation box of this class
+  // ldmatrix row address of slab i of this warp: 16-byte chunk 4*slab + lane/8 of the stage's K
+  // range lives in activation box chunk/8 at swizzled chunk position (chunk%8) ^ (row%8).
+  uint32_t x_off[SPW];
+#pragma unroll
+  for (int i = 0; i < SPW; ++i) {
+    const int chunk = (kq * SPW + i) * 4 + (lane >> 3);
+    x_off[i] = Cfg::X_OFF + (chunk >> 3) * XBOX + (lane & 7) * 128 + ((((chunk & 7) ^ (lane & 7))) << 4);
+  }
+  const int nbv = (w.valid + 7) >> 3;
+  const bool col_ok = w.col0 + cb * 64 < a.N;
+
+  // Epilogue operands fetched now, used after the K loop: output rows of this lane's tokens and
+  // (per-channel mode) the scales of the two columns of each j this warp finishes.
+  const int colb = w.col0 + cb * 64 + g8 * 8;
+  int orow[NB][2];
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int t = nb * 8 + 2 * m4 + h;
+      int r = -1;
+      if (t < w.valid) {
+        r = w.row0 + t;
+        if (a.row_map) r = a.row_map[r];
+        if (r < 0 || r >= a.rows) r = -1;
+        if (a.y_peers && r >= 0) {
+          // (source rank << 20) | token row on that rank
+          const int pr = r / a.chunk_rows, pq = r - pr * a.chunk_rows;
+          const int* ids = reinterpret_cast<const int*>(a.xchg + ((long long)pr * a.chunk_rows + a.chunk_rows - 1) * a.xchg_row_bytes);
+          const int trow = ids[a.chunk_rows + pq];
+          r = (trow >= 0 && trow < a.chunk_rows - 1) ? ((pr << 20) | trow) : -1;   // a peer's output has chunk_rows - 1 rows
+        }
+      }
+      orow[nb][h] = r;
+    }
+  float sfa[JW], sfb[JW];
+#pragma unroll
+  for (int jj = 0; jj < JW; ++jj) {
+    sfa[jj] = 1.f;
+    sfb[jj] = 1.f;
+    if (!a.grouped && col_ok) {
+      const __half* sp = a.scales + (size_t)w.delta * a.N + colb + kq * JW + jj;
+      sfa[jj] = __half2float(sp[0]);
+      sfb[jj] = __half2float(sp[4]);
+    }
+  }
+
+  float acc[4][NB][4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[j][nb][c] = 0.f;
+
+  for (int ks = wu.ks0; ks < wu.ks1; ++ks) {
+    mbar_wait(&full_bar[st], phase, dead);
+    const uint32_t sb = smem_base + st * Cfg::STAGE_BYTES;
+
+    // One stage of this warp's slabs.  FULL: every slab of the stage exists (no per-slab test, so
+    // the four slabs form one straight-line block the compiler can interleave).  GROUPED selects
+    // the scale handling at compile time.
+    auto run_stage = [&](auto full_tag, auto grouped_tag) {
+      constexpr bool FULL = decltype(full_tag)::value;
+      constexpr bool GROUPED = decltype(grouped_tag)::value;
+      constexpr bool POST = kPostScale && GROUPED;
+      uint32_t scs[4] = {0, 0, 0, 0};
+      if constexpr (GROUPED) {
+        const uint4 sc = lds128(sb + s_off);
+        scs[0] = sc.x; scs[1] = sc.y; scs[2] = sc.z; scs[3] = sc.w;
+      }
+      float accg[4][NB][4];   // integer-level partial sums of this warp's slabs (POST)
+
+      // MMAs of one slab from registers: q4 = the lane's four weight words, e0/e1 = its two
+      // metadata words, bf = activation fragments per token block.
+      auto compute_slab = [&](int i, const uint4& q4, uint32_t e0, uint32_t e1, const uint32_t (&bf)[NB][4]) {
+        const uint32_t qs[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t lo0, hi0, lo1, hi1;
+          int4x4_to_half2x2(qs[j], lo0, hi0);
+          int4x4_to_half2x2(qs[j] >> 8, lo1, hi1);
+          if constexpr (GROUPED && !kPostScale) {
+            const uint32_t s0 = __byte_perm(scs[j], 0, 0x1010);  // scale of column j, both halves
+            const uint32_t s1 = __byte_perm(scs[j], 0, 0x3232);  // scale of column j + 4
+            lo0 = hmul2_u32(lo0, s0); hi0 = hmul2_u32(hi0, s0);
+            lo1 = hmul2_u32(lo1, s1); hi1 = hmul2_u32(hi1, s1);
+          }
+          const uint32_t e = (j < 2) ? e0 : e1;
+#pragma unroll
+          for (int nb = 0; nb < NB; ++nb) {
+            if (NB == 1 || nb < nbv) {
+              if constexpr (POST) {
+                if (i == 0) {
+                  if (j & 1) mma_sp_m16n8k32_zero<1>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
+                  else       mma_sp_m16n8k32_zero<0>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
+                } else {
+                  if (j & 1) mma_sp_m16n8k32<1>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
+                  else       mma_sp_m16n8k32<0>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
+                }
+              } else {
+                if (j & 1) mma_sp_m16n8k32<1>(acc[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
+                else       mma_sp_m16n8k32<0>(acc[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
+              }
+            }
+          }
+        }
+      };
+
+      if constexpr (kBulkLoad) {
+        // Small token tiles: pull the warp's whole share of the stage into registers, hand the
+        // stage back to the producer at once (the arrive is a release: the loads above are
+        // performed before it is observed), then do the math from registers.
+        uint4 q4[SPW];
+        uint32_t e0[SPW], e1[SPW], bf[SPW][NB][4];
+#pragma unroll
+        for (int i = 0; i < SPW; ++i) {
+          if (FULL || ks * KS + kq * SPW + i < slabs) {
+            q4[i] = lds128(sb + q_off + i * (Cfg::QB * 512));
+            e0[i] = lds32(sb + m_off + i * (Cfg::QB * 256));
+            e1[i] = lds32(sb + m_off + i * (Cfg::QB * 256) + 128);
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb)
+              if (NB == 1 || nb < nbv) ldmatrix_x4(bf[i][nb], sb + x_off[i] + nb * 1024);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[st]);
+#pragma unroll
+        for (int i = 0; i < SPW; ++i)
+          if (FULL || ks * KS + kq * SPW + i < slabs) compute_slab(i, q4[i], e0[i], e1[i], bf[i]);
+      } else {
+        // 32-token tiles keep 64 accumulators per lane: their slabs run one after the other.
+        constexpr int kSlabUnroll = NB >= 4 ? 1 : SPW;
+#pragma unroll kSlabUnroll
+        for (int i = 0; i < SPW; ++i) {
+          if (FULL || ks * KS + kq * SPW + i < slabs) {
+            const uint4 q4 = lds128(sb + q_off + i * (Cfg::QB * 512));
+            const uint32_t e0 = lds32(sb + m_off + i * (Cfg::QB * 256));
+            const uint32_t e1 = lds32(sb + m_off + i * (Cfg::QB * 256) + 128);
+            uint32_t bf[NB][4];
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb)
+              if (NB == 1 || nb < nbv) ldmatrix_x4(bf[nb], sb + x_off[i] + nb * 1024);
+            compute_slab(i, q4, e0, e1, bf);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[st]);
+      }
+      // A scale group is whole or absent (K is a multiple of 128): slab 0 of the warp decides.
+      if (POST && (FULL || ks * KS + kq * SPW < slabs)) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&scs[j]));
+#pragma unroll
+          for (int nb = 0; nb < NB; ++nb) {
+            if (NB == 1 || nb < nbv) {
+              acc[j][nb][0] = fmaf(accg[j][nb][0], sf.x, acc[j][nb][0]);
+              acc[j][nb][1] = fmaf(accg[j][nb][1], sf.x, acc[j][nb][1]);
+              acc[j][nb][2] = fmaf(accg[j][nb][2], sf.y, acc[j][nb][2]);
+              acc[j][nb][3] = fmaf(accg[j][nb][3], sf.y, acc[j][nb][3]);
+            }
+          }
+        }
+      }
+    };
+    if (col_ok) {
+      const bool full = (ks + 1) * KS <= slabs;
+      if (a.grouped) {
+        if (full) run_stage(std::true_type{}, std::true_type{});
+        else run_stage(std::false_type{}, std::true_type{});
+      } else {
+        if (full) run_stage(std::true_type{}, std::false_type{});
+        else run_stage(std::false_type{}, std::false_type{});
+      }
+    } else {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[st]);
+    }
+    if (++st == STAGES) { st = 0; phase ^= 1; }
+  }
+
+  // Partner warps (same column block) own identical fragments.  Each of them finishes the j's
+  // [kq*JW, (kq+1)*JW): it hands its partial sums of the other j's to their owners through shared
+  // memory, adds the partners' partials to its own in a fixed order, and writes its columns.
+  // The exchange runs in rounds of at most two token blocks (the buffer holds that much).
+  // Barrier 2 (before the stores) keeps a round's partials until every reader of the previous
+  // round is done; barrier 1 separates stores from loads.
+  if constexpr (KQ > 1) {
+    constexpr int CT = Cfg::CTHREADS;
+    constexpr int LANES = SW * 32;
+    constexpr int NBH = NB < 2 ? NB : 2;
+#pragma unroll
+    for (int h0 = 0; h0 < NB; h0 += NBH) {
+      if (!first_item) named_bar_sync(2, CT);
+      first_item = false;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int owner = j / JW;
+        if (owner != kq) {
+          const int slot = kq < owner ? kq : kq - 1;
+          float* dst = red + (((owner * (KQ - 1) + slot) * JW + (j % JW)) * NBH * 4) * LANES + cb * 32 + lane;
+#pragma unroll
+          for (int nb = 0; nb < NBH; ++nb)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) dst[(nb * 4 + c) * LANES] = acc[j][h0 + nb][c];
+        }
+      }
+      named_bar_sync(1, CT);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (j / JW == kq) {
+#pragma unroll
+          for (int slot = 0; slot < KQ - 1; ++slot) {
+            const float* src = red + (((kq * (KQ - 1) + slot) * JW + (j % JW)) * NBH * 4) * LANES + cb * 32 + lane;
+#pragma unroll
+            for (int nb = 0; nb < NBH; ++nb)
+#pragma unroll
+              for (int c = 0; c < 4; ++c) acc[j][h0 + nb][c] += src[(nb * 4 + c) * LANES];
+          }
+        }
+      }
+    }
+  }
+
+  // A piece of a K-split item: park the fp32 partial tile, count in; all but the last arriver are
+  // done with the item.  The last arriver replaces its registers with the sum of every piece's
+  // tile in piece order (its own included), so the result does not depend on who came last.
+  if constexpr (NB == 1) {
+    if (wu.parts > 1) {
+      // slot of piece p of tail item t: ((t * parts + p) * 2 + jj) * CT float4s, this thread's at + tid
+      float4* tile = reinterpret_cast<float4*>(a.ksplit_buf) + (size_t)(wu.tail * wu.parts) * (kKsplitSlotFloats / 4) +
+                     (warp * 32 + lane);
+      // (static accumulator indices under a predicate, as in the epilogue: a run-time index would
+      // push the accumulators out of registers)
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (j / JW == kq)
+          __stcg(tile + (wu.part * 2 + j % JW) * Cfg::CTHREADS,
+                 make_float4(acc[j][0][0], acc[j][0][1], acc[j][0][2], acc[j][0][3]));
+      // One acq_rel atomic by one thread between two CTA barriers orders every thread's tile
+      // stores before the count (release, cumulative over the barrier) and every thread's tile
+      // loads after it (acquire).  A tail piece is a CTA's last unit: the flag word is used once.
+      named_bar_sync(3, Cfg::CTHREADS);
+      volatile int* flag = dead + 1;
+      if (warp == 0 && lane == 0) {
+        int old;
+        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(a.ksplit_cnt + wu.tail) : "memory");
+        *flag = old;
+      }
+      named_bar_sync(3, Cfg::CTHREADS);
+      if (*flag != wu.parts - 1) return PipeState{st, phase, first_item};
+      if (warp == 0 && lane == 0) a.ksplit_cnt[wu.tail] = 0;   // back to zero for the next launch
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (j / JW == kq) {
+          float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+          for (int p = 0; p < wu.parts; ++p) {
+            const float4 v = __ldcg(tile + (p * 2 + j % JW) * Cfg::CTHREADS);
+            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+          }
+          acc[j][0][0] = sum.x; acc[j][0][1] = sum.y; acc[j][0][2] = sum.z; acc[j][0][3] = sum.w;
+        }
+      }
+    }
+  }
+  if (col_ok) {
+    // acc[j][nb][h] is (column colb + j, token nb*8 + 2*m4 + h); acc[j][nb][2 + h] is column colb + 4 + j.
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (j / JW == kq) {
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int r = orow[nb][h];
+            if (r >= 0 && (NB == 1 || nb < nbv)) {
+              __half* yp;
+              if (a.y_peers) {
+                yp = a.y_peers[r >> 20] + (size_t)(r & ((1 << 20) - 1)) * a.N + colb + j;
+              } else {
+                yp = a.y + (size_t)r * a.N + colb + j;
+              }
+              float va = acc[j][nb][h] * sfa[j % JW];
+              float vb = acc[j][nb][2 + h] * sfb[j % JW];
+              if (a.accumulate) {
+                va += __half2float(yp[0]);
+                vb += __half2float(yp[4]);
+              }
+              yp[0] = __float2half_rn(va);
+              yp[4] = __float2half_rn(vb);
+            }
+          }
+        }
+      }
+    }
+  }
+  return PipeState{st, phase, first_item};
+}
 
 // tm_x1 / tm_x2 / tm_x4: the activation matrix with boxes of 8, 16 and 32 rows (one per tile class).
 template <class Cfg>
@@ -204,8 +551,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1)
 delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ CUtensorMap tm_x2,
                   const __grid_constant__ CUtensorMap tm_x4, const __grid_constant__ CUtensorMap tm_q,
                   const __grid_constant__ CUtensorMap tm_m, const __grid_constant__ CUtensorMap tm_s,
-                  const GemmArgs a) {
-  constexpr int NBMAX = Cfg::NB, SW = Cfg::SW, KQ = Cfg::KQ, KS = Cfg::KS, STAGES = Cfg::STAGES;
+                  const __grid_constant__ GemmArgs a) {
+  constexpr int NBMAX = Cfg::NB, SW = Cfg::SW, KS = Cfg::KS, STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* red = reinterpret_cast<float*>(smem + Cfg::RED_OFF);
@@ -274,7 +621,7 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_consta
   // tail is done whole by the CTA that holds its piece 0.  Returns false when this CTA has nothing to do.
   auto settle_unit = [&](WorkUnit& wu, const WorkItem& w) -> bool {
     if (!w.ok) return false;
-    if (wu.parts > 1 && tile_class(w.valid) != 1) {
+    if (wu.parts > 1 && tile_class(w.valid, Cfg::MINNB, NBMAX) != 1) {
       if (wu.part != 0) return false;
       wu.ks0 = 0; wu.ks1 = k_stages; wu.parts = 1;
     }
@@ -299,7 +646,7 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_consta
         WorkUnit wu = work_unit(split, u, (int)gridDim.x, (int)blockIdx.x, k_stages);
         const WorkItem w = decode_item<Cfg>(a, prefix, n_seg, n_stripes, wu.item);
         if (!settle_unit(wu, w)) continue;
-        const int cls = NBMAX == 1 ? 1 : tile_class(w.valid);
+        const int cls = tile_class(w.valid, Cfg::MINNB, NBMAX);
         const CUtensorMap* tmx = cls == 1 ? &tm_x1 : (cls == 2 ? &tm_x2 : &tm_x4);
         const uint32_t box_bytes = (uint32_t)cls * 1024u;          // 8 * cls rows of 128 bytes
         const uint32_t stage_tx = Cfg::NXBOX * box_bytes + weight_tx;
@@ -333,335 +680,9 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_consta
   }
 
   // ------------------------------ consumers ------------------------------
-  const int cb = warp / KQ;   // column block of the stripe
-  const int kq = warp % KQ;   // which share of each stage's slabs
-  const int g8 = lane >> 2;   // quad index: MMA row group / token inside a block of 8
-  const int m4 = lane & 3;
-  constexpr int SPW = KS / KQ;  // slabs per warp per stage
-  const int box = cb / Cfg::QB, within = cb % Cfg::QB;
-  // Per-lane byte offsets inside a stage, fixed for the whole kernel.
-  const uint32_t q_off = Cfg::Q_OFF + box * (KS * Cfg::QB * 512) + within * 512 + lane * 16 + kq * SPW * (Cfg::QB * 512);
-  const uint32_t m_off = Cfg::M_OFF + box * (KS * Cfg::QB * 256) + within * 256 + lane * 4 + kq * SPW * (Cfg::QB * 256);
-  const uint32_t s_off = Cfg::S_OFF + (cb / Cfg::SB) * Cfg::S_BOX_BYTES + ((kq * SPW) / 4) * (Cfg::SB * 128) +
-                         (cb % Cfg::SB) * 128 + g8 * 16;
-  const uint32_t smem_base = smem_u32(smem);
-
-  int st = 0;
-  uint32_t phase = 0;
-  bool first_item = true;
-  constexpr int JW = 4 / KQ;   // accumulator column pairs (j) that each partner warp finishes
-
-  // One work unit with a tile of NB token blocks (the tile's class).
-  auto run_unit = [&](auto nb_tag, const WorkUnit& wu, const WorkItem& w) {
-    constexpr int NB = decltype(nb_tag)::value;
-    // A warp's slabs of one stage lie inside one scale group, so their integer-level products are
-    // accumulated on their own and scaled once per stage in fp32 (small token tiles); large token
-    // tiles scale every weight in fp16 instead, which costs less than scaling many accumulators.
-    constexpr bool kPostScale = (NB <= 2);
-    constexpr bool kBulkLoad = (NB == 1);   // larger tiles would spill: they load slab by slab
-    constexpr uint32_t XBOX = NB * 1024;    // bytes of one 64-K activation box of this class
-    // ldmatrix row address of slab i of this warp: 16-byte chunk 4*slab + lane/8 of the stage's K
-    // range lives in activation box chunk/8 at swizzled chunk position (chunk%8) ^ (row%8).
-    uint32_t x_off[SPW];
-#pragma unroll
-    for (int i = 0; i < SPW; ++i) {
-      const int chunk = (kq * SPW + i) * 4 + (lane >> 3);
-      x_off[i] = Cfg::X_OFF + (chunk >> 3) * XBOX + (lane & 7) * 128 + ((((chunk & 7) ^ (lane & 7))) << 4);
-    }
-    const int nbv = (w.valid + 7) >> 3;
-    const bool col_ok = w.col0 + cb * 64 < a.N;
-
-    // Epilogue operands fetched now, used after the K loop: output rows of this lane's tokens and
-    // (per-channel mode) the scales of the two columns of each j this warp finishes.
-    const int colb = w.col0 + cb * 64 + g8 * 8;
-    int orow[NB][2];
-#pragma unroll
-    for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int t = nb * 8 + 2 * m4 + h;
-        int r = -1;
-        if (t < w.valid) {
-          r = w.row0 + t;
-          if (a.row_map) r = a.row_map[r];
-          if (r < 0 || r >= a.rows) r = -1;
-          if (a.y_peers && r >= 0) {
-            // (source rank << 20) | token row on that rank
-            const int pr = r / a.chunk_rows, pq = r - pr * a.chunk_rows;
-            const int* ids = reinterpret_cast<const int*>(a.xchg + ((long long)pr * a.chunk_rows + a.chunk_rows - 1) * a.xchg_row_bytes);
-            const int trow = ids[a.chunk_rows + pq];
-            r = (trow >= 0 && trow < a.chunk_rows - 1) ? ((pr << 20) | trow) : -1;   // a peer's output has chunk_rows - 1 rows
-          }
-        }
-        orow[nb][h] = r;
-      }
-    float sfa[JW], sfb[JW];
-#pragma unroll
-    for (int jj = 0; jj < JW; ++jj) {
-      sfa[jj] = 1.f;
-      sfb[jj] = 1.f;
-      if (!a.grouped && col_ok) {
-        const __half* sp = a.scales + (size_t)w.delta * a.N + colb + kq * JW + jj;
-        sfa[jj] = __half2float(sp[0]);
-        sfb[jj] = __half2float(sp[4]);
-      }
-    }
-
-    float acc[4][NB][4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-#pragma unroll
-      for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) acc[j][nb][c] = 0.f;
-
-    for (int ks = wu.ks0; ks < wu.ks1; ++ks) {
-      mbar_wait(&full_bar[st], phase, dead);
-      const uint32_t sb = smem_base + st * Cfg::STAGE_BYTES;
-
-      // One stage of this warp's slabs.  FULL: every slab of the stage exists (no per-slab test, so
-      // the four slabs form one straight-line block the compiler can interleave).  GROUPED selects
-      // the scale handling at compile time.
-      auto run_stage = [&](auto full_tag, auto grouped_tag) {
-        constexpr bool FULL = decltype(full_tag)::value;
-        constexpr bool GROUPED = decltype(grouped_tag)::value;
-        constexpr bool POST = kPostScale && GROUPED;
-        uint32_t scs[4] = {0, 0, 0, 0};
-        if constexpr (GROUPED) {
-          const uint4 sc = lds128(sb + s_off);
-          scs[0] = sc.x; scs[1] = sc.y; scs[2] = sc.z; scs[3] = sc.w;
-        }
-        float accg[4][NB][4];   // integer-level partial sums of this warp's slabs (POST)
-
-        // MMAs of one slab from registers: q4 = the lane's four weight words, e0/e1 = its two
-        // metadata words, bf = activation fragments per token block.
-        auto compute_slab = [&](int i, const uint4& q4, uint32_t e0, uint32_t e1, const uint32_t (&bf)[NB][4]) {
-          const uint32_t qs[4] = {q4.x, q4.y, q4.z, q4.w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint32_t lo0, hi0, lo1, hi1;
-            int4x4_to_half2x2(qs[j], lo0, hi0);
-            int4x4_to_half2x2(qs[j] >> 8, lo1, hi1);
-            if constexpr (GROUPED && !kPostScale) {
-              const uint32_t s0 = __byte_perm(scs[j], 0, 0x1010);  // scale of column j, both halves
-              const uint32_t s1 = __byte_perm(scs[j], 0, 0x3232);  // scale of column j + 4
-              lo0 = hmul2_u32(lo0, s0); hi0 = hmul2_u32(hi0, s0);
-              lo1 = hmul2_u32(lo1, s1); hi1 = hmul2_u32(hi1, s1);
-            }
-            const uint32_t e = (j < 2) ? e0 : e1;
-#pragma unroll
-            for (int nb = 0; nb < NB; ++nb) {
-              if (NB == 1 || nb < nbv) {
-                if constexpr (POST) {
-                  if (i == 0) {
-                    if (j & 1) mma_sp_m16n8k32_zero<1>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
-                    else       mma_sp_m16n8k32_zero<0>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
-                  } else {
-                    if (j & 1) mma_sp_m16n8k32<1>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
-                    else       mma_sp_m16n8k32<0>(accg[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
-                  }
-                } else {
-                  if (j & 1) mma_sp_m16n8k32<1>(acc[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
-                  else       mma_sp_m16n8k32<0>(acc[j][nb], lo0, lo1, hi0, hi1, bf[nb], e);
-                }
-              }
-            }
-          }
-        };
-
-        if constexpr (kBulkLoad) {
-          // Small token tiles: pull the warp's whole share of the stage into registers, hand the
-          // stage back to the producer at once (the arrive is a release: the loads above are
-          // performed before it is observed), then do the math from registers.
-          uint4 q4[SPW];
-          uint32_t e0[SPW], e1[SPW], bf[SPW][NB][4];
-#pragma unroll
-          for (int i = 0; i < SPW; ++i) {
-            if (FULL || ks * KS + kq * SPW + i < slabs) {
-              q4[i] = lds128(sb + q_off + i * (Cfg::QB * 512));
-              e0[i] = lds32(sb + m_off + i * (Cfg::QB * 256));
-              e1[i] = lds32(sb + m_off + i * (Cfg::QB * 256) + 128);
-#pragma unroll
-              for (int nb = 0; nb < NB; ++nb)
-                if (NB == 1 || nb < nbv) ldmatrix_x4(bf[i][nb], sb + x_off[i] + nb * 1024);
-            }
-          }
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&empty_bar[st]);
-#pragma unroll
-          for (int i = 0; i < SPW; ++i)
-            if (FULL || ks * KS + kq * SPW + i < slabs) compute_slab(i, q4[i], e0[i], e1[i], bf[i]);
-        } else {
-          // 32-token tiles keep 64 accumulators per lane: their slabs run one after the other.
-          constexpr int kSlabUnroll = NB >= 4 ? 1 : SPW;
-#pragma unroll kSlabUnroll
-          for (int i = 0; i < SPW; ++i) {
-            if (FULL || ks * KS + kq * SPW + i < slabs) {
-              const uint4 q4 = lds128(sb + q_off + i * (Cfg::QB * 512));
-              const uint32_t e0 = lds32(sb + m_off + i * (Cfg::QB * 256));
-              const uint32_t e1 = lds32(sb + m_off + i * (Cfg::QB * 256) + 128);
-              uint32_t bf[NB][4];
-#pragma unroll
-              for (int nb = 0; nb < NB; ++nb)
-                if (NB == 1 || nb < nbv) ldmatrix_x4(bf[nb], sb + x_off[i] + nb * 1024);
-              compute_slab(i, q4, e0, e1, bf);
-            }
-          }
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&empty_bar[st]);
-        }
-        // A scale group is whole or absent (K is a multiple of 128): slab 0 of the warp decides.
-        if (POST && (FULL || ks * KS + kq * SPW < slabs)) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&scs[j]));
-#pragma unroll
-            for (int nb = 0; nb < NB; ++nb) {
-              if (NB == 1 || nb < nbv) {
-                acc[j][nb][0] = fmaf(accg[j][nb][0], sf.x, acc[j][nb][0]);
-                acc[j][nb][1] = fmaf(accg[j][nb][1], sf.x, acc[j][nb][1]);
-                acc[j][nb][2] = fmaf(accg[j][nb][2], sf.y, acc[j][nb][2]);
-                acc[j][nb][3] = fmaf(accg[j][nb][3], sf.y, acc[j][nb][3]);
-              }
-            }
-          }
-        }
-      };
-      if (col_ok) {
-        const bool full = (ks + 1) * KS <= slabs;
-        if (a.grouped) {
-          if (full) run_stage(std::true_type{}, std::true_type{});
-          else run_stage(std::false_type{}, std::true_type{});
-        } else {
-          if (full) run_stage(std::true_type{}, std::false_type{});
-          else run_stage(std::false_type{}, std::false_type{});
-        }
-      } else {
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty_bar[st]);
-      }
-      if (++st == STAGES) { st = 0; phase ^= 1; }
-    }
-
-    // Partner warps (same column block) own identical fragments.  Each of them finishes the j's
-    // [kq*JW, (kq+1)*JW): it hands its partial sums of the other j's to their owners through shared
-    // memory, adds the partners' partials to its own in a fixed order, and writes its columns.
-    // The exchange runs in rounds of at most two token blocks (the buffer holds that much).
-    // Barrier 2 (before the stores) keeps a round's partials until every reader of the previous
-    // round is done; barrier 1 separates stores from loads.
-    if constexpr (KQ > 1) {
-      constexpr int CT = Cfg::CTHREADS;
-      constexpr int LANES = SW * 32;
-      constexpr int NBH = NB < 2 ? NB : 2;
-#pragma unroll
-      for (int h0 = 0; h0 < NB; h0 += NBH) {
-        if (!first_item) named_bar_sync(2, CT);
-        first_item = false;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int owner = j / JW;
-          if (owner != kq) {
-            const int slot = kq < owner ? kq : kq - 1;
-            float* dst = red + (((owner * (KQ - 1) + slot) * JW + (j % JW)) * NBH * 4) * LANES + cb * 32 + lane;
-#pragma unroll
-            for (int nb = 0; nb < NBH; ++nb)
-#pragma unroll
-              for (int c = 0; c < 4; ++c) dst[(nb * 4 + c) * LANES] = acc[j][h0 + nb][c];
-          }
-        }
-        named_bar_sync(1, CT);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (j / JW == kq) {
-#pragma unroll
-            for (int slot = 0; slot < KQ - 1; ++slot) {
-              const float* src = red + (((kq * (KQ - 1) + slot) * JW + (j % JW)) * NBH * 4) * LANES + cb * 32 + lane;
-#pragma unroll
-              for (int nb = 0; nb < NBH; ++nb)
-#pragma unroll
-                for (int c = 0; c < 4; ++c) acc[j][h0 + nb][c] += src[(nb * 4 + c) * LANES];
-            }
-          }
-        }
-      }
-    }
-
-    // A piece of a K-split item: park the fp32 partial tile, count in; all but the last arriver are
-    // done with the item.  The last arriver replaces its registers with the sum of every piece's
-    // tile in piece order (its own included), so the result does not depend on who came last.
-    if constexpr (NB == 1) {
-      if (wu.parts > 1) {
-        // slot of piece p of tail item t: ((t * parts + p) * 2 + jj) * CT float4s, this thread's at + tid
-        float4* tile = reinterpret_cast<float4*>(a.ksplit_buf) + (size_t)(wu.tail * wu.parts) * (kKsplitSlotFloats / 4) +
-                       (warp * 32 + lane);
-        // (static accumulator indices under a predicate, as in the epilogue: a run-time index would
-        // push the accumulators out of registers)
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (j / JW == kq)
-            __stcg(tile + (wu.part * 2 + j % JW) * Cfg::CTHREADS,
-                   make_float4(acc[j][0][0], acc[j][0][1], acc[j][0][2], acc[j][0][3]));
-        // One acq_rel atomic by one thread between two CTA barriers orders every thread's tile
-        // stores before the count (release, cumulative over the barrier) and every thread's tile
-        // loads after it (acquire).  A tail piece is a CTA's last unit: the flag word is used once.
-        named_bar_sync(3, Cfg::CTHREADS);
-        volatile int* flag = dead + 1;
-        if (warp == 0 && lane == 0) {
-          int old;
-          asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(a.ksplit_cnt + wu.tail) : "memory");
-          *flag = old;
-        }
-        named_bar_sync(3, Cfg::CTHREADS);
-        if (*flag != wu.parts - 1) return;
-        if (warp == 0 && lane == 0) a.ksplit_cnt[wu.tail] = 0;   // back to zero for the next launch
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (j / JW == kq) {
-            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 1
-            for (int p = 0; p < wu.parts; ++p) {
-              const float4 v = __ldcg(tile + (p * 2 + j % JW) * Cfg::CTHREADS);
-              sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
-            }
-            acc[j][0][0] = sum.x; acc[j][0][1] = sum.y; acc[j][0][2] = sum.z; acc[j][0][3] = sum.w;
-          }
-        }
-      }
-    }
-    if (col_ok) {
-      // acc[j][nb][h] is (column colb + j, token nb*8 + 2*m4 + h); acc[j][nb][2 + h] is column colb + 4 + j.
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (j / JW == kq) {
-#pragma unroll
-          for (int nb = 0; nb < NB; ++nb) {
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              const int r = orow[nb][h];
-              if (r >= 0 && (NB == 1 || nb < nbv)) {
-                __half* yp;
-                if (a.y_peers) {
-                  yp = a.y_peers[r >> 20] + (size_t)(r & ((1 << 20) - 1)) * a.N + colb + j;
-                } else {
-                  yp = a.y + (size_t)r * a.N + colb + j;
-                }
-                float va = acc[j][nb][h] * sfa[j % JW];
-                float vb = acc[j][nb][2 + h] * sfb[j % JW];
-                if (a.accumulate) {
-                  va += __half2float(yp[0]);
-                  vb += __half2float(yp[4]);
-                }
-                yp[0] = __float2half_rn(va);
-                yp[4] = __float2half_rn(vb);
-              }
-            }
-          }
-        }
-      }
-    }
-  };
-
+  PipeState ps{0, 0u, true};
   WorkItem w_next{};
+
   if (split.units > 0)
     w_next = decode_item<Cfg>(a, prefix, n_seg, n_stripes,
                               work_unit(split, 0, (int)gridDim.x, (int)blockIdx.x, k_stages).item);
@@ -673,14 +694,14 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_consta
       w_next = decode_item<Cfg>(a, prefix, n_seg, n_stripes,
                                 work_unit(split, u + 1, (int)gridDim.x, (int)blockIdx.x, k_stages).item);
     if (!settle_unit(wu, w)) continue;
-    const int cls = NBMAX == 1 ? 1 : tile_class(w.valid);
-    if constexpr (NBMAX >= 4) {
-      if (cls == 4) { run_unit(IntTag<4>{}, wu, w); continue; }
+    const int cls = tile_class(w.valid, Cfg::MINNB, NBMAX);
+    if constexpr (NBMAX >= 4 && Cfg::MINNB <= 4) {
+      if (cls == 4) { ps = run_unit_body<Cfg, 4>(a, smem, ps, wu, w); continue; }
     }
-    if constexpr (NBMAX >= 2) {
-      if (cls == 2) { run_unit(IntTag<2>{}, wu, w); continue; }
+    if constexpr (NBMAX >= 2 && Cfg::MINNB <= 2) {
+      if (cls == 2) { ps = run_unit_body<Cfg, 2>(a, smem, ps, wu, w); continue; }
     }
-    run_unit(IntTag<1>{}, wu, w);
+    if constexpr (Cfg::MINNB <= 1) ps = run_unit_body<Cfg, 1>(a, smem, ps, wu, w);
   }
 }
 

@@ -86,15 +86,19 @@ __device__ __forceinline__ int route_bin(const RouteSrc& s, int raw, int D, bool
   return id >= D ? 0 : id + 1;
 }
 
-// Second tile list: with small_max > 0 a segment of more than small_max tokens leaves the first list
-// (tiles of TT tokens) and is cut into tiles of tt_big tokens in this one, so that small and large
-// segments each get the kernel that suits them (the reference picks its tile per delta from the
-// delta's token count, triteia/csrc/ops/triteia_nm_sbmm.cu:756-762).  counters[4] = its length.
-struct RouteBig {
-  int small_max, tt_big;
+// Tile lists by segment size.  With small_max > 0 a segment of more than small_max tokens leaves the
+// first list (tiles of TT tokens): up to mid_max tokens it is cut into tiles of tt_mid tokens in the
+// `mid` list, beyond that into tiles of tt_big tokens in the `big` list, so that every segment gets
+// the kernel and tile that suit its own token count (the reference picks its tile per delta the same
+// way, triteia/csrc/ops/triteia_nm_sbmm.cu:756-762).  counters[4], counters[5] = lengths of mid, big.
+struct RouteList {
   int* tile_delta;
   int* tile_start;
   int* tile_count;
+};
+struct RouteClasses {
+  int small_max, mid_max, tt_mid, tt_big;
+  RouteList mid, big;
 };
 
 __global__ void __launch_bounds__(kRouteThreads, 1)
@@ -102,7 +106,7 @@ route_kernel(const RouteSrc src, int T, int D, int W, int TT, int* __restrict__ 
              int* __restrict__ seg_delta, int* __restrict__ seg_start, int* __restrict__ seg_count,
              int* __restrict__ tile_delta, int* __restrict__ tile_start, int* __restrict__ tile_count,
              int* __restrict__ counters, int* __restrict__ slot_of, int slot_stride, int* __restrict__ bin_count,
-             const RouteBig big) {
+             const RouteClasses cl) {
   extern __shared__ int sm[];
   pdl_launch_dependents();
   const int bins = D + 1;             // bin 0 = id -1 (and out-of-range ids)
@@ -110,7 +114,8 @@ route_kernel(const RouteSrc src, int T, int D, int W, int TT, int* __restrict__ 
   int* bin_start = hist + bins * W;   // [bins + 1]
   int* seg_flag = bin_start + bins + 1;   // [bins]
   int* tile_cnt = seg_flag + bins;        // [bins]
-  int* tile_cnt2 = tile_cnt + bins;       // [bins]
+  int* tile_cnt2 = tile_cnt + bins;       // [bins] tiles in the mid list
+  int* tile_cnt3 = tile_cnt2 + bins;      // [bins] tiles in the big list
   __shared__ int warp_tot[33];
   __shared__ int n_invalid;
 
@@ -173,15 +178,18 @@ route_kernel(const RouteSrc src, int T, int D, int W, int TT, int* __restrict__ 
   for (int b = tid; b < bins; b += blockDim.x) {
     const int cnt = bin_start[b + 1] - bin_start[b];
     const bool is_seg = b >= 1 && cnt > 0;
-    const bool is_big = is_seg && big.small_max > 0 && cnt > big.small_max;
+    const bool leaves = is_seg && cl.small_max > 0 && cnt > cl.small_max;
+    const bool is_big = leaves && cnt > cl.mid_max;
     seg_flag[b] = is_seg ? 1 : 0;
-    tile_cnt[b] = (is_seg && !is_big) ? (cnt + TT - 1) / TT : 0;
-    tile_cnt2[b] = is_big ? (cnt + big.tt_big - 1) / big.tt_big : 0;
+    tile_cnt[b] = (is_seg && !leaves) ? (cnt + TT - 1) / TT : 0;
+    tile_cnt2[b] = (leaves && !is_big) ? (cnt + cl.tt_mid - 1) / cl.tt_mid : 0;
+    tile_cnt3[b] = is_big ? (cnt + cl.tt_big - 1) / cl.tt_big : 0;
   }
   __syncthreads();
   const int n_seg = block_exclusive_scan(seg_flag, bins, warp_tot);
   const int n_tiles = block_exclusive_scan(tile_cnt, bins, warp_tot);
-  const int n_tiles2 = big.small_max > 0 ? block_exclusive_scan(tile_cnt2, bins, warp_tot) : 0;
+  const int n_tiles2 = cl.small_max > 0 ? block_exclusive_scan(tile_cnt2, bins, warp_tot) : 0;
+  const int n_tiles3 = cl.small_max > 0 ? block_exclusive_scan(tile_cnt3, bins, warp_tot) : 0;
   for (int b = tid + 1; b < bins; b += blockDim.x) {
     const int start = bin_start[b], cnt = bin_start[b + 1] - start;
     if (cnt > 0) {
@@ -189,13 +197,16 @@ route_kernel(const RouteSrc src, int T, int D, int W, int TT, int* __restrict__ 
       if (seg_delta) seg_delta[s] = b - 1;
       if (seg_start) seg_start[s] = start;
       if (seg_count) seg_count[s] = cnt;
-      const bool is_big = big.small_max > 0 && cnt > big.small_max;
-      if (is_big) {
-        int tpos = tile_cnt2[b];
-        for (int off = 0; off < cnt; off += big.tt_big, ++tpos) {
-          big.tile_delta[tpos] = b - 1;
-          big.tile_start[tpos] = start + off;
-          big.tile_count[tpos] = min(big.tt_big, cnt - off);
+      const bool leaves = cl.small_max > 0 && cnt > cl.small_max;
+      if (leaves) {
+        const bool is_big = cnt > cl.mid_max;
+        const RouteList& l = is_big ? cl.big : cl.mid;
+        const int tt = is_big ? cl.tt_big : cl.tt_mid;
+        int tpos = is_big ? tile_cnt3[b] : tile_cnt2[b];
+        for (int off = 0; off < cnt; off += tt, ++tpos) {
+          l.tile_delta[tpos] = b - 1;
+          l.tile_start[tpos] = start + off;
+          l.tile_count[tpos] = min(tt, cnt - off);
         }
       } else if (tile_delta && tile_start && tile_count) {
         int tpos = tile_cnt[b];
@@ -215,6 +226,7 @@ route_kernel(const RouteSrc src, int T, int D, int W, int TT, int* __restrict__ 
     counters[2] = bin_start[1];
     counters[3] = n_invalid;
     counters[4] = n_tiles2;
+    counters[5] = n_tiles3;
   }
 }
 
@@ -256,18 +268,18 @@ extern "C" int trb_route_max_tiles(int num_tokens, int num_deltas, int tile_toke
 namespace trb {
 int route_launch_src(const RouteSrc& src, int T, int D, int TT, int* perm, int* seg_delta, int* seg_start,
                      int* seg_count, int* tile_delta, int* tile_start, int* tile_count, int* counters, int* slot_of,
-                     int slot_stride, int* bin_count, cudaStream_t stream, const RouteBig* big_list = nullptr) {
+                     int slot_stride, int* bin_count, cudaStream_t stream, const RouteClasses* classes = nullptr) {
   if (T < 0 || T > 65536 || D < 1 || D > 8191 || TT < 1) return TRB_ERR_PROB_SHAPE;
   if ((src.indices == nullptr && src.chunk_base == nullptr && T > 0) || counters == nullptr) return TRB_ERR_BAD_ARG;
   const int bins = D + 1;
   // Small batches: 8 warps (cheaper block syncs), and no more histogram copies than 32-token pieces.
   const int threads = (T <= 2048 && bins <= 2048) ? 256 : kRouteThreads;
-  int W = (50000 - 4 * bins - 1) / bins;   // shared-memory budget of ~195 KiB
+  int W = (50000 - 5 * bins - 1) / bins;   // shared-memory budget of ~195 KiB
   const int w_cap = threads / 32, w_need = (T + 31) / 32;
   W = W > w_cap ? w_cap : W;
   W = W > w_need ? w_need : W;
   W = W < 1 ? 1 : W;
-  const size_t smem = (size_t)(bins * W + 4 * bins + 1) * sizeof(int);
+  const size_t smem = (size_t)(bins * W + 5 * bins + 1) * sizeof(int);
   static std::atomic<bool> attr_set[64];
   int dev = 0;
   cudaGetDevice(&dev);
@@ -276,13 +288,15 @@ int route_launch_src(const RouteSrc& src, int T, int D, int TT, int* perm, int* 
       return TRB_ERR_CUDA;
     attr_set[dev].store(true, std::memory_order_release);
   }
-  RouteBig big{};
-  if (big_list != nullptr) {
-    big = *big_list;
-    if (big.small_max < 1 || big.tt_big < 1 || !big.tile_delta || !big.tile_start || !big.tile_count) return TRB_ERR_BAD_ARG;
+  RouteClasses cl{};
+  if (classes != nullptr) {
+    cl = *classes;
+    if (cl.small_max < 1 || cl.mid_max < cl.small_max || cl.tt_mid < 1 || cl.tt_big < 1 || !cl.mid.tile_delta ||
+        !cl.mid.tile_start || !cl.mid.tile_count || !cl.big.tile_delta || !cl.big.tile_start || !cl.big.tile_count)
+      return TRB_ERR_BAD_ARG;
   }
   route_kernel<<<1, threads, smem, stream>>>(src, T, D, W, TT, perm, seg_delta, seg_start, seg_count, tile_delta,
-                                                   tile_start, tile_count, counters, slot_of, slot_stride, bin_count, big);
+                                                   tile_start, tile_count, counters, slot_of, slot_stride, bin_count, cl);
   return cudaGetLastError() == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
 }
 
