@@ -317,34 +317,36 @@ __global__ void __launch_bounds__(256) lora_shrink_rows_kernel(__half* __restric
   if (!has) return;
   const __half* am = A + idx * (int64_t)h1 * rank;
   const __half* x = X + (int64_t)b * h1;
-  float acc[64];
-#pragma unroll
-  for (int j = 0; j < 64; ++j) acc[j] = 0.f;
+  // A row of A holds rank halves = rv 16-byte pieces.  `pw` lanes (rv rounded up to a power of two)
+  // share a row, so a warp load covers 32 / pw consecutive rows: contiguous memory, 8 accumulators
+  // per lane.
   const int rv = rank / 8;
-  for (int k = tid; k < h1; k += 256) {
-    const float xk = __half2float(x[k]);
-    const uint4* row = reinterpret_cast<const uint4*>(am + (int64_t)k * rank);
+  const int pw = rv <= 1 ? 1 : (rv <= 2 ? 2 : (rv <= 4 ? 4 : 8));
+  const int sub = lane & (pw - 1), rl = lane / pw, rows_per_warp = 32 / pw;
+  float acc[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      if (i < rv) {
-        const uint4 wv = row[i];
-        const uint32_t* pw = reinterpret_cast<const uint32_t*>(&wv);
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  if (sub < rv) {
+#pragma unroll 4
+    for (int k = warp * rows_per_warp + rl; k < h1; k += 8 * rows_per_warp) {
+      const float xk = __half2float(x[k]);
+      const uint4 wv = *reinterpret_cast<const uint4*>(am + (int64_t)k * rank + sub * 8);
+      const uint32_t* pwv = reinterpret_cast<const uint32_t*>(&wv);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&pw[e]));
-          acc[i * 8 + 2 * e] = fmaf(xk, f.x, acc[i * 8 + 2 * e]);
-          acc[i * 8 + 2 * e + 1] = fmaf(xk, f.y, acc[i * 8 + 2 * e + 1]);
-        }
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&pwv[e]));
+        acc[2 * e] = fmaf(xk, f.x, acc[2 * e]);
+        acc[2 * e + 1] = fmaf(xk, f.y, acc[2 * e + 1]);
       }
     }
   }
+  // lanes with the same `sub` hold partial sums of the same 8 columns
+  for (int o = pw; o < 32; o <<= 1)
 #pragma unroll
-  for (int j = 0; j < 64; ++j) {
-    if (j < rank) {
-      const float s = warp_sum(acc[j]);
-      if (lane == 0) part[warp][j] = s;
-    }
-  }
+    for (int e = 0; e < 8; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], o);
+  if (lane < pw && sub < rv)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) part[warp][sub * 8 + e] = acc[e];
   __syncthreads();
   if (tid < rank) {
     float s = 0.f;

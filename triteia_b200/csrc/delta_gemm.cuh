@@ -565,6 +565,7 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_consta
   const int warp = tid >> 5;
   const int lane = tid & 31;
 
+  pdl_launch_dependents();
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -573,8 +574,8 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_consta
     *dead = 0;
     fence_mbar_init();
   }
-  pdl_launch_dependents();
   pdl_wait();   // everything below reads what the kernels launched before this one wrote
+  if (a.mode == kSegTiles && a.n_seg_ptr != nullptr && *a.n_seg_ptr <= 0) return;   // the router left this list empty
 
   int n_seg = a.n_seg_ptr ? *a.n_seg_ptr : a.n_seg;
   n_seg = max(0, min(n_seg, a.mode == kSegTiles ? a.n_seg : kMaxSegments));

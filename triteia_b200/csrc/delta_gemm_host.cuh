@@ -182,14 +182,16 @@ static_assert(TcSpPairCfg::SMEM_ALLOC <= 232448, "shared memory budget of one sm
 // The mma.sp kernel comes in two tile ranges and two geometries.  Tiles of 8 tokens (decode: a
 // delta has a handful of tokens) run in a kernel that holds nothing else, because every other tile
 // class compiled beside it costs the hot loop registers; tiles of 16 and 32 tokens share a second
-// kernel.  Wide outputs: 256-column items, two warps per column block (half as many work items, so
-// half the per-item cost per byte streamed); otherwise 128-column items, four warps per column block.
-using CfgWide8 = GemmCfg<1, 4, 2, 8, 5>;
+// kernel.  The decode kernel on wide outputs: 256-column items, two warps per column block (half as
+// many work items, so half the per-item cost per byte streamed); otherwise 128-column items, four
+// warps per column block.
+#ifndef TRB_W8_STAGES
+#define TRB_W8_STAGES 5
+#endif
+using CfgWide8 = GemmCfg<1, 4, 2, 8, TRB_W8_STAGES>;
 using CfgNarrow8 = GemmCfg<1, 2, 4, 8, 6>;
-using CfgWideMid = GemmCfg<4, 4, 2, 8, 5, 2>;
-using CfgNarrowMid = GemmCfg<4, 2, 4, 8, 6, 2>;
-static_assert(CfgWide8::SMEM_ALLOC <= 232448 && CfgNarrow8::SMEM_ALLOC <= 232448 && CfgWideMid::SMEM_ALLOC <= 232448 &&
-                  CfgNarrowMid::SMEM_ALLOC <= 232448,
+using CfgMid = GemmCfg<4, 2, 4, 8, 6, 2>;      // 128-column items whatever the width: mid-sized segments are few
+static_assert(CfgWide8::SMEM_ALLOC <= 232448 && CfgNarrow8::SMEM_ALLOC <= 232448 && CfgMid::SMEM_ALLOC <= 232448,
               "shared memory budget of one sm_100 CTA");
 constexpr int kSmallTile = 8;      // token tile of the decode kernel
 constexpr int kMidTile = 32;       // largest token tile of the second mma.sp kernel
@@ -217,7 +219,7 @@ int gemm_dispatch(const GemmCall& c, const GemmArgs& a, int tile_tokens) {
   if (e != cudaSuccess) return TRB_ERR_CUDA;
   switch (tile_tokens) {
     case kSmallTile: return (a.N % 256 == 0 && a.N >= 2048) ? launch_cfg<CfgWide8>(c, a) : launch_cfg<CfgNarrow8>(c, a);
-    case kMidTile: return (a.N % 256 == 0 && a.N >= 2048) ? launch_cfg<CfgWideMid>(c, a) : launch_cfg<CfgNarrowMid>(c, a);
+    case kMidTile: return launch_cfg<CfgMid>(c, a);
     case kBigTile: return a.y_peers ? TRB_ERR_KERN_SHAPE : launch_tc(c, a);
     default: return TRB_ERR_KERN_SHAPE;
   }

@@ -196,6 +196,14 @@ delta_gemm_tcsp_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
 
   int n_seg = 0;
 
+  // A tile list that the router left empty (the usual case at decode sizes): leave before anything
+  // is set up.  Both CTAs of a pair read the same count.
+  pdl_launch_dependents();
+  if (a.mode == kSegTiles && a.n_seg_ptr != nullptr) {
+    pdl_wait();
+    if (*a.n_seg_ptr <= 0) return;
+  }
+
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
