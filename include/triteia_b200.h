@@ -216,8 +216,8 @@ int trb_row_checksum(const void* y, void* sums, int rows, int prob_m, int accumu
  * host cost of a launch made from Python exceeds the run time of most of these kernels).  Rows
  * [class_row0[c], +class_rows[c]) form size class c with its own segment list (class_ids /
  * class_starts / class_counts, class_segs[c] entries, starts relative to the class's first row) and
- * its kernel: class_tile[c] = 8 (segments of up to 8 rows: the decode kernel), 32 (up to 128 rows: the
- * mma.sp kernel with tiles of 16 or 32 rows chosen per segment) or 256 (longer: the tcgen05 kernel).  Per linear i every class
+ * its kernel: class_tile[c] = 8 (short segments: 8-row tiles of the mma.sp kernel) or 256 (long
+ * segments: 256-row tiles of the tcgen05 kernel).  Per linear i every class
  * gets one segment-list launch on x_of[i] [rows, k[i]] -> y_of[i] [rows, n[i]], then y_of[i] is
  * folded into checksum [rows] fp32 (trb_row_checksum, accumulate).  ksplit: NULL, or
  * trb_sbmm_ksplit_bytes() bytes of working memory (256-byte aligned, first 512 bytes zero on entry

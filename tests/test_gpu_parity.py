@@ -809,7 +809,7 @@ def test_base_gemm_with_lora_expand(cuda, M, rank):
 # ------------------------------------------------------------------ tiles chosen per segment, long lists
 def test_sbmm_zipf_batch_mixed_tiles(cuda):
     """A Zipf(1.5) batch of 512 tokens over 64 deltas through the one-call path: the hot deltas
-    (more than 128 rows) go to the tcgen05 kernel, mid-sized ones to 16- and 32-token tiles, the tail to
+    (more than 32 rows) go to the tcgen05 kernel in 256-token tiles, the others to the mma.sp kernel in
     8-token tiles, all inside one call.  Every row against the oracle; run twice, bit-identical."""
     ops = _ops()
     T, D, K, N = 512, 64, 512, 768
@@ -819,7 +819,7 @@ def test_sbmm_zipf_batch_mixed_tiles(cuda):
     idx_np = rng.choice(D, T, p=p / p.sum()).astype(np.int32)
     idx_np[rng.choice(T, 20, replace=False)] = -1
     counts = np.bincount(idx_np[idx_np >= 0], minlength=D)
-    assert counts.max() > 128 and ((counts > 8) & (counts <= 128)).any() and ((counts > 0) & (counts <= 8)).any()
+    assert counts.max() > 32 and ((counts > 8) & (counts <= 32)).any() and ((counts > 0) & (counts <= 8)).any()
     x = torch.randn(T, K, dtype=torch.float16, device=cuda, generator=torch.Generator(cuda).manual_seed(51))
     idx = torch.from_numpy(idx_np).to(cuda)
     y = ops.sbmm_4bit_2_4_native(qs, x, metas, ss, idx)
@@ -829,14 +829,15 @@ def test_sbmm_zipf_batch_mixed_tiles(cuda):
     assert _lib().device_status(0) == 0
 
 
-@pytest.mark.parametrize("count", [8, 9, 16, 17, 32, 33, 64, 100, 128, 129, 300])
-def test_sbmm_segment_sizes_around_the_class_bounds(cuda, count):
-    """One delta with `count` rows among singletons: up to 8 rows the decode kernel, 9..128 rows tiles
-    of 16 / 32 tokens on the second mma.sp kernel, more rows tiles of the tcgen05 kernel."""
+@pytest.mark.parametrize("count", [8, 9, 32, 33, 100, 256, 300])
+@pytest.mark.parametrize("others", [6, 130])
+def test_sbmm_segment_sizes_around_the_class_bounds(cuda, count, others):
+    """One delta with `count` rows among `others` other rows: up to 32 rows it is cut into 8-token
+    tiles; beyond that it goes to the tcgen05 kernel when the batch has more than 128 tokens."""
     ops = _ops()
     D, K, N = 6, 256, 512
     qs, metas, ss = packed(N, K, -1, seed=60 + count, num=D)
-    idx_np = np.concatenate([np.full(count, 2), np.arange(D), [-1, -1]]).astype(np.int32)
+    idx_np = np.concatenate([np.full(count, 2), np.arange(others) % D, [-1, -1]]).astype(np.int32)
     np.random.default_rng(count).shuffle(idx_np)
     T = idx_np.size
     x = torch.randn(T, K, dtype=torch.float16, device=cuda, generator=torch.Generator(cuda).manual_seed(count))

@@ -144,7 +144,7 @@ def test_stack_plan_groups_rows_by_size_class_and_delta():
     """Row order and per-class segment lists of the stack's local pass (pure torch, no GPU)."""
     from triteia_b200.stack import DeltaStackShard
 
-    counts = {0: 170, 1: 3, 2: 9, 3: 1, 5: 129, 7: 8, 9: 128}          # delta id -> rows
+    counts = {0: 40, 1: 3, 2: 9, 3: 1, 5: 33, 7: 8, 9: 32}          # delta id -> rows
     ids = torch.cat([torch.full((c,), d, dtype=torch.int32) for d, c in counts.items()])
     ids = ids[torch.randperm(ids.numel(), generator=torch.Generator().manual_seed(0))]
     shard = DeltaStackShard.__new__(DeltaStackShard)                  # _plan needs no weights

@@ -63,11 +63,9 @@ constexpr int kKsplitSlots = 148;             // pieces over all tail items
 constexpr int kKsplitSlotFloats = 256 * 8;    // one 8-token x 256-column fp32 tile
 constexpr size_t kKsplitBufBytes = (size_t)kKsplitSlots * kKsplitSlotFloats * 4;
 
-template <int NB_, int SW_, int KQ_, int KS_, int STAGES_, int MINNB_ = 1>
+template <int NB_, int SW_, int KQ_, int KS_, int STAGES_>
 struct GemmCfg {
-  static constexpr int NB = NB_;          // token blocks of 8 in the largest tile; a tile's class (1, 2 or 4
-                                          // blocks) follows from its row count, item by item
-  static constexpr int MINNB = MINNB_;    // smallest class compiled in: shorter tiles run as this class
+  static constexpr int NB = NB_;          // token blocks of 8 per tile
   static constexpr int SW = SW_;          // 64-column blocks per stripe
   static constexpr int KQ = KQ_;          // warps sharing one column block (split over slabs)
   static constexpr int KS = KS_;          // 32-K slabs per pipeline stage
@@ -194,14 +192,6 @@ __device__ __forceinline__ WorkItem decode_item(const GemmArgs& a, const int* pr
   return w;
 }
 
-// Token blocks of the class that serves a tile of `valid` rows in a kernel whose classes span [lo, hi].
-__device__ __forceinline__ int tile_class(int valid, int lo, int hi) {
-  const int c = valid <= 8 ? 1 : (valid <= 16 ? 2 : 4);
-  return c < lo ? lo : (c > hi ? hi : c);
-}
-
-template <int V> using IntTag = std::integral_constant<int, V>;
-
 // Where a consumer warp stands in the stage ring, carried from one work unit to the next.
 struct PipeState {
   int st;
@@ -209,7 +199,7 @@ struct PipeState {
   bool first_item;
 };
 
-// One work unit of a consumer warp with a tile of NB token blocks (the tile's class).
+// One work unit of a consumer warp: a tile of NB token blocks against one stripe (or a K range of it).
 template <class Cfg, int NB>
 __device__ __forceinline__ PipeState run_unit_body(const GemmArgs& a, uint8_t* smem, PipeState ps, const WorkUnit wu,
                                                    const WorkItem w) {
@@ -545,11 +535,9 @@ __device__ __forceinline__ PipeState run_unit_body(const GemmArgs& a, uint8_t* s
   return PipeState{st, phase, first_item};
 }
 
-// tm_x1 / tm_x2 / tm_x4: the activation matrix with boxes of 8, 16 and 32 rows (one per tile class).
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
-delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ CUtensorMap tm_x2,
-                  const __grid_constant__ CUtensorMap tm_x4, const __grid_constant__ CUtensorMap tm_q,
+delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_q,
                   const __grid_constant__ CUtensorMap tm_m, const __grid_constant__ CUtensorMap tm_s,
                   const __grid_constant__ GemmArgs a) {
   constexpr int NBMAX = Cfg::NB, SW = Cfg::SW, KS = Cfg::KS, STAGES = Cfg::STAGES;
@@ -617,47 +605,31 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_consta
   const int groups = a.grouped ? a.K / 128 : 1;
   // Work units of this CTA: whole items in the full rounds, then (maybe) a K range of a tail item.
   const TailSplit split = tail_split(n_items, k_stages, (int)gridDim.x, (int)blockIdx.x,
-                                     SW * 512 <= kKsplitSlotFloats && a.ksplit_buf != nullptr);
-  // Only 8-token tiles are cut along K (the partial-tile slots hold 8 tokens): a larger tile of the
-  // tail is done whole by the CTA that holds its piece 0.  Returns false when this CTA has nothing to do.
-  auto settle_unit = [&](WorkUnit& wu, const WorkItem& w) -> bool {
-    if (!w.ok) return false;
-    if (wu.parts > 1 && tile_class(w.valid, Cfg::MINNB, NBMAX) != 1) {
-      if (wu.part != 0) return false;
-      wu.ks0 = 0; wu.ks1 = k_stages; wu.parts = 1;
-    }
-    return true;
-  };
+                                     NBMAX == 1 && SW * 512 <= kKsplitSlotFloats && a.ksplit_buf != nullptr);
 
   if (warp == Cfg::CW) {
     // ------------------------------ producer ------------------------------
     if (lane == 0) {
-      prefetch_tmap(&tm_x1);
-      if (NBMAX >= 2) prefetch_tmap(&tm_x2);
-      if (NBMAX >= 4) prefetch_tmap(&tm_x4);
+      prefetch_tmap(&tm_x);
       prefetch_tmap(&tm_q);
       prefetch_tmap(&tm_m);
       if (a.grouped) prefetch_tmap(&tm_s);
       const uint64_t pol_w = policy_evict_first();
       const uint64_t pol_x = policy_evict_last();
-      const uint32_t weight_tx = Cfg::Q_BYTES + Cfg::M_BYTES + (a.grouped ? Cfg::S_BYTES : 0);
+      const uint32_t stage_tx = Cfg::X_BYTES + Cfg::Q_BYTES + Cfg::M_BYTES + (a.grouped ? Cfg::S_BYTES : 0);
       int st = 0;
       uint32_t phase = 0;
       for (int u = 0; u < split.units; ++u) {
-        WorkUnit wu = work_unit(split, u, (int)gridDim.x, (int)blockIdx.x, k_stages);
+        const WorkUnit wu = work_unit(split, u, (int)gridDim.x, (int)blockIdx.x, k_stages);
         const WorkItem w = decode_item<Cfg>(a, prefix, n_seg, n_stripes, wu.item);
-        if (!settle_unit(wu, w)) continue;
-        const int cls = tile_class(w.valid, Cfg::MINNB, NBMAX);
-        const CUtensorMap* tmx = cls == 1 ? &tm_x1 : (cls == 2 ? &tm_x2 : &tm_x4);
-        const uint32_t box_bytes = (uint32_t)cls * 1024u;          // 8 * cls rows of 128 bytes
-        const uint32_t stage_tx = Cfg::NXBOX * box_bytes + weight_tx;
+        if (!w.ok) continue;
         for (int ks = wu.ks0; ks < wu.ks1; ++ks) {
           mbar_wait(&empty_bar[st], phase ^ 1, dead);
           uint8_t* sbase = smem + st * Cfg::STAGE_BYTES;
           mbar_arrive_expect_tx(&full_bar[st], stage_tx);
 #pragma unroll
           for (int b = 0; b < Cfg::NXBOX; ++b)
-            tma_load_2d_hint(sbase + Cfg::X_OFF + b * box_bytes, tmx, ks * KS * 32 + b * 64, w.row0,
+            tma_load_2d_hint(sbase + Cfg::X_OFF + b * Cfg::X_BOX_BYTES, &tm_x, ks * KS * 32 + b * 64, w.row0,
                              &full_bar[st], pol_x);
           const int wrow = w.delta * slabs + ks * KS;
 #pragma unroll
@@ -688,21 +660,14 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_consta
     w_next = decode_item<Cfg>(a, prefix, n_seg, n_stripes,
                               work_unit(split, 0, (int)gridDim.x, (int)blockIdx.x, k_stages).item);
   for (int u = 0; u < split.units; ++u) {
-    WorkUnit wu = work_unit(split, u, (int)gridDim.x, (int)blockIdx.x, k_stages);
+    const WorkUnit wu = work_unit(split, u, (int)gridDim.x, (int)blockIdx.x, k_stages);
     const WorkItem w = w_next;
     // Descriptor of the next item: its global loads are in flight during this item's K loop.
     if (u + 1 < split.units)
       w_next = decode_item<Cfg>(a, prefix, n_seg, n_stripes,
                                 work_unit(split, u + 1, (int)gridDim.x, (int)blockIdx.x, k_stages).item);
-    if (!settle_unit(wu, w)) continue;
-    const int cls = tile_class(w.valid, Cfg::MINNB, NBMAX);
-    if constexpr (NBMAX >= 4 && Cfg::MINNB <= 4) {
-      if (cls == 4) { ps = run_unit_body<Cfg, 4>(a, smem, ps, wu, w); continue; }
-    }
-    if constexpr (NBMAX >= 2 && Cfg::MINNB <= 2) {
-      if (cls == 2) { ps = run_unit_body<Cfg, 2>(a, smem, ps, wu, w); continue; }
-    }
-    if constexpr (Cfg::MINNB <= 1) ps = run_unit_body<Cfg, 1>(a, smem, ps, wu, w);
+    if (!w.ok) continue;
+    ps = run_unit_body<Cfg, NBMAX>(a, smem, ps, wu, w);
   }
 }
 

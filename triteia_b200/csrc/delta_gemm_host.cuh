@@ -70,14 +70,10 @@ template <class Cfg>
 static int launch_cfg(const GemmCall& c, const GemmArgs& a) {
   const int slabs = a.K / 32;
   const int groups = a.grouped ? a.K / 128 : 1;
-  CUtensorMap tx[3], tq, tm, ts;
-  for (int i = 0; i < 3; ++i) {   // one activation map per tile class: boxes of 8, 16 and 32 rows
-    const int rows = 8 << i;
-    if (rows > Cfg::TT) { tx[i] = tx[i - 1]; continue; }   // never dereferenced
-    if (!make_map_2d(&tx[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, c.x, (uint64_t)a.rows, (uint64_t)a.K, rows, 64,
-                     CU_TENSOR_MAP_SWIZZLE_128B))
-      return TRB_ERR_CUDA;
-  }
+  CUtensorMap tx, tq, tm, ts;
+  if (!make_map_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, c.x, (uint64_t)a.rows, (uint64_t)a.K, Cfg::TT, 64,
+                   CU_TENSOR_MAP_SWIZZLE_128B))
+    return TRB_ERR_CUDA;
   if (!make_map_2d(&tq, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, c.q, (uint64_t)c.num_deltas * slabs, 2ull * a.N, Cfg::KS,
                    Cfg::QB * 128, CU_TENSOR_MAP_SWIZZLE_NONE))
     return TRB_ERR_CUDA;
@@ -115,7 +111,7 @@ static int launch_cfg(const GemmCall& c, const GemmArgs& a) {
   at[0].val.programmaticStreamSerializationAllowed = 1;
   lc.attrs = at;
   lc.numAttrs = 1;
-  return cudaLaunchKernelEx(&lc, delta_gemm_kernel<Cfg>, tx[0], tx[1], tx[2], tq, tm, ts, a) == cudaSuccess ? TRB_OK
+  return cudaLaunchKernelEx(&lc, delta_gemm_kernel<Cfg>, tx, tq, tm, ts, a) == cudaSuccess ? TRB_OK
                                                                                                              : TRB_ERR_CUDA;
 }
 
@@ -179,28 +175,25 @@ static int launch_tc(const GemmCall& c, const GemmArgs& a) {
 }
 static_assert(TcSpPairCfg::SMEM_ALLOC <= 232448, "shared memory budget of one sm_100 CTA");
 
-// The mma.sp kernel comes in two tile ranges and two geometries.  Tiles of 8 tokens (decode: a
-// delta has a handful of tokens) run in a kernel that holds nothing else, because every other tile
-// class compiled beside it costs the hot loop registers; tiles of 16 and 32 tokens share a second
-// kernel.  The decode kernel on wide outputs: 256-column items, two warps per column block (half as
-// many work items, so half the per-item cost per byte streamed); otherwise 128-column items, four
-// warps per column block.
+// The mma.sp kernel works on tiles of 8 tokens (decode: a delta has a handful of tokens).  Larger
+// tile classes of the same kernel (16 and 32 tokens) were built and measured: compiled beside the
+// 8-token path they cost its hot loop registers (86 -> 102 us on the decode benchmark), and as a
+// kernel of their own they ran under-filled launches slower than either neighbour, so segments are
+// cut into 8-token tiles up to kSmallSegMax tokens and go to the tcgen05 kernel beyond that.
+// Wide outputs: 256-column items, two warps per column block (half as many work items, so half the
+// per-item cost per byte streamed); otherwise 128-column items, four warps per column block.
 #ifndef TRB_W8_STAGES
 #define TRB_W8_STAGES 5
 #endif
 using CfgWide8 = GemmCfg<1, 4, 2, 8, TRB_W8_STAGES>;
 using CfgNarrow8 = GemmCfg<1, 2, 4, 8, 6>;
-using CfgMid = GemmCfg<4, 2, 4, 8, 6, 2>;      // 128-column items whatever the width: mid-sized segments are few
-static_assert(CfgWide8::SMEM_ALLOC <= 232448 && CfgNarrow8::SMEM_ALLOC <= 232448 && CfgMid::SMEM_ALLOC <= 232448,
-              "shared memory budget of one sm_100 CTA");
-constexpr int kSmallTile = 8;      // token tile of the decode kernel
-constexpr int kMidTile = 32;       // largest token tile of the second mma.sp kernel
+static_assert(CfgWide8::SMEM_ALLOC <= 232448 && CfgNarrow8::SMEM_ALLOC <= 232448, "shared memory budget of one sm_100 CTA");
+constexpr int kSmallTile = 8;      // token tile of the mma.sp kernel
 constexpr int kBigTile = 256;      // token tile of the tcgen05 kernel
-constexpr int kMidSegMax = 128;    // the router sends segments of more tokens than this to the tcgen05 kernel
+constexpr int kSmallSegMax = 32;   // the router sends segments of more tokens than this to the tcgen05 kernel ...
+constexpr int kBigMinTokens = 128; // ... when the batch has more tokens than this (smaller batches: one launch)
 
-int gemm_tile_tokens(int tokens_per_segment) {
-  return tokens_per_segment <= kSmallTile ? kSmallTile : (tokens_per_segment <= kMidTile ? kMidTile : kBigTile);
-}
+int gemm_tile_tokens(int tokens_per_segment) { return tokens_per_segment <= kSmallSegMax ? kSmallTile : kBigTile; }
 
 static int check_common(const void* A, const void* B, const void* meta, void* C, const void* s, int N, int T, int K,
                         int groupsize) {
@@ -219,7 +212,6 @@ int gemm_dispatch(const GemmCall& c, const GemmArgs& a, int tile_tokens) {
   if (e != cudaSuccess) return TRB_ERR_CUDA;
   switch (tile_tokens) {
     case kSmallTile: return (a.N % 256 == 0 && a.N >= 2048) ? launch_cfg<CfgWide8>(c, a) : launch_cfg<CfgNarrow8>(c, a);
-    case kMidTile: return launch_cfg<CfgMid>(c, a);
     case kBigTile: return a.y_peers ? TRB_ERR_KERN_SHAPE : launch_tc(c, a);
     default: return TRB_ERR_KERN_SHAPE;
   }
@@ -251,7 +243,7 @@ extern "C" int trb_mul_2_4(const void* A, const void* B, const void* meta, void*
 // are zero again when the launch has finished).  Without it (nullptr) this is trb_sbmm_2_4.
 extern "C" size_t trb_sbmm_ksplit_bytes(void) { return 512 + kKsplitBufBytes; }
 
-// tile_tokens: 0 = choose from the average segment length; kSmallTile / kMidTile / kBigTile = forced.
+// tile_tokens: 0 = choose from the average segment length; kSmallTile / kBigTile = forced.
 static int sbmm_segments(const void* A, const void* B, const void* meta, void* C, const void* s, const void* indices,
                          const void* starts, const void* counts, int prob_m, int prob_n, int prob_k, int prob_r,
                          int groupsize, int dev, void* stream, int sms, void* ksplit, size_t ksplit_bytes,
@@ -335,23 +327,20 @@ constexpr size_t kCounterBytes = 1024;
 constexpr int kKsplitCntOffset = 64;
 static_assert(kKsplitCntOffset * 4 + kKsplitItems * 4 <= (int)kCounterBytes, "counters fit the scratch head");
 
-// Capacity of the tile lists the router fills: one 8-token tile per segment of at most 8 tokens,
-// tiles of at most kMidTile tokens for segments of 9..kMidSegMax tokens, tiles of kBigTile tokens
-// for the longer ones.
+// Capacity of the tile lists the router fills: 8-token tiles for segments of at most kSmallSegMax
+// tokens (all segments in batches of at most kBigMinTokens tokens), kBigTile-token tiles for the rest.
 static size_t small_tile_capacity(int num_tokens, int num_deltas) {
-  return (size_t)(num_tokens < num_deltas ? num_tokens : num_deltas);
+  return (size_t)trb_route_max_tiles(num_tokens, num_deltas, kSmallTile);
 }
-static size_t mid_tile_capacity(int num_tokens) { return (size_t)(num_tokens / kMidTile + num_tokens / (kSmallTile + 1) + 1); }
-static size_t big_tile_capacity(int num_tokens) { return (size_t)(num_tokens / kBigTile + num_tokens / (kMidSegMax + 1) + 1); }
+static size_t big_tile_capacity(int num_tokens) { return (size_t)(num_tokens / kBigTile + num_tokens / (kSmallSegMax + 1) + 1); }
 
 // The least scratch the indexed path works with (no tail K split).
 static size_t indexed_scratch_min(int num_tokens, int prob_k, int num_deltas) {
   if (num_tokens <= 0 || prob_k <= 0 || num_deltas <= 0) return kCounterBytes;
   size_t b = kCounterBytes;                                                      // counters
   b += align_up((size_t)num_tokens * 4, 256);                                    // perm
-  b += 3 * align_up(small_tile_capacity(num_tokens, num_deltas) * 4, 256);       // tile list, segments of up to 8 tokens
-  b += 3 * align_up(mid_tile_capacity(num_tokens) * 4, 256);                     // tile list, 9..128 tokens
-  b += 3 * align_up(big_tile_capacity(num_tokens) * 4, 256);                     // tile list, longer segments
+  b += 3 * align_up(small_tile_capacity(num_tokens, num_deltas) * 4, 256);       // tile list, short segments
+  b += 3 * align_up(big_tile_capacity(num_tokens) * 4, 256);                     // tile list, long segments
   b += align_up((size_t)num_tokens * prob_k * 2, 256);                           // gathered activations
   return b;
 }
@@ -370,11 +359,10 @@ namespace trb {
 // rows of x and y.  mode: 0 = overwrite rows that have a delta and zero the others, 1 = accumulate,
 // 2 = overwrite rows that have a delta and leave the others untouched.
 // The router cuts every segment into tiles that fit its own token count (the reference chooses its
-// tile per delta the same way, triteia/csrc/ops/triteia_nm_sbmm.cu:756-762): up to 8 tokens -> the
-// decode kernel, 9..128 tokens -> the second mma.sp kernel in tiles of 16 or 32 tokens, more -> the
-// tcgen05 kernel in tiles of 256.  The lists are consumed without the host knowing their lengths: a
-// launch whose list is empty ends at once, and a launch whose list must be empty for this batch size
-// is not made.
+// tile per delta the same way, triteia/csrc/ops/triteia_nm_sbmm.cu:756-762): segments of up to
+// kSmallSegMax tokens -> 8-token tiles of the mma.sp kernel, longer ones -> 256-token tiles of the
+// tcgen05 kernel.  The lists are consumed without the host knowing their lengths: a launch whose list
+// is empty ends at once, and batches of at most kBigMinTokens tokens make the mma.sp launch only.
 int sbmm_indexed_impl(const void* x, const void* qweights, const void* metas, const void* scales, const RouteSrc& src,
                       void* y, int num_tokens, int prob_m, int prob_k, int num_deltas, int groupsize, int mode,
                       void* scratch, size_t scratch_bytes, int dev, cudaStream_t stream,
@@ -388,38 +376,32 @@ int sbmm_indexed_impl(const void* x, const void* qweights, const void* metas, co
   if (scratch_bytes < min_bytes) return TRB_ERR_SCRATCH;
   if (cudaSetDevice(dev) != cudaSuccess) return TRB_ERR_CUDA;
 
-  const bool use_mid = num_tokens > kSmallTile;
-  // The peer-store epilogue exists in the mma.sp kernels only; the tcgen05 kernel writes 16-byte pieces.
-  const bool use_big = y_peers == nullptr && num_tokens > kMidSegMax && (prob_m & 7) == 0;
-  const size_t cap_small = small_tile_capacity(num_tokens, num_deltas), cap_mid = mid_tile_capacity(num_tokens),
-               cap_big = big_tile_capacity(num_tokens);
+  // The peer-store epilogue exists in the mma.sp kernel only; the tcgen05 kernel writes 16-byte pieces.
+  const bool use_big = y_peers == nullptr && num_tokens > kBigMinTokens && (prob_m & 7) == 0;
+  const size_t cap_small = small_tile_capacity(num_tokens, num_deltas), cap_big = big_tile_capacity(num_tokens);
 
   uint8_t* p = (uint8_t*)scratch;
   int* counters = (int*)p; p += kCounterBytes;
-  // Tail K split of the decode kernel: only with room for its partial tiles behind the rest.
+  // Tail K split of the mma.sp kernel: only with room for its partial tiles behind the rest.
   const bool ksplit = scratch_bytes >= min_bytes + kKsplitBufBytes;
   int* perm = (int*)p; p += align_up((size_t)num_tokens * 4, 256);
-  RouteList small{}, mid{}, big{};
+  RouteList small{}, big{};
   auto carve = [&](RouteList& l, size_t cap) {
     l.tile_delta = (int*)p; p += align_up(cap * 4, 256);
     l.tile_start = (int*)p; p += align_up(cap * 4, 256);
     l.tile_count = (int*)p; p += align_up(cap * 4, 256);
   };
   carve(small, cap_small);
-  carve(mid, cap_mid);
   carve(big, cap_big);
   void* x_sorted = p;
   RouteClasses cl{};
-  cl.small_max = kSmallTile;
-  cl.mid_max = use_big ? kMidSegMax : (1 << 30);
-  cl.tt_mid = kMidTile;
+  cl.small_max = kSmallSegMax;
   cl.tt_big = kBigTile;
-  cl.mid = mid;
   cl.big = big;
 
   int r = route_launch_src(src, num_tokens, num_deltas, kSmallTile, perm, nullptr, nullptr, nullptr, small.tile_delta,
                            small.tile_start, small.tile_count, counters, nullptr, 0, nullptr, stream,
-                           use_mid ? &cl : nullptr);
+                           use_big ? &cl : nullptr);
   if (r != TRB_OK) return r;
   r = gather_launch(x, perm, counters, x_sorted, y, num_tokens, prob_k, prob_m, mode == 0 ? 1 : 0, stream,
                     ksplit ? counters + kKsplitCntOffset : nullptr, kKsplitItems);
@@ -434,11 +416,9 @@ int sbmm_indexed_impl(const void* x, const void* qweights, const void* metas, co
   a.row_map = perm;
   a.accumulate = mode == 1;
   GemmCall c{x_sorted, qweights, metas, scales, num_deltas, groupsize, dev, -1, stream};
-  // Largest segments first: at decode sizes those lists are empty, their CTAs are resident before
-  // the gather ends and leave at once.
   if (use_big) {
     a.seg_delta = big.tile_delta; a.seg_start = big.tile_start; a.seg_count = big.tile_count;
-    a.n_seg_ptr = counters + 5;
+    a.n_seg_ptr = counters + 4;
     a.n_seg = (int)cap_big;
     r = gemm_dispatch(c, a, kBigTile);
     if (r != TRB_OK) return r;
@@ -447,13 +427,6 @@ int sbmm_indexed_impl(const void* x, const void* qweights, const void* metas, co
   a.xchg = src.chunk_base;
   a.xchg_row_bytes = src.row_bytes;
   a.chunk_rows = chunk_rows;
-  if (use_mid) {
-    a.seg_delta = mid.tile_delta; a.seg_start = mid.tile_start; a.seg_count = mid.tile_count;
-    a.n_seg_ptr = counters + 4;
-    a.n_seg = (int)cap_mid;
-    r = gemm_dispatch(c, a, kMidTile);
-    if (r != TRB_OK) return r;
-  }
   a.seg_delta = small.tile_delta; a.seg_start = small.tile_start; a.seg_count = small.tile_count;
   a.n_seg_ptr = counters + 1;
   a.n_seg = (int)cap_small;

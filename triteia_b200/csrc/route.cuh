@@ -87,18 +87,18 @@ __device__ __forceinline__ int route_bin(const RouteSrc& s, int raw, int D, bool
 }
 
 // Tile lists by segment size.  With small_max > 0 a segment of more than small_max tokens leaves the
-// first list (tiles of TT tokens): up to mid_max tokens it is cut into tiles of tt_mid tokens in the
-// `mid` list, beyond that into tiles of tt_big tokens in the `big` list, so that every segment gets
-// the kernel and tile that suit its own token count (the reference picks its tile per delta the same
-// way, triteia/csrc/ops/triteia_nm_sbmm.cu:756-762).  counters[4], counters[5] = lengths of mid, big.
+// first list (tiles of TT tokens) and is cut into tiles of tt_big tokens in the `big` list, so that
+// short and long segments each get the kernel that suits them (the reference picks its tile per delta
+// from the delta's token count, triteia/csrc/ops/triteia_nm_sbmm.cu:756-762).  counters[4] = length
+// of the big list.
 struct RouteList {
   int* tile_delta;
   int* tile_start;
   int* tile_count;
 };
 struct RouteClasses {
-  int small_max, mid_max, tt_mid, tt_big;
-  RouteList mid, big;
+  int small_max, tt_big;
+  RouteList big;
 };
 
 __global__ void __launch_bounds__(kRouteThreads, 1)
@@ -114,8 +114,7 @@ route_kernel(const RouteSrc src, int T, int D, int W, int TT, int* __restrict__ 
   int* bin_start = hist + bins * W;   // [bins + 1]
   int* seg_flag = bin_start + bins + 1;   // [bins]
   int* tile_cnt = seg_flag + bins;        // [bins]
-  int* tile_cnt2 = tile_cnt + bins;       // [bins] tiles in the mid list
-  int* tile_cnt3 = tile_cnt2 + bins;      // [bins] tiles in the big list
+  int* tile_cnt2 = tile_cnt + bins;       // [bins] tiles in the big list
   __shared__ int warp_tot[33];
   __shared__ int n_invalid;
 
@@ -178,18 +177,15 @@ route_kernel(const RouteSrc src, int T, int D, int W, int TT, int* __restrict__ 
   for (int b = tid; b < bins; b += blockDim.x) {
     const int cnt = bin_start[b + 1] - bin_start[b];
     const bool is_seg = b >= 1 && cnt > 0;
-    const bool leaves = is_seg && cl.small_max > 0 && cnt > cl.small_max;
-    const bool is_big = leaves && cnt > cl.mid_max;
+    const bool is_big = is_seg && cl.small_max > 0 && cnt > cl.small_max;
     seg_flag[b] = is_seg ? 1 : 0;
-    tile_cnt[b] = (is_seg && !leaves) ? (cnt + TT - 1) / TT : 0;
-    tile_cnt2[b] = (leaves && !is_big) ? (cnt + cl.tt_mid - 1) / cl.tt_mid : 0;
-    tile_cnt3[b] = is_big ? (cnt + cl.tt_big - 1) / cl.tt_big : 0;
+    tile_cnt[b] = (is_seg && !is_big) ? (cnt + TT - 1) / TT : 0;
+    tile_cnt2[b] = is_big ? (cnt + cl.tt_big - 1) / cl.tt_big : 0;
   }
   __syncthreads();
   const int n_seg = block_exclusive_scan(seg_flag, bins, warp_tot);
   const int n_tiles = block_exclusive_scan(tile_cnt, bins, warp_tot);
   const int n_tiles2 = cl.small_max > 0 ? block_exclusive_scan(tile_cnt2, bins, warp_tot) : 0;
-  const int n_tiles3 = cl.small_max > 0 ? block_exclusive_scan(tile_cnt3, bins, warp_tot) : 0;
   for (int b = tid + 1; b < bins; b += blockDim.x) {
     const int start = bin_start[b], cnt = bin_start[b + 1] - start;
     if (cnt > 0) {
@@ -197,16 +193,12 @@ route_kernel(const RouteSrc src, int T, int D, int W, int TT, int* __restrict__ 
       if (seg_delta) seg_delta[s] = b - 1;
       if (seg_start) seg_start[s] = start;
       if (seg_count) seg_count[s] = cnt;
-      const bool leaves = cl.small_max > 0 && cnt > cl.small_max;
-      if (leaves) {
-        const bool is_big = cnt > cl.mid_max;
-        const RouteList& l = is_big ? cl.big : cl.mid;
-        const int tt = is_big ? cl.tt_big : cl.tt_mid;
-        int tpos = is_big ? tile_cnt3[b] : tile_cnt2[b];
-        for (int off = 0; off < cnt; off += tt, ++tpos) {
-          l.tile_delta[tpos] = b - 1;
-          l.tile_start[tpos] = start + off;
-          l.tile_count[tpos] = min(tt, cnt - off);
+      if (cl.small_max > 0 && cnt > cl.small_max) {
+        int tpos = tile_cnt2[b];
+        for (int off = 0; off < cnt; off += cl.tt_big, ++tpos) {
+          cl.big.tile_delta[tpos] = b - 1;
+          cl.big.tile_start[tpos] = start + off;
+          cl.big.tile_count[tpos] = min(cl.tt_big, cnt - off);
         }
       } else if (tile_delta && tile_start && tile_count) {
         int tpos = tile_cnt[b];
@@ -226,7 +218,6 @@ route_kernel(const RouteSrc src, int T, int D, int W, int TT, int* __restrict__ 
     counters[2] = bin_start[1];
     counters[3] = n_invalid;
     counters[4] = n_tiles2;
-    counters[5] = n_tiles3;
   }
 }
 
@@ -274,12 +265,12 @@ int route_launch_src(const RouteSrc& src, int T, int D, int TT, int* perm, int* 
   const int bins = D + 1;
   // Small batches: 8 warps (cheaper block syncs), and no more histogram copies than 32-token pieces.
   const int threads = (T <= 2048 && bins <= 2048) ? 256 : kRouteThreads;
-  int W = (50000 - 5 * bins - 1) / bins;   // shared-memory budget of ~195 KiB
+  int W = (50000 - 4 * bins - 1) / bins;   // shared-memory budget of ~195 KiB
   const int w_cap = threads / 32, w_need = (T + 31) / 32;
   W = W > w_cap ? w_cap : W;
   W = W > w_need ? w_need : W;
   W = W < 1 ? 1 : W;
-  const size_t smem = (size_t)(bins * W + 5 * bins + 1) * sizeof(int);
+  const size_t smem = (size_t)(bins * W + 4 * bins + 1) * sizeof(int);
   static std::atomic<bool> attr_set[64];
   int dev = 0;
   cudaGetDevice(&dev);
@@ -291,8 +282,7 @@ int route_launch_src(const RouteSrc& src, int T, int D, int TT, int* perm, int* 
   RouteClasses cl{};
   if (classes != nullptr) {
     cl = *classes;
-    if (cl.small_max < 1 || cl.mid_max < cl.small_max || cl.tt_mid < 1 || cl.tt_big < 1 || !cl.mid.tile_delta ||
-        !cl.mid.tile_start || !cl.mid.tile_count || !cl.big.tile_delta || !cl.big.tile_start || !cl.big.tile_count)
+    if (cl.small_max < 1 || cl.tt_big < 1 || !cl.big.tile_delta || !cl.big.tile_start || !cl.big.tile_count)
       return TRB_ERR_BAD_ARG;
   }
   route_kernel<<<1, threads, smem, stream>>>(src, T, D, W, TT, perm, seg_delta, seg_start, seg_count, tile_delta,

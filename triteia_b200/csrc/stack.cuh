@@ -61,8 +61,7 @@ extern "C" int trb_row_checksum(const void* y, void* sums, int rows, int prob_m,
 // host cost per launch is a few microseconds (a Python call per launch costs more than most of
 // these kernels run).  Rows are grouped by (segment size class, delta id); every class is a
 // contiguous row range with its own segment list and gets its own launch per linear, so the
-// grouped kernel that fits the class runs (class_tile[c]: 8 = the decode kernel, 32 = the mma.sp kernel
-// with tiles of 16 or 32 tokens chosen per segment, 256 = the tcgen05 kernel).  `ksplit` (optional): working memory
+// grouped kernel that fits the class runs (class_tile[c]: 8 = the mma.sp kernel, 256 = the tcgen05 kernel).  `ksplit` (optional): working memory
 // of trb_sbmm_ksplit_bytes() bytes for the tail K split of small launches, first 512 bytes zero on
 // entry (and again on exit).  After each linear its output is
 // folded into the per-row checksum.  Arrays are host arrays; the pointers in them are device
@@ -88,8 +87,7 @@ extern "C" int trb_stack_pass(int n_linears, const void* const* q, const void* c
       if (class_rows[c] == 0 || class_segs[c] == 0) continue;
       const __half* x = (const __half*)x_of[i] + (size_t)class_row0[c] * k[i];
       __half* y = (__half*)y_of[i] + (size_t)class_row0[c] * n[i];
-      if (class_tile[c] != trb::kSmallTile && class_tile[c] != trb::kMidTile && class_tile[c] != trb::kBigTile)
-        return TRB_ERR_BAD_ARG;
+      if (class_tile[c] != trb::kSmallTile && class_tile[c] != trb::kBigTile) return TRB_ERR_BAD_ARG;
       const bool small = class_tile[c] == trb::kSmallTile;
       const int rc = sbmm_segments(x, q[i], meta[i], y, s[i], class_ids[c], class_starts[c], class_counts[c], n[i],
                                    class_rows[c], k[i], class_segs[c], groupsize, dev, stream, -1,

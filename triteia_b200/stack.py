@@ -51,11 +51,10 @@ class DeltaStackShard:
         self.layers = layers
         self.n_last = layers[-1][-1].n
 
-    # Segments are handled in size classes, one launch per class and linear: up to 8 rows -> the decode
-    # kernel, 9..128 rows -> the second mma.sp kernel (which tiles every segment by its own length: 16
-    # or 32 rows), longer ones -> the tcgen05 kernel (256-row tiles).
-    CLASS_BOUNDS = (8, 128)
-    CLASS_TILES = (8, 32, 256)
+    # Segments are handled in two size classes, one launch per class and linear: up to 32 rows ->
+    # 8-row tiles of the mma.sp kernel, longer ones -> 256-row tiles of the tcgen05 kernel.
+    CLASS_BOUNDS = (32,)
+    CLASS_TILES = (8, 256)
 
     def _plan(self, local_ids):
         """Rows ordered by (size class, delta id) and, per class, its row range and segment list."""
