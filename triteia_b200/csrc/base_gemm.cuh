@@ -7,34 +7,38 @@
 // delta parts in separate passes over y (triteia/python/ops/matmul/ldmm.py:72-76, 86-107;
 // sbmm.py:90-93; lora.py:5-9).  Here one kernel on the fifth-generation tensor cores produces
 // base + LoRA in one TMEM accumulator and writes y once:
-//   tcgen05.mma.kind::f16, D[M = 128 output features, N = token tile] in tensor memory (two
-//   accumulators, so the epilogue of one work item overlaps the MMAs of the next);
+//   tcgen05.mma.cta_group::2.kind::f16: two CTAs of a cluster work on one item of 256 output features
+//   x one token tile, 128 features each (own A tile, own accumulator: TMEM lanes = features, columns =
+//   tokens) and each stages HALF of the token tile, so an SM pulls a third less through TMA per flop
+//   than alone -- at 256 decode tokens the product is bound by that intake, not by the tensor pipe or
+//   HBM; two accumulators, so the epilogue of one work item overlaps the MMAs of the next;
 //   A operand = W_base rows [128 x 64 K] as they lie in memory (K-major, TMA with 128-byte swizzle),
 //   for the LoRA chunks = B rows [64 Kv x 128 features] as they lie in memory (MN-major operand);
 //   B operand = x (or V) rows [token tile x 64 K], K-major;
-//   warp 0: TMA producer (one thread), warp 1: MMA issuer (one thread) and TMEM owner,
-//   warps 2-5: epilogue (tcgen05.ld, fp16 convert, 32 x 32 transposes through shared memory,
-//   16-byte stores).  Every wait is bounded.
+//   warp 0: TMA producer (one thread), warp 1: MMA issuer (one thread of the leader CTA) and TMEM
+//   owner, warps 2-5: epilogue (tcgen05.ld, fp16 convert, 32 x 32 transposes through shared memory,
+//   16-byte stores), warp 6: tells the leader when this CTA's stage has landed.  No TMA load uses
+//   multicast.  Every wait is bounded; both CTAs meet at a cluster barrier before either leaves.
 #pragma once
 
-#include "tc_common.cuh"
+#include "delta_gemm_tcsp.cuh"
 
 namespace trb {
 
 struct BaseCfg {
   static constexpr int KC = 64;             // K per pipeline stage (one 128-byte swizzle atom of fp16)
-  static constexpr int STAGES = 4;
+  static constexpr int STAGES = 6;
   static constexpr int EPI_WARPS = 4;
-  static constexpr int THREADS = (2 + EPI_WARPS) * 32;
+  static constexpr int THREADS = (3 + EPI_WARPS) * 32;
   static constexpr int MAX_TT = 256;        // largest token tile (UMMA N)
-  static constexpr int A_BYTES = 128 * KC * 2;           // 16 KiB
-  static constexpr int B_BYTES = MAX_TT * KC * 2;        // 32 KiB (a smaller token tile uses the front)
+  static constexpr int A_BYTES = 128 * KC * 2;                 // 16 KiB: this CTA's 128 features
+  static constexpr int B_BYTES = (MAX_TT / 2) * KC * 2;        // 16 KiB: this CTA's half of the token tile
   static constexpr int A_OFF = 0;
   static constexpr int B_OFF = A_BYTES;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;  // 48 KiB, a multiple of 1 KiB
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;        // 32 KiB, a multiple of 1 KiB
   static constexpr int XPOSE_OFF = STAGES * STAGE_BYTES;                  // [EPI_WARPS][32 tokens][32 features] halves
   static constexpr int BAR_OFF = XPOSE_OFF + EPI_WARPS * 2048;
-  static constexpr int NUM_BARS = 2 * STAGES + 4;
+  static constexpr int NUM_BARS = 3 * STAGES + 4;
   static constexpr int SMEM_BYTES = BAR_OFF + NUM_BARS * 8 + 16;
   static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;
   static constexpr uint32_t TMEM_COLS = 512;
@@ -63,13 +67,14 @@ __device__ __forceinline__ uint64_t tc_smem_desc_mn(uint32_t smem_addr, uint32_t
   return d;
 }
 
-// kind::f16 with a run-time instruction descriptor (token tile and operand majorness vary).
-__device__ __forceinline__ void tc_mma_f16_idesc(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                                 uint32_t accumulate) {
+// Dense kind::f16 for a CTA pair with a run-time instruction descriptor (token tile and operand
+// majorness vary): M = 256 (128 TMEM lanes in each CTA), N rows of B split over the two CTAs.
+__device__ __forceinline__ void tc_mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
       : "memory");
 }
@@ -82,10 +87,11 @@ base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::BAR_OFF);   // TMA data of a stage landed
-  uint64_t* empty_bar = full_bar + STAGES;                                 // MMAs of a stage retired
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::BAR_OFF);   // this CTA's TMA data of a stage landed
+  uint64_t* ready_bar = full_bar + STAGES;                                 // leader: both CTAs' data landed
+  uint64_t* empty_bar = ready_bar + STAGES;                                // MMAs of a stage retired
   uint64_t* accready_bar = empty_bar + STAGES;                             // [2] accumulator complete
-  uint64_t* accfree_bar = accready_bar + 2;                                // [2] accumulator drained
+  uint64_t* accfree_bar = accready_bar + 2;                                // [2] leader: accumulator drained by both
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accfree_bar + 2);
   volatile int* dead = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -93,34 +99,39 @@ base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   const int warp = tid >> 5;
   const int lane = tid & 31;
 
+  pdl_launch_dependents();
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
+      mbar_init(&ready_bar[s], 2);
       mbar_init(&empty_bar[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&accready_bar[b], 1);
-      mbar_init(&accfree_bar[b], Cfg::EPI_WARPS);
+      mbar_init(&accfree_bar[b], 2 * Cfg::EPI_WARPS);
     }
     *dead = 0;
     fence_mbar_init();
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
                  "r"(Cfg::TMEM_COLS)
                  : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
   }
-  pdl_launch_dependents();
   pdl_wait();   // x and V may come from the kernels launched just before
   tc_fence_before();
   __syncthreads();
+  cluster_sync_all();     // both CTAs' barriers exist before any remote arrive
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int n_stripes = (a.N + 127) / 128;
+  const uint32_t rank = cluster_ctarank();
+  const int n_stripes = (a.N + 255) / 256;            // an item: 256 features (128 per CTA) x one token tile
   const int n_tiles = (a.T + a.tt - 1) / a.tt;
   const int n_items = n_tiles * n_stripes;            // item = tile * n_stripes + stripe
+  const int item0 = (int)(blockIdx.x >> 1), item_step = (int)(gridDim.x >> 1);
+  const int half_tt = a.tt >> 1;                      // tokens of a tile staged by one CTA
   const int kw = a.K / Cfg::KC;                        // chunks of the base product
   const int kl = (a.kv + Cfg::KC - 1) / Cfg::KC;       // chunks of the LoRA expand
   const int k_chunks = kw + kl;
@@ -137,12 +148,12 @@ base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       }
       const uint64_t pol_w = policy_evict_first();
       const uint64_t pol_x = policy_evict_last();
-      const uint32_t stage_tx = Cfg::A_BYTES + a.tt * Cfg::KC * 2;
+      const uint32_t stage_tx = Cfg::A_BYTES + half_tt * Cfg::KC * 2;
       int st = 0;
       uint32_t phase = 0;
-      for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+      for (int item = item0; item < n_items; item += item_step) {
         const int tile = item / n_stripes, stripe = item - tile * n_stripes;
-        const int row0 = tile * a.tt, col0 = stripe * 128;
+        const int row0 = tile * a.tt + (int)rank * half_tt, col0 = stripe * 256 + (int)rank * 128;
         for (int kc = 0; kc < k_chunks; ++kc) {
           mbar_wait(&empty_bar[st], phase ^ 1, dead);
           uint8_t* sbase = smem + st * Cfg::STAGE_BYTES;
@@ -162,23 +173,23 @@ base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       }
     }
   } else if (warp == 1) {
-    // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
-      // D fp32, A and B fp16; N = token tile, M = 128; bit 15: A is MN-major (the LoRA chunks)
+    // ------------------------------ MMA issuer (leader CTA) ------------------------------
+    if (lane == 0 && rank == 0) {
+      // D fp32, A and B fp16 / bf16; N = token tile, M = 256; bit 15: A is MN-major (the LoRA chunks)
       const uint32_t fmt = a.bf16 ? 1u : 0u;           // operand format field: 0 = fp16, 1 = bf16
-      const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (((uint32_t)a.tt >> 3) << 17) | ((128u >> 4) << 24);
+      const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (((uint32_t)a.tt >> 3) << 17) | ((256u >> 4) << 24);
       const uint32_t idesc_mn = idesc | (1u << 15);
       int st = 0;
       uint32_t phase = 0;
       uint32_t use[2] = {0, 0};
       int local = 0;
-      for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+      for (int item = item0; item < n_items; item += item_step) {
         const int buf = local & 1;
-        mbar_wait(&accfree_bar[buf], (use[buf] & 1) ^ 1, dead);
+        mbar_wait_cluster(&accfree_bar[buf], (use[buf] & 1) ^ 1, dead);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * Cfg::MAX_TT;
         for (int kc = 0; kc < k_chunks; ++kc) {
-          mbar_wait(&full_bar[st], phase, dead);
+          mbar_wait_cluster(&ready_bar[st], phase, dead);
           tc_fence_after();
           const uint32_t sb = smem_base + st * Cfg::STAGE_BYTES;
           const uint64_t bdesc = tc_smem_desc(sb + Cfg::B_OFF);
@@ -186,31 +197,47 @@ base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
             const uint64_t adesc = tc_smem_desc(sb + Cfg::A_OFF);
 #pragma unroll
             for (int k = 0; k < Cfg::KC / 16; ++k)   // +32 bytes of K per instruction = +2 in the address field
-              tc_mma_f16_idesc(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kc > 0 || k > 0) ? 1u : 0u);
+              tc_mma_f16_pair(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kc > 0 || k > 0) ? 1u : 0u);
           } else {
 #pragma unroll
             for (int k = 0; k < Cfg::KC / 16; ++k) {  // 16 K rows of 128 bytes per instruction
-              const uint64_t adesc = tc_smem_desc_mn(sb + Cfg::A_OFF + k * 2048, 8192, 1024);   // 64-feature halves 8 KiB apart, 8-row K groups 1 KiB apart
-              tc_mma_f16_idesc(d_tmem, adesc, bdesc + 2 * k, idesc_mn, (kc > 0 || k > 0) ? 1u : 0u);
+              // 64-feature halves 8 KiB apart, 8-row K groups 1 KiB apart
+              const uint64_t adesc = tc_smem_desc_mn(sb + Cfg::A_OFF + k * 2048, 8192, 1024);
+              tc_mma_f16_pair(d_tmem, adesc, bdesc + 2 * k, idesc_mn, (kc > 0 || k > 0) ? 1u : 0u);
             }
           }
-          tc_commit(&empty_bar[st]);
+          tc_commit_pair(&empty_bar[st]);
           if (++st == STAGES) { st = 0; phase ^= 1; }
         }
-        tc_commit(&accready_bar[buf]);
+        tc_commit_pair(&accready_bar[buf]);
         ++use[buf];
         ++local;
+      }
+    }
+  } else if (warp == 2 + Cfg::EPI_WARPS) {
+    // ------------------------------ stage relay: this CTA's data landed -> the leader ------------------------------
+    if (lane == 0) {
+      const uint32_t ready_leader = mapa_shared(smem_u32(ready_bar), 0);
+      int st = 0;
+      uint32_t phase = 0;
+      for (int item = item0; item < n_items; item += item_step) {
+        for (int kc = 0; kc < k_chunks; ++kc) {
+          mbar_wait(&full_bar[st], phase, dead);
+          mbar_arrive_cluster(ready_leader + st * 8);
+          if (++st == STAGES) { st = 0; phase ^= 1; }
+        }
       }
     }
   } else {
     // ------------------------------ epilogue warps ------------------------------
     const int ew = warp - 2;
     const int quad = warp & 3;                        // TMEM lanes this warp may touch: 32 * quad .. + 31
+    const uint32_t accfree_leader = mapa_shared(smem_u32(accfree_bar), 0);
     uint32_t use[2] = {0, 0};
     int local = 0;
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    for (int item = item0; item < n_items; item += item_step) {
       const int tile = item / n_stripes, stripe = item - tile * n_stripes;
-      const int row0 = tile * a.tt, col0 = stripe * 128;
+      const int row0 = tile * a.tt, col0 = stripe * 256 + (int)rank * 128;
       const int valid = min(a.tt, a.T - row0);
       const int buf = local & 1;
       if (ew == 0) {                                  // one warp polls, the others park on the hardware barrier
@@ -236,7 +263,7 @@ base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         if (b == nbatch - 1) {                        // the accumulator is in registers: hand the buffer back
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&accfree_bar[buf]);
+          if (lane == 0) mbar_arrive_cluster(accfree_leader + buf * 8);
         }
         __half* patch = reinterpret_cast<__half*>(smem + Cfg::XPOSE_OFF + ew * 2048);
         if (a.bf16) {
@@ -289,9 +316,10 @@ base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
 
   tc_fence_before();
   __syncthreads();
+  cluster_sync_all();   // neither CTA leaves, or frees TMEM, while the other may still touch it
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::TMEM_COLS) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::TMEM_COLS) : "memory");
   }
 }
 
@@ -327,7 +355,7 @@ __global__ void __launch_bounds__(256) lora_shrink_rows_kernel(__half* __restric
 #pragma unroll
   for (int e = 0; e < 8; ++e) acc[e] = 0.f;
   if (sub < rv) {
-#pragma unroll 4
+#pragma unroll 8
     for (int k = warp * rows_per_warp + rl; k < h1; k += 8 * rows_per_warp) {
       const float xk = __half2float(x[k]);
       const uint4 wv = *reinterpret_cast<const uint4*>(am + (int64_t)k * rank + sub * 8);
@@ -368,10 +396,10 @@ static int base_gemm_launch(const void* x, const void* w, void* y, int T, int N,
   a.bf16 = bf16;
   const CUtensorMapDataType dt = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUtensorMap tx, tw, tv, tb;
-  if (!make_map_2d(&tx, dt, 2, x, (uint64_t)T, (uint64_t)K, a.tt, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return TRB_ERR_CUDA;
+  if (!make_map_2d(&tx, dt, 2, x, (uint64_t)T, (uint64_t)K, a.tt / 2, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return TRB_ERR_CUDA;
   if (!make_map_2d(&tw, dt, 2, w, (uint64_t)N, (uint64_t)K, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return TRB_ERR_CUDA;
   if (kv > 0) {
-    if (!make_map_2d(&tv, dt, 2, v, (uint64_t)T, (uint64_t)kv, a.tt, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return TRB_ERR_CUDA;
+    if (!make_map_2d(&tv, dt, 2, v, (uint64_t)T, (uint64_t)kv, a.tt / 2, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return TRB_ERR_CUDA;
     if (!make_map_2d(&tb, dt, 2, b, (uint64_t)kv, (uint64_t)N, 64, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return TRB_ERR_CUDA;
   } else {
     tv = tx;   // never dereferenced
@@ -388,19 +416,24 @@ static int base_gemm_launch(const void* x, const void* w, void* y, int T, int N,
       attr_set[dev] = true;
     }
   }
-  const long long items = (long long)((T + a.tt - 1) / a.tt) * ((N + 127) / 128);
-  int grid = sm_count(dev);
-  if (items < grid) grid = (int)items;
+  const long long items = (long long)((T + a.tt - 1) / a.tt) * ((N + 255) / 256);   // one item per CTA pair
+  int pairs = sm_count(dev) / 2;
+  if (pairs < 1) pairs = 1;
+  if (items < pairs) pairs = (int)items;
   cudaLaunchConfig_t lc = {};
-  lc.gridDim = dim3(grid);
+  lc.gridDim = dim3(2 * pairs);
   lc.blockDim = dim3(BaseCfg::THREADS);
   lc.dynamicSmemBytes = BaseCfg::SMEM_ALLOC;
   lc.stream = stream;
-  cudaLaunchAttribute at[1];
+  cudaLaunchAttribute at[2];
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // the kernel waits (pdl_wait) before it reads
   at[0].val.programmaticStreamSerializationAllowed = 1;
+  at[1].id = cudaLaunchAttributeClusterDimension;
+  at[1].val.clusterDim.x = 2;
+  at[1].val.clusterDim.y = 1;
+  at[1].val.clusterDim.z = 1;
   lc.attrs = at;
-  lc.numAttrs = 1;
+  lc.numAttrs = 2;
   return cudaLaunchKernelEx(&lc, base_gemm_kernel, tx, tw, tv, tb, a) == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
 }
 
