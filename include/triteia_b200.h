@@ -48,6 +48,13 @@ const char* trb_status_string(int status);
  * csrc/ops/common/mem.h:112-124). */
 int trb_device_status(int dev, int* status_out);
 
+/* Self-test of the bounded device-side waits: launches one CTA that waits, for at most max_polls
+ * polls (1 .. 1 000 000), on a barrier nothing ever signals.  The wait expires, the kernel stores 1
+ * into *gave_up_flag (device int, may be NULL), records TRB_ERR_TIMEOUT in the device error word and
+ * ends normally: after it trb_device_status reports TRB_ERR_TIMEOUT once, then 0.  No counterpart in
+ * the reference (its waits have no limit, csrc/ops/common/mem.h:112-124). */
+int trb_selftest_timeout(int max_polls, void* gave_up_flag, int dev, void* stream);
+
 /* C[T,N] = A[T,K] @ dequant(B, meta, s).  Overwrites C.
  * Replaces marlin::marlin_cuda_2_4 (csrc/ops/marlin_nm.cu:42-119), same argument order:
  * prob_m = N (output features), prob_n = T (tokens), prob_k = K.  `groupsize` is in dense-K
@@ -270,6 +277,20 @@ int trb_lora_indexed(void* y, const void* x, const void* wa, const void* wb, con
 int trb_base_gemm(const void* x, const void* base_weight, void* y, int num_tokens, int prob_m, int prob_k,
                   const void* lora_v, const void* lora_b, int lora_k, int accumulate, int dtype, int dev,
                   void* stream);
+
+/* SGMV on a stacked weight tensor, on the tcgen05 tensor cores:
+ *   y[s[i] : s[i + 1], :] (+)= x[s[i] : s[i + 1], :] @ w[i],   i < num_problems,
+ * x [num_rows, d_in], y [num_rows, d_out], w [num_problems, d_in, d_out] row-major (the layout of the
+ * Python operators' weights_A / weights_B), s int32 [num_problems + 1] on the device (a negative
+ * s[0] counts as 0).  Same arithmetic as trb_sgmv / sgmv<T> (csrc/ops/sgmv.cuh:61-174: alpha = 1,
+ * beta = 1 with accumulate != 0, fp32 accumulation) without the per-problem pointer array: the
+ * weights of a problem are rows [i * d_in, (i + 1) * d_in) of one tensor, which one TMA descriptor
+ * covers.  Called twice (shrink into v, expand into y) it is the LoRA pair of lora_sgmv
+ * (triteia/python/ops/matmul/lora.py:50-105).  max_rows: an upper bound of the longest segment when
+ * the caller knows one (0: num_rows); it sizes the token tile.  d_in % 8 == 0, d_out % 8 == 0,
+ * num_problems <= 1024; dtype TRB_F16 or TRB_BF16. */
+int trb_sgmv_stacked(void* y, const void* x, const void* w, const void* s, int num_problems, int num_rows,
+                     int d_in, int d_out, int max_rows, int accumulate, int dtype, int dev, void* stream);
 
 /* Shrink half of the indexed LoRA, written as the operand of trb_base_gemm: row b of v[B, v_cols]
  * (fp16) becomes zero except columns [id * rank, (id + 1) * rank) = scale * x[b] @ A[id], with

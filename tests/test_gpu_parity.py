@@ -862,3 +862,77 @@ def test_sbmm_more_than_1024_segments(cuda):
     check(ops.sbmm_4bit_2_4_native(qs, x, metas, ss, idx), ref)
     check(ops.sbmm_4bit_2_4_segments(qs, x, metas, ss, idx), ref)
     assert _lib().device_status(0) == 0
+
+
+# ------------------------------------------------------------------ bounded waits, converter on the device, reference host code
+def test_bounded_wait_expires_and_reports(cuda):
+    """A wait on a barrier nothing signals gives up after its poll limit, the kernel ends normally and
+    the device error word carries TRB_ERR_TIMEOUT exactly once; the context stays usable."""
+    L = _lib()
+    assert L.device_status(0) == 0
+    flag = torch.zeros(1, dtype=torch.int32, device=cuda)
+    L.check(L.lib.trb_selftest_timeout(1000, L.ptr(flag), 0, L.stream_of(flag)), "selftest_timeout")
+    assert L.device_status(0) == L.ERR_TIMEOUT
+    assert int(flag.item()) == 1
+    assert L.device_status(0) == 0
+    qs, metas, ss, x, idx, _ = sbmm_inputs(16, 3, 128, 256, -1, seed=3)
+    check(_ops().sbmm_4bit_2_4_native(qs, x, metas, ss, idx), sbmm_ref(qs, metas, ss, x, idx, None))
+    assert L.device_status(0) == 0
+
+
+def test_converter_on_device_through_sbmm(cuda):
+    """A GPTQ-style module converted on the GPU (packer kernel for fp16 CUDA chunks), tp 1 and 2: the
+    chunks pass the output check of verify_weights, and the tp-1 packed tensors pushed through sbmm as a
+    one-delta set match the oracle on the dequantised source weight."""
+    from tests.test_converter import _gptq_module
+    from triteia_b200.converters.deltazip import convert_state_dict
+    from triteia_b200.converters.verify_weights import check_output, check_tp_group_equal
+    rng = np.random.default_rng(5)
+    src = {}
+    dense = {}
+    for name, k, n in (("model.layers.0.self_attn.q_proj", 256, 512), ("model.layers.0.self_attn.k_proj", 256, 512),
+                       ("model.layers.0.self_attn.v_proj", 256, 512), ("model.layers.0.self_attn.o_proj", 256, 512)):
+        mod, d = _gptq_module(rng, k, n)
+        dense[name] = d
+        for key, t in mod.items():
+            src[f"{name}.{key}"] = t.to(cuda)
+    one = convert_state_dict(src, 1, use_kernel=True)
+    two = convert_state_dict(src, 2, use_kernel=True)
+    assert check_tp_group_equal(two) == []
+    for module in ("model.layers.0.self_attn.qkv_proj", "model.layers.0.self_attn.o_proj"):
+        assert check_output(two, one, module, nr=64) < 1e-2
+    q, m, s = (one[f"model.layers.0.self_attn.qkv_proj.0.{c}"] for c in ("qweight", "meta", "scales"))
+    x = torch.randn(24, 256, dtype=torch.float16, device=cuda, generator=torch.Generator(cuda).manual_seed(1))
+    idx = torch.zeros(24, dtype=torch.int32, device=cuda)
+    y = _ops().sbmm_4bit_2_4_native(q[None], x, m[None], s[None], idx)
+    w = np.concatenate([dense[f"model.layers.0.self_attn.{p}_proj"] for p in "qkv"], axis=1).astype(np.float32)
+    check(y, x.float().cpu().numpy() @ w, mean_tol=None)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rank", [8, 16, 64])
+def test_sgmv_stacked_ragged_segments(cuda, rank, dtype):
+    """The tensor-core SGMV on stacked weights: ragged segments (one empty, one of a single row, one
+    longer than a token tile), rows before the first segment untouched, shrink then expand against
+    the oracle's lora statement."""
+    from triteia_b200.ops.matmul.lora import sgmv_stacked
+    M, K, N = 5, 512, 768
+    lens = [7, 0, 1, 300, 40]
+    lead = 5                                             # rows without an adapter in front
+    T = lead + sum(lens)
+    g = torch.Generator(cuda).manual_seed(rank)
+    A = (torch.randn(M, K, rank, device=cuda, generator=g) / K ** 0.5).to(dtype)
+    B = (torch.randn(M, rank, N, device=cuda, generator=g) / rank ** 0.5).to(dtype)
+    x = torch.randn(T, K, device=cuda, generator=g).to(dtype)
+    seg = torch.tensor(np.concatenate([[lead], lead + np.cumsum(lens)]).astype(np.int32), device=cuda)
+    y0 = torch.randn(T, N, device=cuda, generator=g).to(dtype)
+    y = y0.clone()
+    v = torch.zeros(T, rank, dtype=dtype, device=cuda)
+    sgmv_stacked(v, x, A, seg, accumulate=False)
+    sgmv_stacked(y, v, B, seg, accumulate=True)
+    idx = np.concatenate([np.full(lead, -1)] + [np.full(n, i) for i, n in enumerate(lens)])
+    ref = y0.float().cpu().numpy() + oracle.lora(A.float().cpu().numpy(), B.float().cpu().numpy(), x.float().cpu().numpy(), idx)
+    err = oracle.row_rel_err(y.float().cpu().numpy(), ref)
+    assert err.max() <= (ROW_TOL if dtype == torch.float16 else 3e-2), f"row rel err {err.max():.4g}"
+    assert torch.equal(y[:lead], y0[:lead])
+    assert _lib().device_status(0) == 0

@@ -21,6 +21,7 @@ SIGNATURES = {
     "trb_version": (_i, []),
     "trb_status_string": (ctypes.c_char_p, [_i]),
     "trb_device_status": (_i, [_i, ctypes.POINTER(_i)]),
+    "trb_selftest_timeout": (_i, [_i, _vp, _i, _vp]),
     "trb_mul_2_4": (_i, [_vp] * 5 + [_i] * 3 + [_vp, _i, _i, _vp] + [_i] * 4),
     "trb_sbmm_2_4": (_i, [_vp] * 8 + [_i] * 4 + [_vp, _i, _i, _vp] + [_i] * 4),
     "trb_bmm_2_4": (_i, [_vp] * 5 + [_i] * 3 + [_vp, _i, _i, _vp] + [_i] * 4),
@@ -48,6 +49,7 @@ SIGNATURES = {
     "trb_lora_bgmv_fused": (_i, [_vp] * 5 + [_i] * 6 + [_f, _i, _i, _vp]),
     "trb_lora_indexed": (_i, [_vp] * 5 + [_i] * 6 + [_f, _i, _i, _vp]),
     "trb_base_gemm": (_i, [_vp] * 3 + [_i] * 3 + [_vp, _vp] + [_i] * 4 + [_vp]),
+    "trb_sgmv_stacked": (_i, [_vp] * 4 + [_i] * 9 + [_vp]),
     "trb_lora_shrink_rows": (_i, [_vp] * 4 + [_i] * 6 + [_f, _i, _vp]),
     "trb_sgmv_tmp_size": (_sz, [_i]),
     "trb_sgmv": (_i, [_vp] * 5 + [_i] * 6 + [_vp]),

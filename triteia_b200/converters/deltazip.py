@@ -22,8 +22,9 @@ from ..utils.quant_utils import dequantize_weight
 
 
 @torch.no_grad()
-def convert_state_dict(tensors, tp_size):
-    """tensors: {key: tensor} of the source checkpoint.  Returns the converted {key: tensor}."""
+def convert_state_dict(tensors, tp_size, use_kernel=False):
+    """tensors: {key: tensor} of the source checkpoint.  Returns the converted {key: tensor}.
+    use_kernel: pack fp16 CUDA chunks with the packer kernel instead of the torch packer."""
     new_tensors = {}
     remaining = list(tensors.keys())
     modules = [k[: -len(".qweight")] for k in tensors if k.endswith(".qweight")]
@@ -48,12 +49,12 @@ def convert_state_dict(tensors, tp_size):
             target, pos = pack_modules[src].split(":")
             fused.setdefault(m[: -len(src)] + target, []).append((int(pos), m))
         elif any(m.endswith(k) for k in row_chunking_modules):
-            emit(m, *torch_weight_to_sparse_marlin(dense[m][0], dense[m][1], tp_size=tp_size, chunk_by="row"))
+            emit(m, *torch_weight_to_sparse_marlin(dense[m][0], dense[m][1], tp_size=tp_size, chunk_by="row", use_kernel=use_kernel))
     for name, parts in fused.items():
         parts.sort()
         weight = torch.cat([dense[m][0] for _, m in parts], dim=1)
         scales = torch.cat([dense[m][1] for _, m in parts], dim=1)
-        emit(name, *torch_weight_to_sparse_marlin(weight, scales, tp_size=tp_size, chunk_by="column"))
+        emit(name, *torch_weight_to_sparse_marlin(weight, scales, tp_size=tp_size, chunk_by="column", use_kernel=use_kernel))
     for key in remaining:
         if any(k in key for k in uncompressed_row_chunking_modules) and key.endswith(".weight"):
             w = tensors[key]

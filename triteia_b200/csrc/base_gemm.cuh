@@ -37,7 +37,8 @@ struct BaseCfg {
   static constexpr int B_OFF = A_BYTES;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;        // 32 KiB, a multiple of 1 KiB
   static constexpr int XPOSE_OFF = STAGES * STAGE_BYTES;                  // [EPI_WARPS][32 tokens][32 features] halves
-  static constexpr int BAR_OFF = XPOSE_OFF + EPI_WARPS * 2048;
+  static constexpr int PREFIX_OFF = XPOSE_OFF + EPI_WARPS * 2048;         // int [kMaxSegments + 2]: tiles before each segment
+  static constexpr int BAR_OFF = PREFIX_OFF + (kMaxSegments + 2) * 4;
   static constexpr int NUM_BARS = 3 * STAGES + 4;
   static constexpr int SMEM_BYTES = BAR_OFF + NUM_BARS * 8 + 16;
   static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;
@@ -52,6 +53,11 @@ struct BaseArgs {
   __half* y;          // fp16 or bf16 by `bf16`
   int accumulate;     // y += result instead of y = result
   int bf16;           // operands and output are bfloat16
+  // Segmented form (seg != nullptr), the SGMV of the LoRA operators: rows [seg[i], seg[i + 1]) of the
+  // input [T, seg_k] meet weight i of a stacked tensor [n_seg, seg_k, N] (row-major, so an MN-major
+  // operand as it lies in memory).  K is unused, x is the input, the stacked weights come through tm_b.
+  const int* seg;
+  int n_seg, seg_k;
 };
 
 // MN-major operand, 128-byte swizzle: a row of the tile is one K index and holds 64 consecutive
@@ -87,6 +93,7 @@ base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  int* prefix = reinterpret_cast<int*>(smem + Cfg::PREFIX_OFF);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::BAR_OFF);   // this CTA's TMA data of a stage landed
   uint64_t* ready_bar = full_bar + STAGES;                                 // leader: both CTAs' data landed
   uint64_t* empty_bar = ready_bar + STAGES;                                // MMAs of a stage retired
@@ -120,6 +127,27 @@ base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
   }
   pdl_wait();   // x and V may come from the kernels launched just before
+  const int n_seg = a.seg != nullptr ? max(0, min(a.n_seg, kMaxSegments)) : 0;
+  if (a.seg != nullptr && warp == 0) {   // token tiles before each segment
+    int running = 0;
+    for (int base = 0; base < n_seg; base += 32) {
+      const int sg = base + lane;
+      int c = 0;
+      if (sg < n_seg) {
+        const int cnt = a.seg[sg + 1] - max(0, a.seg[sg]);
+        c = cnt > 0 ? (cnt + a.tt - 1) / a.tt : 0;
+      }
+      int inc = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += v;
+      }
+      if (sg < n_seg) prefix[sg] = running + inc - c;
+      running += __shfl_sync(0xffffffffu, inc, 31);
+    }
+    if (lane == 0) prefix[n_seg] = running;
+  }
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();     // both CTAs' barriers exist before any remote arrive
@@ -128,12 +156,30 @@ base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
 
   const uint32_t rank = cluster_ctarank();
   const int n_stripes = (a.N + 255) / 256;            // an item: 256 features (128 per CTA) x one token tile
-  const int n_tiles = (a.T + a.tt - 1) / a.tt;
+  const int n_tiles = a.seg != nullptr ? prefix[n_seg] : (a.T + a.tt - 1) / a.tt;
   const int n_items = n_tiles * n_stripes;            // item = tile * n_stripes + stripe
+  // Token tile -> (first row, rows in use, segment).
+  auto tile_rows = [&](int tile, int& row0, int& valid, int& sg) {
+    if (a.seg == nullptr) {
+      sg = 0;
+      row0 = tile * a.tt;
+      valid = min(a.tt, a.T - row0);
+      return;
+    }
+    int lo = 0, hi = n_seg;  // largest segment with prefix[seg] <= tile
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (prefix[mid] <= tile) lo = mid; else hi = mid;
+    }
+    sg = lo;
+    const int start = max(0, a.seg[sg]), end = min(a.T, a.seg[sg + 1]);
+    row0 = start + (tile - prefix[sg]) * a.tt;
+    valid = max(0, min(a.tt, end - row0));
+  };
   const int item0 = (int)(blockIdx.x >> 1), item_step = (int)(gridDim.x >> 1);
   const int half_tt = a.tt >> 1;                      // tokens of a tile staged by one CTA
-  const int kw = a.K / Cfg::KC;                        // chunks of the base product
-  const int kl = (a.kv + Cfg::KC - 1) / Cfg::KC;       // chunks of the LoRA expand
+  const int kw = a.seg != nullptr ? 0 : a.K / Cfg::KC;                                  // chunks of the base product
+  const int kl = ((a.seg != nullptr ? a.seg_k : a.kv) + Cfg::KC - 1) / Cfg::KC;         // MN-major chunks (LoRA)
   const int k_chunks = kw + kl;
   const uint32_t smem_base = smem_u32(smem);
 
@@ -153,7 +199,12 @@ base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       uint32_t phase = 0;
       for (int item = item0; item < n_items; item += item_step) {
         const int tile = item / n_stripes, stripe = item - tile * n_stripes;
-        const int row0 = tile * a.tt + (int)rank * half_tt, col0 = stripe * 256 + (int)rank * 128;
+        int row0, valid, sg;
+        tile_rows(tile, row0, valid, sg);
+        row0 += (int)rank * half_tt;
+        const int col0 = stripe * 256 + (int)rank * 128;
+        const int wrow0 = a.seg != nullptr ? sg * a.seg_k : 0;      // first row of this segment's weight
+        const CUtensorMap* tm_in = a.seg != nullptr ? &tm_x : &tm_v;
         for (int kc = 0; kc < k_chunks; ++kc) {
           mbar_wait(&empty_bar[st], phase ^ 1, dead);
           uint8_t* sbase = smem + st * Cfg::STAGE_BYTES;
@@ -164,9 +215,9 @@ base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
           } else {
             const int j = kc - kw;
             // two boxes of [64 K rows x 64 features]: features col0.. and col0 + 64..
-            tma_load_2d_hint(sbase + Cfg::A_OFF, &tm_b, col0, j * Cfg::KC, &full_bar[st], pol_x);
-            tma_load_2d_hint(sbase + Cfg::A_OFF + 8192, &tm_b, col0 + 64, j * Cfg::KC, &full_bar[st], pol_x);
-            tma_load_2d_hint(sbase + Cfg::B_OFF, &tm_v, j * Cfg::KC, row0, &full_bar[st], pol_x);
+            tma_load_2d_hint(sbase + Cfg::A_OFF, &tm_b, col0, wrow0 + j * Cfg::KC, &full_bar[st], pol_x);
+            tma_load_2d_hint(sbase + Cfg::A_OFF + 8192, &tm_b, col0 + 64, wrow0 + j * Cfg::KC, &full_bar[st], pol_x);
+            tma_load_2d_hint(sbase + Cfg::B_OFF, tm_in, j * Cfg::KC, row0, &full_bar[st], pol_x);
           }
           if (++st == STAGES) { st = 0; phase ^= 1; }
         }
@@ -237,8 +288,9 @@ base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     int local = 0;
     for (int item = item0; item < n_items; item += item_step) {
       const int tile = item / n_stripes, stripe = item - tile * n_stripes;
-      const int row0 = tile * a.tt, col0 = stripe * 256 + (int)rank * 128;
-      const int valid = min(a.tt, a.T - row0);
+      int row0, valid, sg;
+      tile_rows(tile, row0, valid, sg);
+      const int col0 = stripe * 256 + (int)rank * 128;
       const int buf = local & 1;
       if (ew == 0) {                                  // one warp polls, the others park on the hardware barrier
         uint32_t polls = 0;
@@ -255,7 +307,7 @@ base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       named_bar_sync(4, Cfg::EPI_WARPS * 32);
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * Cfg::MAX_TT;
-      const int nbatch = (valid + 31) >> 5;
+      const int nbatch = max(1, (valid + 31) >> 5);
       for (int b = 0; b < nbatch; ++b) {
         uint32_t v[32];
         tc_ld32(taddr + b * 32, v);
@@ -386,40 +438,13 @@ __global__ void __launch_bounds__(256) lora_shrink_rows_kernel(__half* __restric
 
 static_assert(BaseCfg::SMEM_ALLOC <= 232448, "shared memory budget of one sm_100 CTA");
 
-static int base_gemm_launch(const void* x, const void* w, void* y, int T, int N, int K, const void* v, const void* b,
-                            int kv, int accumulate, int bf16, int dev, cudaStream_t stream) {
-  BaseArgs a{};
-  a.T = T; a.N = N; a.K = K; a.kv = kv;
-  a.tt = T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
-  a.y = (__half*)y;
-  a.accumulate = accumulate;
-  a.bf16 = bf16;
-  const CUtensorMapDataType dt = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  CUtensorMap tx, tw, tv, tb;
-  if (!make_map_2d(&tx, dt, 2, x, (uint64_t)T, (uint64_t)K, a.tt / 2, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return TRB_ERR_CUDA;
-  if (!make_map_2d(&tw, dt, 2, w, (uint64_t)N, (uint64_t)K, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return TRB_ERR_CUDA;
-  if (kv > 0) {
-    if (!make_map_2d(&tv, dt, 2, v, (uint64_t)T, (uint64_t)kv, a.tt / 2, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return TRB_ERR_CUDA;
-    if (!make_map_2d(&tb, dt, 2, b, (uint64_t)kv, (uint64_t)N, 64, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return TRB_ERR_CUDA;
-  } else {
-    tv = tx;   // never dereferenced
-    tb = tw;
-  }
-  static std::mutex mu;
-  static bool attr_set[64] = {};
-  {
-    std::lock_guard<std::mutex> lock(mu);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-      if (cudaFuncSetAttribute(base_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BaseCfg::SMEM_ALLOC) !=
-          cudaSuccess)
-        return TRB_ERR_CUDA;
-      attr_set[dev] = true;
-    }
-  }
-  const long long items = (long long)((T + a.tt - 1) / a.tt) * ((N + 255) / 256);   // one item per CTA pair
+static int base_gemm_launch_args(const BaseArgs& a, const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tv,
+                                 const CUtensorMap& tb, long long items, int dev, cudaStream_t stream) {
+  static std::atomic<bool> attr_set[64];
+  if (!ensure_smem_attr(base_gemm_kernel, dev, BaseCfg::SMEM_ALLOC, attr_set)) return TRB_ERR_CUDA;
   int pairs = sm_count(dev) / 2;
   if (pairs < 1) pairs = 1;
-  if (items < pairs) pairs = (int)items;
+  if (items < pairs) pairs = (int)(items > 0 ? items : 1);
   cudaLaunchConfig_t lc = {};
   lc.gridDim = dim3(2 * pairs);
   lc.blockDim = dim3(BaseCfg::THREADS);
@@ -435,6 +460,50 @@ static int base_gemm_launch(const void* x, const void* w, void* y, int T, int N,
   lc.attrs = at;
   lc.numAttrs = 2;
   return cudaLaunchKernelEx(&lc, base_gemm_kernel, tx, tw, tv, tb, a) == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
+}
+
+static int token_tile_for(int rows) { return rows <= 32 ? 32 : rows <= 64 ? 64 : rows <= 128 ? 128 : 256; }
+
+static int base_gemm_launch(const void* x, const void* w, void* y, int T, int N, int K, const void* v, const void* b,
+                            int kv, int accumulate, int bf16, int dev, cudaStream_t stream) {
+  BaseArgs a{};
+  a.T = T; a.N = N; a.K = K; a.kv = kv;
+  a.tt = token_tile_for(T);
+  a.y = (__half*)y;
+  a.accumulate = accumulate;
+  a.bf16 = bf16;
+  const CUtensorMapDataType dt = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUtensorMap tx, tw, tv, tb;
+  if (!make_map_2d(&tx, dt, 2, x, (uint64_t)T, (uint64_t)K, a.tt / 2, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return TRB_ERR_CUDA;
+  if (!make_map_2d(&tw, dt, 2, w, (uint64_t)N, (uint64_t)K, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return TRB_ERR_CUDA;
+  if (kv > 0) {
+    if (!make_map_2d(&tv, dt, 2, v, (uint64_t)T, (uint64_t)kv, a.tt / 2, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return TRB_ERR_CUDA;
+    if (!make_map_2d(&tb, dt, 2, b, (uint64_t)kv, (uint64_t)N, 64, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return TRB_ERR_CUDA;
+  } else {
+    tv = tx;   // never dereferenced
+    tb = tw;
+  }
+  const long long items = (long long)((T + a.tt - 1) / a.tt) * ((N + 255) / 256);   // one item per CTA pair
+  return base_gemm_launch_args(a, tx, tw, tv, tb, items, dev, stream);
+}
+
+// Segmented form: y[seg[i] : seg[i + 1]] (+)= x[same rows] @ w[i], w stacked [n_seg, d_in, d_out].
+static int sgmv_stacked_launch(void* y, const void* x, const void* w, const int* seg, int n_seg, int T, int d_in,
+                               int d_out, int max_rows, int accumulate, int bf16, int dev, cudaStream_t stream) {
+  BaseArgs a{};
+  a.T = T; a.N = d_out; a.K = 0; a.kv = 0;
+  a.tt = token_tile_for(max_rows > 0 ? max_rows : T);
+  a.y = (__half*)y;
+  a.accumulate = accumulate;
+  a.bf16 = bf16;
+  a.seg = seg; a.n_seg = n_seg; a.seg_k = d_in;
+  const CUtensorMapDataType dt = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUtensorMap tx, tb;
+  if (!make_map_2d(&tx, dt, 2, x, (uint64_t)T, (uint64_t)d_in, a.tt / 2, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return TRB_ERR_CUDA;
+  if (!make_map_2d(&tb, dt, 2, w, (uint64_t)n_seg * d_in, (uint64_t)d_out, 64, 64, CU_TENSOR_MAP_SWIZZLE_128B))
+    return TRB_ERR_CUDA;
+  const long long items = ((long long)T / a.tt + n_seg) * ((d_out + 255) / 256);     // upper bound: the lengths are on the device
+  return base_gemm_launch_args(a, tx, tx, tx, tb, items, dev, stream);
 }
 
 }  // namespace trb
@@ -453,6 +522,20 @@ extern "C" int trb_base_gemm(const void* x, const void* base_weight, void* y, in
   if (cudaSetDevice(dev) != cudaSuccess) return TRB_ERR_CUDA;
   return base_gemm_launch(x, base_weight, y, num_tokens, prob_m, prob_k, lora_v, lora_b, lora_k, accumulate ? 1 : 0,
                           dtype == TRB_BF16, dev, (cudaStream_t)stream);
+}
+
+extern "C" int trb_sgmv_stacked(void* y, const void* x, const void* w, const void* s, int num_problems, int num_rows,
+                                int d_in, int d_out, int max_rows, int accumulate, int dtype, int dev, void* stream) {
+  using namespace trb;
+  if (num_problems == 0 || num_rows == 0) return TRB_OK;
+  if (num_problems < 0 || num_rows < 0 || !y || !x || !w || !s) return TRB_ERR_BAD_ARG;
+  if (d_in <= 0 || d_out <= 0 || d_in % 8 != 0 || d_out % 8 != 0 || num_problems > kMaxSegments) return TRB_ERR_KERN_SHAPE;
+  if ((long long)num_problems * d_in >= (1ll << 31)) return TRB_ERR_KERN_SHAPE;
+  if (dtype != TRB_F16 && dtype != TRB_BF16) return TRB_ERR_KERN_SHAPE;
+  if (((uintptr_t)x | (uintptr_t)y | (uintptr_t)w) & 15) return TRB_ERR_BAD_ARG;
+  if (cudaSetDevice(dev) != cudaSuccess) return TRB_ERR_CUDA;
+  return sgmv_stacked_launch(y, x, w, (const int*)s, num_problems, num_rows, d_in, d_out, max_rows, accumulate ? 1 : 0,
+                             dtype == TRB_BF16, dev, (cudaStream_t)stream);
 }
 
 extern "C" int trb_lora_shrink_rows(void* v, const void* x, const void* wa, const void* indices, int index_is_64bit,

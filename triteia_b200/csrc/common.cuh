@@ -78,13 +78,14 @@ __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
 // Bounded wait.  `dead` is a CTA-wide shared flag: once any wait of the CTA has expired every
 // later wait returns at once, so a broken pipeline drains in bounded time instead of hanging.
 // The launch's output is then garbage and g_device_status says so.
-__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volatile int* dead) {
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volatile int* dead,
+                                          uint32_t max_polls = kMaxPolls) {
   if (mbar_try_wait(bar, parity)) return;
   uint32_t polls = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return;
     if ((polls & 15u) == 0 && *dead) return;   // the flag is a shared-memory read: not on every poll
-    if (++polls > kMaxPolls) {
+    if (++polls > max_polls) {
       *dead = 1;
       atomicExch(&g_device_status, TRB_ERR_TIMEOUT);
       return;

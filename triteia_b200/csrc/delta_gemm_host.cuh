@@ -496,7 +496,34 @@ extern "C" int trb_device_status(int dev, int* status_out) {
   return TRB_OK;
 }
 
-extern "C" int trb_version(void) { return 100; }
+// Self-test of the bounded waits: one CTA waits on an mbarrier that nothing ever signals, with a
+// limit of `max_polls` polls.  The wait gives up by construction, the kernel records
+// TRB_ERR_TIMEOUT in the device error word and ends normally; nothing hangs and the context stays
+// usable.  trb_device_status then returns (and clears) the code.
+namespace trb {
+__global__ void selftest_timeout_kernel(uint32_t max_polls, int* gave_up) {
+  __shared__ uint64_t bar;
+  __shared__ int dead;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    dead = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  mbar_wait(&bar, 0, &dead, max_polls);     // phase 0 never completes: no arrival is ever made
+  __syncthreads();
+  if (threadIdx.x == 0 && gave_up != nullptr) *gave_up = dead;
+}
+}  // namespace trb
+
+extern "C" int trb_selftest_timeout(int max_polls, void* gave_up_flag, int dev, void* stream) {
+  if (max_polls < 1 || max_polls > 1000000) return TRB_ERR_BAD_ARG;
+  if (cudaSetDevice(dev) != cudaSuccess) return TRB_ERR_CUDA;
+  trb::selftest_timeout_kernel<<<1, 64, 0, (cudaStream_t)stream>>>((uint32_t)max_polls, (int*)gave_up_flag);
+  return cudaGetLastError() == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
+}
+
+extern "C" int trb_version(void) { return 101; }
 
 extern "C" const char* trb_status_string(int status) {
   switch (status) {

@@ -48,20 +48,38 @@ def lora_bgmv(weights_A, weights_B, x, indices, base_weight=None, layer_idx=0, s
     return lora_indexed(y, x, weights_A, weights_B, indices, scale)
 
 
+def sgmv_stacked(y, x, weights, seg, accumulate=True, max_rows=0):
+    """In place: y[seg[i]:seg[i+1]] (+)= x[seg[i]:seg[i+1]] @ weights[i]; weights [S, d_in, d_out]
+    contiguous, seg int32 [S + 1] on the device."""
+    S, d_in, d_out = weights.shape
+    err = lib.trb_sgmv_stacked(ptr(y), ptr(x), ptr(weights), ptr(seg), S, x.shape[0], d_in, d_out, int(max_rows),
+                               int(accumulate), _lib.dtype_tag(x.dtype), dev_of(x), stream_of(x))
+    if err == _lib.ERR_KERN_SHAPE:
+        raise RuntimeError(f"No suitable kernel. d_in={d_in} d_out={d_out} problems={S} dtype={x.dtype}")
+    _lib.check(err, "sgmv_stacked")
+    return y
+
+
 def lora_sgmv(weights_A, weights_B, x, indices, base_weight=None, layer_idx=0):
     """One adapter per contiguous token segment; indices grouped by id with the -1 run first.
-    The segment pointer array is built on the device (the reference loops on the host with
-    `.item()`, lora.py:63-78)."""
+    The segment offsets are built on the device (the reference loops on the host with `.item()`,
+    lora.py:63-78), and shrink and expand are two launches of one tensor-core kernel on the stacked
+    weights as they are (no per-problem pointer arrays; the reference's two grouped GEMMs go through
+    `add_lora_sgmv_cutlass`, triteia/python/capi/punica.py:4-32, which stays available in capi)."""
     y = _base(x, base_weight, weights_B.shape[2])
     M, _, rank = weights_A.shape
     ids = torch.arange(-1, M, device=x.device, dtype=indices.dtype)
     counts = (indices[:, None] == ids[None, :]).sum(0)           # [-1, 0, .., M-1]
     s = torch.cumsum(counts, 0).to(torch.int32)                   # s[i] = first row of adapter i
-    wa = weights_A.unsqueeze(1)
-    wb = weights_B.unsqueeze(1)
-    step_a, step_b = wa.stride(0) * wa.element_size(), wb.stride(0) * wb.element_size()
-    ar = torch.arange(M, device=x.device, dtype=torch.int64)
-    wa_ptr = wa.data_ptr() + ar * step_a
-    wb_ptr = wb.data_ptr() + ar * step_b
-    add_lora_sgmv_cutlass(y, x, wa_ptr, wb_ptr, s, layer_idx, rank)
+    if not (weights_A.is_contiguous() and weights_B.is_contiguous() and x.is_contiguous()):
+        weights_A, weights_B, x = weights_A.contiguous(), weights_B.contiguous(), x.contiguous()
+    if rank % 8 != 0 or x.shape[1] % 8 != 0 or y.shape[1] % 8 != 0 or M > 1024:
+        wa, wb = weights_A.unsqueeze(1), weights_B.unsqueeze(1)   # shapes the tensor-core kernel does not take
+        ar = torch.arange(M, device=x.device, dtype=torch.int64)
+        add_lora_sgmv_cutlass(y, x, wa.data_ptr() + ar * (wa.stride(0) * wa.element_size()),
+                              wb.data_ptr() + ar * (wb.stride(0) * wb.element_size()), s, layer_idx, rank)
+        return y
+    v = torch.empty(x.shape[0], rank, dtype=x.dtype, device=x.device)
+    sgmv_stacked(v, x, weights_A, s, accumulate=False)
+    sgmv_stacked(y, v, weights_B, s, accumulate=True)
     return y
