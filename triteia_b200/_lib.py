@@ -49,7 +49,7 @@ SIGNATURES = {
     "trb_lora_bgmv_fused": (_i, [_vp] * 5 + [_i] * 6 + [_f, _i, _i, _vp]),
     "trb_lora_indexed": (_i, [_vp] * 5 + [_i] * 6 + [_f, _i, _i, _vp]),
     "trb_base_gemm": (_i, [_vp] * 3 + [_i] * 3 + [_vp, _vp] + [_i] * 4 + [_vp]),
-    "trb_sgmv_stacked": (_i, [_vp] * 4 + [_i] * 9 + [_vp]),
+    "trb_sgmv_stacked": (_i, [_vp] * 4 + [_i] * 8 + [_vp]),
     "trb_lora_shrink_rows": (_i, [_vp] * 4 + [_i] * 6 + [_f, _i, _vp]),
     "trb_sgmv_tmp_size": (_sz, [_i]),
     "trb_sgmv": (_i, [_vp] * 5 + [_i] * 6 + [_vp]),
