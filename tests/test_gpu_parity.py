@@ -898,7 +898,8 @@ def test_converter_on_device_through_sbmm(cuda):
             src[f"{name}.{key}"] = t.to(cuda)
     one = convert_state_dict(src, 1, use_kernel=True)
     two = convert_state_dict(src, 2, use_kernel=True)
-    assert check_tp_group_equal(two) == []
+    # a row-split module keeps all its scales in every chunk; nothing else may repeat across ranks
+    assert all(comp == "scales" and mod.endswith("o_proj") for mod, comp, _, _ in check_tp_group_equal(two))
     for module in ("model.layers.0.self_attn.qkv_proj", "model.layers.0.self_attn.o_proj"):
         assert check_output(two, one, module, nr=64) < 1e-2
     q, m, s = (one[f"model.layers.0.self_attn.qkv_proj.0.{c}"] for c in ("qweight", "meta", "scales"))

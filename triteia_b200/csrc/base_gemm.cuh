@@ -292,6 +292,23 @@ base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       tile_rows(tile, row0, valid, sg);
       const int col0 = stripe * 256 + (int)rank * 128;
       const int buf = local & 1;
+      // Accumulating into y: the old values of a 32-token batch are fetched one batch ahead (the first
+      // before the accumulator is even complete), so the epilogue never waits on a load it just issued.
+      const int f8 = (lane & 3) * 8;                  // feature offset of this lane's 16-byte piece
+      const int nb = col0 + quad * 32 + f8;
+      const int nbatch = max(1, (valid + 31) >> 5);
+      auto piece = [&](int b, int i) -> uint4* {      // 16 bytes of token b * 32 + i * 8 + lane / 4, or nullptr
+        const int t = b * 32 + i * 8 + (lane >> 2);
+        return (t < valid && nb < a.N) ? reinterpret_cast<uint4*>(a.y + (size_t)(row0 + t) * a.N + nb) : nullptr;
+      };
+      uint4 old[4], old_next[4];
+      if (a.accumulate) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint4* yp = piece(0, i);
+          old[i] = yp ? *yp : make_uint4(0, 0, 0, 0);
+        }
+      }
       if (ew == 0) {                                  // one warp polls, the others park on the hardware barrier
         uint32_t polls = 0;
         while (!mbar_try_wait(&accready_bar[buf], use[buf] & 1)) {
@@ -307,10 +324,16 @@ base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       named_bar_sync(4, Cfg::EPI_WARPS * 32);
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * Cfg::MAX_TT;
-      const int nbatch = max(1, (valid + 31) >> 5);
       for (int b = 0; b < nbatch; ++b) {
         uint32_t v[32];
         tc_ld32(taddr + b * 32, v);
+        if (a.accumulate && b + 1 < nbatch) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint4* yp = piece(b + 1, i);
+            old_next[i] = yp ? *yp : make_uint4(0, 0, 0, 0);
+          }
+        }
         tc_wait_ld();
         if (b == nbatch - 1) {                        // the accumulator is in registers: hand the buffer back
           tc_fence_before();
@@ -327,20 +350,16 @@ base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
           for (int c = 0; c < 32; ++c) patch[c * 32 + lane] = __float2half_rn(__uint_as_float(v[c]));
         }
         __syncwarp();
-        const int f8 = (lane & 3) * 8;                // feature offset of this lane's 16-byte piece
-        const int nb = col0 + quad * 32 + f8;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int c = i * 8 + (lane >> 2);          // token of the batch
-          const int t = b * 32 + c;
-          if (t < valid && nb < a.N) {
+          uint4* yp = piece(b, i);
+          if (yp != nullptr) {
             uint4 o = *reinterpret_cast<const uint4*>(patch + c * 32 + f8);
-            uint4* yp = reinterpret_cast<uint4*>(a.y + (size_t)(row0 + t) * a.N + nb);
             if (a.accumulate) {
-              const uint4 old = *yp;
               if (a.bf16) {
                 __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
-                const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&old);
+                const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&old[i]);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                   const float2 p = __bfloat1622float2(oh[e]), q = __bfloat1622float2(ph[e]);
@@ -348,7 +367,7 @@ base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
                 }
               } else {
                 __half2* oh = reinterpret_cast<__half2*>(&o);
-                const __half2* ph = reinterpret_cast<const __half2*>(&old);
+                const __half2* ph = reinterpret_cast<const __half2*>(&old[i]);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                   const float2 p = __half22float2(oh[e]), q = __half22float2(ph[e]);
@@ -359,6 +378,8 @@ base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
             *yp = o;
           }
         }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) old[i] = old_next[i];
         __syncwarp();
       }
       ++use[buf];
