@@ -28,7 +28,7 @@ namespace trb {
 struct BaseCfg {
   static constexpr int KC = 64;             // K per pipeline stage (one 128-byte swizzle atom of fp16)
   static constexpr int STAGES = 6;
-  static constexpr int EPI_WARPS = 4;
+  static constexpr int EPI_WARPS = 8;       // two per TMEM lane quadrant: each takes half of the token batches
   static constexpr int THREADS = (3 + EPI_WARPS) * 32;
   static constexpr int MAX_TT = 256;        // largest token tile (UMMA N)
   static constexpr int A_BYTES = 128 * KC * 2;                 // 16 KiB: this CTA's 128 features
@@ -115,7 +115,7 @@ base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&accready_bar[b], 1);
-      mbar_init(&accfree_bar[b], 2 * Cfg::EPI_WARPS);
+      mbar_init(&accfree_bar[b], 2 * Cfg::EPI_WARPS);   // every epilogue warp of both CTAs
     }
     *dead = 0;
     fence_mbar_init();
@@ -292,22 +292,28 @@ base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       tile_rows(tile, row0, valid, sg);
       const int col0 = stripe * 256 + (int)rank * 128;
       const int buf = local & 1;
-      // Accumulating into y: the old values of a 32-token batch are fetched one batch ahead (the first
-      // before the accumulator is even complete), so the epilogue never waits on a load it just issued.
+      // Each warp drains the 32-token batches b0, b0 + 1, ... of its TMEM lane quadrant (two warps share a
+      // quadrant and split the batches).  Accumulating into y: the old values of all its batches are
+      // fetched before the accumulator is complete, so the epilogue never waits on a load it just issued.
+      constexpr int MAXB = BaseCfg::MAX_TT / 32 / 2;    // batches per warp
       const int f8 = (lane & 3) * 8;                  // feature offset of this lane's 16-byte piece
       const int nb = col0 + quad * 32 + f8;
       const int nbatch = max(1, (valid + 31) >> 5);
+      const int per = (nbatch + 1) >> 1;
+      const int b0 = (ew >> 2) * per, b1 = min(nbatch, b0 + per);
       auto piece = [&](int b, int i) -> uint4* {      // 16 bytes of token b * 32 + i * 8 + lane / 4, or nullptr
         const int t = b * 32 + i * 8 + (lane >> 2);
         return (t < valid && nb < a.N) ? reinterpret_cast<uint4*>(a.y + (size_t)(row0 + t) * a.N + nb) : nullptr;
       };
-      uint4 old[4], old_next[4];
+      uint4 old[MAXB][4];
       if (a.accumulate) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint4* yp = piece(0, i);
-          old[i] = yp ? *yp : make_uint4(0, 0, 0, 0);
-        }
+        for (int k = 0; k < MAXB; ++k)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint4* yp = b0 + k < b1 ? piece(b0 + k, i) : nullptr;
+            old[k][i] = yp ? *yp : make_uint4(0, 0, 0, 0);
+          }
       }
       if (ew == 0) {                                  // one warp polls, the others park on the hardware barrier
         uint32_t polls = 0;
@@ -324,22 +330,22 @@ base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       named_bar_sync(4, Cfg::EPI_WARPS * 32);
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * Cfg::MAX_TT;
-      for (int b = 0; b < nbatch; ++b) {
-        uint32_t v[32];
-        tc_ld32(taddr + b * 32, v);
-        if (a.accumulate && b + 1 < nbatch) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const uint4* yp = piece(b + 1, i);
-            old_next[i] = yp ? *yp : make_uint4(0, 0, 0, 0);
-          }
+      for (int k = 0; k < MAXB; ++k) {
+        const int b = b0 + k;
+        uint32_t v[32];
+        if (b < b1) {
+          tc_ld32(taddr + b * 32, v);
+          tc_wait_ld();
         }
-        tc_wait_ld();
-        if (b == nbatch - 1) {                        // the accumulator is in registers: hand the buffer back
+        // hand the buffer back once per warp and item: after its last batch is in registers, or at
+        // once if it has no batch
+        if (b == b1 - 1 || (b1 <= b0 && k == 0)) {
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(accfree_leader + buf * 8);
         }
+        if (b >= b1) continue;
         __half* patch = reinterpret_cast<__half*>(smem + Cfg::XPOSE_OFF + ew * 2048);
         if (a.bf16) {
           __nv_bfloat16* pb = reinterpret_cast<__nv_bfloat16*>(patch);
@@ -359,7 +365,7 @@ base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
             if (a.accumulate) {
               if (a.bf16) {
                 __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
-                const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&old[i]);
+                const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&old[k][i]);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                   const float2 p = __bfloat1622float2(oh[e]), q = __bfloat1622float2(ph[e]);
@@ -367,7 +373,7 @@ base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
                 }
               } else {
                 __half2* oh = reinterpret_cast<__half2*>(&o);
-                const __half2* ph = reinterpret_cast<const __half2*>(&old[i]);
+                const __half2* ph = reinterpret_cast<const __half2*>(&old[k][i]);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                   const float2 p = __half22float2(oh[e]), q = __half22float2(ph[e]);
@@ -378,8 +384,6 @@ base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
             *yp = o;
           }
         }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) old[i] = old_next[i];
         __syncwarp();
       }
       ++use[buf];
