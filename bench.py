@@ -310,10 +310,16 @@ def run_decode(args, world, rank, dev, barrier, dist):
 
     if world == 1:
         op = lambda xd, idd: ops.sbmm_4bit_2_4_native(qs, xd, metas, ss, idd)
+        make_op = lambda: op
         launches_per_step = 3   # router, row gather, grouped kernel
     else:
         exchange_kind, exchange = new_exchange()
         op = lambda xd, idd: exchange(xd, idd)
+
+        def make_op():
+            """An exchange of its own (buffers, barriers) for a step that runs beside other steps."""
+            _, ex = new_exchange()
+            return lambda xd, idd: ex(xd, idd)
         launches_per_step = 5 if exchange_kind == "p2p" else 6   # plan + pack, router + gather + grouped kernel (+ combine)
     step_resident = lambda: op(x_dev, idx_dev)
 
@@ -352,11 +358,12 @@ def run_decode(args, world, rank, dev, barrier, dist):
             self.x_dev, self.idx_dev = torch.empty_like(x_dev), torch.empty_like(idx_dev)
             self.stream = torch.cuda.Stream()
             self.graph = None
+            self.op = op if number == 0 else make_op()
 
         def body(self):
             self.x_dev.copy_(self.x_host, non_blocking=True)
             self.idx_dev.copy_(self.idx_host, non_blocking=True)
-            y = op(self.x_dev, self.idx_dev)
+            y = self.op(self.x_dev, self.idx_dev)
             self.y_host.copy_(y, non_blocking=True)
             return y
 
@@ -388,11 +395,12 @@ def run_decode(args, world, rank, dev, barrier, dist):
         if i >= 2:
             e2e_lat.append((time.perf_counter() - t0) * 1e3)
     barrier()
-    # throughput: at N = 1 three steps in flight on three streams, every slot with its own inputs and its own
-    # scratch, so the copies of one step overlap the kernels of another (the host waits for a slot's
-    # previous result before it reuses the slot).  With the cross-GPU exchange one step is in flight:
-    # its exchange buffers are single.  No flush: every step streams the touched deltas, far more than L2.
-    n_slots = int(os.environ.get("TRB_E2E_SLOTS", "3")) if world == 1 else 1
+    # throughput: three steps in flight on three streams, every slot with its own inputs, its own scratch
+    # and (N > 1) its own exchange buffers and barriers, so the copies and the exchange of one step
+    # overlap the kernels of another (the host waits for a slot's previous result before it reuses
+    # the slot; every rank launches the slots in the same order).  With the NCCL exchange one step is
+    # in flight (one communicator).  No flush: every step streams the touched deltas, far more than L2.
+    n_slots = int(os.environ.get("TRB_E2E_SLOTS", "3")) if (world == 1 or exchange_kind == "p2p") else 1
     slots = [lat_slot] + [E2ESlot(i) for i in range(1, n_slots)]
     e2e_mode = "eager"
     if not args.eager:
