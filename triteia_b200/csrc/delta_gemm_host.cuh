@@ -182,10 +182,7 @@ static_assert(TcSpPairCfg::SMEM_ALLOC <= 232448, "shared memory budget of one sm
 // cut into 8-token tiles up to kSmallSegMax tokens and go to the tcgen05 kernel beyond that.
 // Wide outputs: 256-column items, two warps per column block (half as many work items, so half the
 // per-item cost per byte streamed); otherwise 128-column items, four warps per column block.
-#ifndef TRB_W8_STAGES
-#define TRB_W8_STAGES 5
-#endif
-using CfgWide8 = GemmCfg<1, 4, 2, 8, TRB_W8_STAGES>;
+using CfgWide8 = GemmCfg<1, 4, 2, 8, 5>;
 using CfgNarrow8 = GemmCfg<1, 2, 4, 8, 6>;
 static_assert(CfgWide8::SMEM_ALLOC <= 232448 && CfgNarrow8::SMEM_ALLOC <= 232448, "shared memory budget of one sm_100 CTA");
 constexpr int kSmallTile = 8;      // token tile of the mma.sp kernel
