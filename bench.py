@@ -725,7 +725,8 @@ def run_prefill(args, dev, shape):
 
 # --------------------------------------------------------------------------- stack leg (any N, strong scaling)
 def run_stack(args, world, rank, dev, barrier, dist, layers):
-    """L layers of the seven Llama-2-7B linears, 128 deltas sharded by id over the ranks, 512 tokens in all
+    """L layers of the Llama-2-7B linears (q/k/v and gate/up fused into one packed matrix each, as the
+    reference's converter stores them: four linears per layer), 128 deltas sharded by id over the ranks, 512 tokens in all
     (512 / N per rank), delta id ~ Zipf(1.5); one dispatch and one combine per pass.  Strong scaling: the
     same batch and the same deltas at every N."""
     from triteia_b200 import stack
@@ -773,7 +774,7 @@ def run_stack(args, world, rank, dev, barrier, dist, layers):
     barrier()
     mine = set(range(rank, D, world))
     touched_local = len({int(i) for i in ids_all if int(i) in mine})
-    per_layer = sum(k * n // 4 + k * n // 8 + (k // group) * n * 2 for _, k, n in stack.LLAMA_7B_LINEARS)
+    per_layer = sum(k * n // 4 + k * n // 8 + (k // group) * n * 2 for _, k, n in stack.LLAMA_7B_FUSED_LINEARS)
     t = torch.tensor(times + [t_e2e, float(touched_local)], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -790,7 +791,7 @@ def run_stack(args, world, rank, dev, barrier, dist, layers):
             "steps": steps, "ms_per_step": t_step, "timing": spread(times), "higher_is_better": True,
             "scaling": "strong", "dtype": "f16", "data": "synthetic",
             "config": {"workload": f"stack-llama7b-linears-{L}layers-128deltas-512tok-zipf1.5-g128", "layers": L,
-                       "tokens_total": T_total, "linears_per_pass": 7 * L, "ms_per_layer": t_step / L,
+                       "tokens_total": T_total, "linears_per_pass": len(stack.LLAMA_7B_FUSED_LINEARS) * L, "linears": "qkv and gate_up fused as the reference's converter stores them", "ms_per_layer": t_step / L,
                        "distinct_deltas_touched": len(set(int(i) for i in ids_all)),
                        "touched_on_busiest_rank": int(touched_max), "build_s": t_build,
                        "l2": "inputs larger than L2 (every linear streams its touched deltas: 6-17 MB each, all distinct)",

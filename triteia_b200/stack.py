@@ -28,6 +28,13 @@ LLAMA_7B_LINEARS = (
     ("q", 4096, 4096), ("k", 4096, 4096), ("v", 4096, 4096), ("o", 4096, 4096),
     ("gate", 4096, 11008), ("up", 4096, 11008), ("down", 11008, 4096),
 )
+# The same layer as the reference's converter stores it: q/k/v fused into one packed matrix along the
+# output features, gate/up likewise (triteia/python/configs/models/llama.py:8-14,
+# triteia/tools/converters/convert_deltazip.py:98-123).  Four launches per layer instead of seven,
+# each with up to three times the work items.
+LLAMA_7B_FUSED_LINEARS = (
+    ("qkv", 4096, 3 * 4096), ("o", 4096, 4096), ("gate_up", 4096, 2 * 11008), ("down", 11008, 4096),
+)
 
 
 class StackLinear:
@@ -167,7 +174,7 @@ def stack_sharded(x_by_width, indices, local_stack, n_last, group=None):
     return y, cs
 
 
-def random_stack_shard(num_deltas, rank, world, num_layers, linears=LLAMA_7B_LINEARS, groupsize=128, device="cuda",
+def random_stack_shard(num_deltas, rank, world, num_layers, linears=LLAMA_7B_FUSED_LINEARS, groupsize=128, device="cuda",
                        seed=0):
     """Seeded synthetic shard: for every layer and linear the packed deltas with global ids
     rank, rank + world, ... (local-id order).  Every (layer, linear, global id) has its own seed, so
