@@ -130,6 +130,15 @@ int trb_sbmm_indexed(const void* x, const void* qweights, const void* metas, con
                      int num_deltas, int index_offset, int groupsize, int accumulate,
                      void* scratch, size_t scratch_bytes, int dev, void* stream);
 
+/* trb_sbmm_indexed in two calls with the same arguments and the same scratch: phase 1 = router +
+ * row gather (with accumulate != 0 they write nothing but the scratch, so they may run on another
+ * stream beside the kernel that produces y, e.g. the base product of ldmm), phase 2 = the grouped
+ * kernels, phase 3 = both (= trb_sbmm_indexed).  The caller orders phase 2 after phase 1. */
+int trb_sbmm_indexed_phase(const void* x, const void* qweights, const void* metas, const void* scales,
+                           const void* indices, void* y, int num_tokens, int prob_m, int prob_k,
+                           int num_deltas, int index_offset, int groupsize, int accumulate,
+                           void* scratch, size_t scratch_bytes, int phase, int dev, void* stream);
+
 /* trb_sbmm_indexed without a scratch argument, for hosts that cannot allocate device memory for
  * the library (a server whose arena owns all of HBM and offers foreign code no allocator, a plugin
  * contract that bans cudaMalloc after start-up because it stalls the whole device).  The working

@@ -32,6 +32,7 @@ SIGNATURES = {
     "trb_sbmm_ksplit_bytes": (_sz, []),
     "trb_sbmm_2_4_ksplit": (_i, [_vp] * 8 + [_i] * 6 + [_vp, _vp, _sz]),
     "trb_sbmm_indexed": (_i, [_vp] * 6 + [_i] * 7 + [_vp, _sz, _i, _vp]),
+    "trb_sbmm_indexed_phase": (_i, [_vp] * 6 + [_i] * 7 + [_vp, _sz, _i, _i, _vp]),
     "trb_sbmm_indexed_static_capacity": (_sz, []),
     "trb_sbmm_indexed_static": (_i, [_vp] * 6 + [_i] * 7 + [_i, _vp]),
     "trb_shard_buffer_rows": (_sz, [_i, _i]),

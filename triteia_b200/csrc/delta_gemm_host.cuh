@@ -363,8 +363,10 @@ namespace trb {
 int sbmm_indexed_impl(const void* x, const void* qweights, const void* metas, const void* scales, const RouteSrc& src,
                       void* y, int num_tokens, int prob_m, int prob_k, int num_deltas, int groupsize, int mode,
                       void* scratch, size_t scratch_bytes, int dev, cudaStream_t stream,
-                      const void* y_peers = nullptr, int chunk_rows = 0) {
-  if (num_deltas <= 0) return TRB_ERR_BAD_ARG;
+                      const void* y_peers = nullptr, int chunk_rows = 0, int phases = 3) {
+  // phases: bit 0 = router + gather (they write the scratch only, unless mode 0 zeroes rows of y),
+  // bit 1 = the grouped kernels (they read the scratch and write y).
+  if (num_deltas <= 0 || (phases & 3) == 0) return TRB_ERR_BAD_ARG;
   const int rc = check_common(x, qweights, metas, y, scales, prob_m, num_tokens, prob_k, groupsize);
   if (rc == -1) return TRB_OK;
   if (rc != TRB_OK) return rc;
@@ -396,13 +398,17 @@ int sbmm_indexed_impl(const void* x, const void* qweights, const void* metas, co
   cl.tt_big = kBigTile;
   cl.big = big;
 
-  int r = route_launch_src(src, num_tokens, num_deltas, kSmallTile, perm, nullptr, nullptr, nullptr, small.tile_delta,
-                           small.tile_start, small.tile_count, counters, nullptr, 0, nullptr, stream,
-                           use_big ? &cl : nullptr);
-  if (r != TRB_OK) return r;
-  r = gather_launch(x, perm, counters, x_sorted, y, num_tokens, prob_k, prob_m, mode == 0 ? 1 : 0, stream,
-                    ksplit ? counters + kKsplitCntOffset : nullptr, kKsplitItems);
-  if (r != TRB_OK) return r;
+  int r = TRB_OK;
+  if (phases & 1) {
+    r = route_launch_src(src, num_tokens, num_deltas, kSmallTile, perm, nullptr, nullptr, nullptr, small.tile_delta,
+                         small.tile_start, small.tile_count, counters, nullptr, 0, nullptr, stream,
+                         use_big ? &cl : nullptr);
+    if (r != TRB_OK) return r;
+    r = gather_launch(x, perm, counters, x_sorted, y, num_tokens, prob_k, prob_m, mode == 0 ? 1 : 0, stream,
+                      ksplit ? counters + kKsplitCntOffset : nullptr, kKsplitItems);
+    if (r != TRB_OK) return r;
+  }
+  if (!(phases & 2)) return TRB_OK;
 
   GemmArgs a{};
   a.mode = kSegTiles;
@@ -445,6 +451,23 @@ extern "C" int trb_sbmm_indexed(const void* x, const void* qweights, const void*
   src.id_offset = index_offset;
   return sbmm_indexed_impl(x, qweights, metas, scales, src, y, num_tokens, prob_m, prob_k, num_deltas, groupsize,
                            accumulate ? 1 : 0, scratch, scratch_bytes, dev, (cudaStream_t)stream_v);
+}
+
+// trb_sbmm_indexed in two calls, so that a caller can run the router and the row gather (phase 1:
+// they touch nothing but the scratch when accumulate != 0) on one stream beside other work -- the
+// base product of ldmm -- and the grouped kernels (phase 2) after both.  Same arguments and the
+// same scratch in both calls; phase 3 = trb_sbmm_indexed.
+extern "C" int trb_sbmm_indexed_phase(const void* x, const void* qweights, const void* metas, const void* scales,
+                                      const void* indices, void* y, int num_tokens, int prob_m, int prob_k,
+                                      int num_deltas, int index_offset, int groupsize, int accumulate, void* scratch,
+                                      size_t scratch_bytes, int phase, int dev, void* stream_v) {
+  if (num_tokens > 0 && !indices) return TRB_ERR_BAD_ARG;
+  if (phase < 1 || phase > 3) return TRB_ERR_BAD_ARG;
+  RouteSrc src{};
+  src.indices = (const int*)indices;
+  src.id_offset = index_offset;
+  return sbmm_indexed_impl(x, qweights, metas, scales, src, y, num_tokens, prob_m, prob_k, num_deltas, groupsize,
+                           accumulate ? 1 : 0, scratch, scratch_bytes, dev, (cudaStream_t)stream_v, nullptr, 0, phase);
 }
 
 // Owner-side step of the sharded path: the received exchange buffer (world chunks of cap + 1 rows of K

@@ -85,6 +85,35 @@ def sbmm_indexed(xs, qweights, metas, ss, indices, y=None, index_offset=0):
     return y
 
 
+class IndexedDeltaCall:
+    """`sbmm_indexed(..., y=y)` in two steps, so that the router and the row gather (`plan`, which
+    write nothing but the scratch) can run on another stream beside the kernel that produces y, and
+    the grouped kernels (`run`) after both.  The scratch belongs to the stream that is current at
+    construction; `plan` may be issued on any stream, the caller orders `run` after it."""
+
+    def __init__(self, xs, qweights, metas, ss, indices, y, index_offset=0):
+        T, K = xs.shape
+        D, G, N = ss.shape
+        if indices.dtype != torch.int32:
+            indices = indices.to(torch.int32)
+        self.t = (xs, qweights, metas, ss, indices, y)
+        self.dims = (T, N, K, D, int(index_offset), -1 if G == 1 else K // G)
+        self.buf = scratch(xs.device, lib.trb_sbmm_indexed_scratch_bytes(T, K, D))
+
+    def _call(self, phase):
+        xs, q, m, s, idx, y = self.t
+        T, N, K, D, off, groupsize = self.dims
+        err = lib.trb_sbmm_indexed_phase(ptr(xs), ptr(q), ptr(m), ptr(s), ptr(idx), ptr(y), T, N, K, D, off, groupsize,
+                                         1, ptr(self.buf), self.buf.numel(), phase, dev_of(xs), stream_of(xs))
+        _lib.check(err, "sbmm_indexed_phase")
+
+    def plan(self):
+        self._call(1)
+
+    def run(self):
+        self._call(2)
+
+
 def sbmm_4bit_2_4_native(qweights, xs, metas, ss, indices, base_weight=None):
     if not xs.is_contiguous():
         xs = xs.contiguous()
