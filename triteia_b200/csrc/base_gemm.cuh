@@ -404,12 +404,15 @@ base_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
 // in [0, num_adapters); the row stays zero for any other id.  One CTA per token, A [M, h1, rank] in
 // its natural layout.  This is the shrink half of the reference's BGMV pair
 // (triteia/csrc/ops/bgmv_impl.cuh:15-137) writing straight into the operand of the expand above.
+constexpr int kShrinkThreads = 512;
+
 template <class IdxT>
-__global__ void __launch_bounds__(256) lora_shrink_rows_kernel(__half* __restrict__ V, const __half* __restrict__ X,
+__global__ void __launch_bounds__(kShrinkThreads) lora_shrink_rows_kernel(__half* __restrict__ V, const __half* __restrict__ X,
                                                                const __half* __restrict__ A,
                                                                const IdxT* __restrict__ indices, int h1, int rank,
                                                                int num_adapters, int v_cols, float scale) {
-  __shared__ float part[8][64];
+  constexpr int WARPS = kShrinkThreads / 32;
+  __shared__ float part[WARPS][64];
   const int b = blockIdx.x;
   pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -417,7 +420,7 @@ __global__ void __launch_bounds__(256) lora_shrink_rows_kernel(__half* __restric
   const long long idx = (long long)indices[b];
   const bool has = idx >= 0 && idx < num_adapters;
   const int lo8 = has ? (int)idx * rank / 8 : -1, hi8 = has ? lo8 + rank / 8 : -1;
-  for (int i = tid; i < v_cols / 8; i += 256)
+  for (int i = tid; i < v_cols / 8; i += kShrinkThreads)
     if (i < lo8 || i >= hi8) vrow[i] = make_uint4(0, 0, 0, 0);
   if (!has) return;
   const __half* am = A + idx * (int64_t)h1 * rank;
@@ -433,7 +436,7 @@ __global__ void __launch_bounds__(256) lora_shrink_rows_kernel(__half* __restric
   for (int e = 0; e < 8; ++e) acc[e] = 0.f;
   if (sub < rv) {
 #pragma unroll 8
-    for (int k = warp * rows_per_warp + rl; k < h1; k += 8 * rows_per_warp) {
+    for (int k = warp * rows_per_warp + rl; k < h1; k += WARPS * rows_per_warp) {
       const float xk = __half2float(x[k]);
       const uint4 wv = *reinterpret_cast<const uint4*>(am + (int64_t)k * rank + sub * 8);
       const uint32_t* pwv = reinterpret_cast<const uint32_t*>(&wv);
@@ -456,7 +459,7 @@ __global__ void __launch_bounds__(256) lora_shrink_rows_kernel(__half* __restric
   if (tid < rank) {
     float s = 0.f;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) s += part[w][tid];
+    for (int w = 0; w < WARPS; ++w) s += part[w][tid];
     V[(int64_t)b * v_cols + idx * rank + tid] = __float2half_rn(s * scale);
   }
 }
@@ -575,10 +578,10 @@ extern "C" int trb_lora_shrink_rows(void* v, const void* x, const void* wa, cons
   if (cudaSetDevice(dev) != cudaSuccess) return TRB_ERR_CUDA;
   cudaStream_t st = (cudaStream_t)stream;
   if (index_is_64bit)
-    lora_shrink_rows_kernel<int64_t><<<batch, 256, 0, st>>>((__half*)v, (const __half*)x, (const __half*)wa,
+    lora_shrink_rows_kernel<int64_t><<<batch, kShrinkThreads, 0, st>>>((__half*)v, (const __half*)x, (const __half*)wa,
                                                             (const int64_t*)indices, h1, rank, num_adapters, v_cols, scale);
   else
-    lora_shrink_rows_kernel<int32_t><<<batch, 256, 0, st>>>((__half*)v, (const __half*)x, (const __half*)wa,
+    lora_shrink_rows_kernel<int32_t><<<batch, kShrinkThreads, 0, st>>>((__half*)v, (const __half*)x, (const __half*)wa,
                                                             (const int32_t*)indices, h1, rank, num_adapters, v_cols, scale);
   return cudaGetLastError() == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
 }

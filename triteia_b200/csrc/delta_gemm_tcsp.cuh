@@ -50,7 +50,7 @@ struct TcSpCfgT {
   static constexpr int B_ROWS = TT / CTAS;  // tokens of the tile staged by one CTA
   static constexpr int DECODE_TEAMS = 2;    // teams of 8 warps take alternate K chunks
   static constexpr int DECODE_WARPS = 8 * DECODE_TEAMS;
-  static constexpr int EPI_WARPS = 4;
+  static constexpr int EPI_WARPS = 8;       // two per TMEM lane quadrant: each drains half of the token batches
   static constexpr int THREADS = (3 + DECODE_WARPS + EPI_WARPS) * 32;
   static constexpr int A_BYTES = 128 * (KC / 2) * 2;     // 8 KiB of stored halves
   static constexpr int B_BYTES = B_ROWS * KC * 2;        // 32 KiB, 16 KiB per CTA of a pair
@@ -482,20 +482,26 @@ delta_gemm_tcsp_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
       named_bar_sync(4, Cfg::EPI_WARPS * 32);
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
-      const int nbatch = (w.valid + 31) >> 5;
-      for (int b = 0; b < nbatch; ++b) {
+      const int nbatch = max(1, (w.valid + 31) >> 5);
+      // The two warps of a quadrant split the 32-token batches; each hands the accumulator back once,
+      // when its last batch is in registers (at once if it has none): the next item's MMAs may then
+      // overwrite it.
+      const int per = (nbatch + 1) >> 1;
+      const int b0 = (ew >> 2) * per, b1 = min(nbatch, b0 + per);
+      auto release = [&]() {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (PAIR) mbar_arrive_cluster(mapa_shared(smem_u32(accfree_bar), 0));
+          else mbar_arrive(accfree_bar);
+        }
+      };
+      if (b1 <= b0) release();
+      for (int b = b0; b < b1; ++b) {
         uint32_t v[32];
         tc_ld32(taddr + b * 32, v);
         tc_wait_ld();
-        if (b == nbatch - 1) {
-          // The accumulator is in registers: the next item's MMAs may overwrite it.
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) {
-            if constexpr (PAIR) mbar_arrive_cluster(mapa_shared(smem_u32(accfree_bar), 0));
-            else mbar_arrive(accfree_bar);
-          }
-        }
+        if (b == b1 - 1) release();
         // Transpose the 32-token x 32-feature block through a private 2 KiB patch of shared memory, so
         // that a lane stores 8 consecutive features (16 bytes) of one token instead of one feature.
         {
