@@ -501,6 +501,58 @@ __device__ __forceinline__ PipeState run_unit_body(const GemmArgs& a, uint8_t* s
       }
     }
   }
+  if constexpr (NB == 1 && KQ > 1) {
+    if (a.y_peers != nullptr) {
+      // Results that leave for other GPUs go out in 16-byte pieces: the CTA's 8-token tile is put
+      // together in shared memory (the partner-exchange buffer is free once every owner has read its
+      // partials) and each thread stores eight consecutive features of one token over NVLink, instead
+      // of eight 2-byte stores per thread.
+      constexpr int CT = Cfg::CTHREADS;
+      constexpr int COLS = SW * 64;
+      static_assert(8 * COLS * 2 + 32 <= Cfg::RED_FLOATS * 4, "the staged tile fits the exchange buffer");
+      __half* tile = reinterpret_cast<__half*>(red);
+      int* trow = reinterpret_cast<int*>(tile + 8 * COLS);
+      named_bar_sync(4, CT);
+      if (col_ok) {
+        __half* tp = tile + cb * 64 + g8 * 8;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (j / JW == kq) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              tp[(2 * m4 + h) * COLS + j] = __float2half_rn(acc[j][0][h] * sfa[j % JW]);
+              tp[(2 * m4 + h) * COLS + j + 4] = __float2half_rn(acc[j][0][2 + h] * sfb[j % JW]);
+            }
+          }
+        }
+      }
+      if (warp == 0 && g8 == 0) {
+        trow[2 * m4] = orow[0][0];
+        trow[2 * m4 + 1] = orow[0][1];
+      }
+      named_bar_sync(5, CT);
+      for (int p = warp * 32 + lane; p < COLS; p += CT) {       // 8 tokens x COLS / 8 pieces
+        const int t = p / (COLS / 8), c = (p % (COLS / 8)) * 8;
+        const int r = trow[t];
+        if (r >= 0 && w.col0 + c < a.N) {
+          uint4 o = *reinterpret_cast<const uint4*>(tile + t * COLS + c);
+          uint4* yp = reinterpret_cast<uint4*>(a.y_peers[r >> 20] + (size_t)(r & ((1 << 20) - 1)) * a.N + w.col0 + c);
+          if (a.accumulate) {
+            const uint4 old = *yp;
+            __half2* oh = reinterpret_cast<__half2*>(&o);
+            const __half2* ph = reinterpret_cast<const __half2*>(&old);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 x2 = __half22float2(oh[e]), y2 = __half22float2(ph[e]);
+              oh[e] = __floats2half2_rn(x2.x + y2.x, x2.y + y2.y);
+            }
+          }
+          *yp = o;
+        }
+      }
+      return PipeState{st, phase, first_item};
+    }
+  }
   if (col_ok) {
     // acc[j][nb][h] is (column colb + j, token nb*8 + 2*m4 + h); acc[j][nb][2 + h] is column colb + 4 + j.
 #pragma unroll
