@@ -264,7 +264,8 @@ int route_launch_src(const RouteSrc& src, int T, int D, int TT, int* perm, int* 
   if ((src.indices == nullptr && src.chunk_base == nullptr && T > 0) || counters == nullptr) return TRB_ERR_BAD_ARG;
   const int bins = D + 1;
   // Small batches: 8 warps (cheaper block syncs), and no more histogram copies than 32-token pieces.
-  const int threads = (T <= 2048 && bins <= 2048) ? 256 : kRouteThreads;
+  // every warp should see at most one or two 32-token steps (each step is a chain of dependent loads)
+  const int threads = (T <= 256 && bins <= 2048) ? 256 : kRouteThreads;
   int W = (50000 - 4 * bins - 1) / bins;   // shared-memory budget of ~195 KiB
   const int w_cap = threads / 32, w_need = (T + 31) / 32;
   W = W > w_cap ? w_cap : W;
