@@ -187,24 +187,6 @@ int trb_shard_compute(const void* recv_buf, const void* qweights, const void* me
                       void* scratch, size_t scratch_bytes, int dev, void* stream);
 int trb_shard_combine(const void* back_buf, const void* slot_of, void* y, int num_tokens, int prob_m,
                       int world, int accumulate, int dev, void* stream);
-/* The peer form with both cross-GPU barriers folded into the kernels (no barrier launch at all):
- * peer_sync_ptrs = device array of `world` pointers to every rank's sync array (128 int32, zero at
- * start, peer-mapped memory), sync_state = 4 int32 of this rank's own device memory (zero at
- * start).  The CTA of the pack kernel that finishes last tells every peer "my rows are in your
- * buffer" and waits (bounded) for the same from every peer, so when trb_shard_dispatch_sync's kernel
- * has completed every rank's rows have arrived here; the grouped kernel of trb_shard_compute_sync
- * does the same after its last result row, so when it has completed this rank's output tensor holds
- * every result and no rank still reads its receive buffer.  Every rank makes the same sequence of
- * calls on one exchange.  A wait that expires records TRB_ERR_TIMEOUT (trb_device_status). */
-int trb_shard_dispatch_sync(const void* x, const void* indices, int num_tokens, int prob_k, int world,
-                            void* send_buf, const void* peer_recv_ptrs, int my_rank, void* y_zero,
-                            int prob_m, void* slot_of, void* plan, const void* peer_sync_ptrs,
-                            void* sync_state, int dev, void* stream);
-int trb_shard_compute_sync(const void* recv_buf, const void* qweights, const void* metas,
-                           const void* scales, void* y_work, int world, int cap, int prob_m, int prob_k,
-                           int num_local_deltas, int groupsize, const void* peer_out_ptrs, int my_rank,
-                           void* scratch, size_t scratch_bytes, const void* peer_sync_ptrs,
-                           void* sync_state, int dev, void* stream);
 
 /* Dense fp16 weight [K, N] from a packed delta (W = fp16(level) * fp16(scale), rounded once).
  * The on-GPU statement of the format; bit-exact against the CPU decoder.  No counterpart

@@ -63,7 +63,7 @@ def _worker(rank, world, port, out_dir, backend):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("backend", ["cuda", "p2p", "p2p-barrier"])
+@pytest.mark.parametrize("backend", ["cuda", "p2p"])
 @pytest.mark.parametrize("world", [1, 2])
 def test_sharded_exchange_cuda(cuda, tmp_path, world, backend):
     if torch.cuda.device_count() < world:

@@ -38,8 +38,6 @@ SIGNATURES = {
     "trb_shard_buffer_rows": (_sz, [_i, _i]),
     "trb_shard_dispatch": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _i, _vp]),
     "trb_shard_compute": (_i, [_vp] * 5 + [_i] * 6 + [_vp, _i, _vp, _sz, _i, _vp]),
-    "trb_shard_dispatch_sync": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp]),
-    "trb_shard_compute_sync": (_i, [_vp] * 5 + [_i] * 6 + [_vp, _i, _vp, _sz, _vp, _vp, _i, _vp]),
     "trb_shard_combine": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "trb_unpack_2_4": (_i, [_vp] * 4 + [_i] * 4 + [_vp]),
     "trb_pack_2_4": (_i, [_vp] * 5 + [_i] * 4 + [_vp]),

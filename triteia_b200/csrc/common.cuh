@@ -221,57 +221,6 @@ __device__ __forceinline__ void int4x4_to_half2x2(uint32_t q, uint32_t& lo, uint
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-// ---------------------------------------------------------------------------------------------
-// Barrier across the GPUs of a sharded exchange, folded into the tail of a kernel instead of a
-// launch of its own.  Every CTA calls rank_barrier_tail() as its last act (all `threads` threads of
-// the named barrier `bar_id`; stores to peers come before it).  The CTA that finishes last on this GPU
-// tells every peer "rank me has finished step e" (one int per rank in the peer's sync array, which
-// lives in peer-mapped memory) and waits, with a poll limit, until every peer has told it the same:
-// when the kernel has completed on a GPU, all ranks have finished this kernel's work, and what they
-// stored into this GPU's memory before signalling is visible here.  On expiry the device error
-// word is set and the kernel ends normally.
-//   peer_sync[r]  rank r's sync array (ints); slot selects which of its rows of 64 ints is used
-//   state[0]      steps finished so far (the value signalled is state[0] + 1), state[1] CTAs done
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ void st_release_sys(int* p, int v) {
-  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ int ld_acquire_sys(const int* p) {
-  int v;
-  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void rank_barrier_tail(int* const* peer_sync, int slot, int my_rank, int world, int* state,
-                                                  int bar_id, int threads, int tid, int* smem_flag) {
-  __threadfence_system();                       // this thread's stores to peers are performed
-  named_bar_sync(bar_id, threads);
-  if (tid == 0) {
-    const int old = atomicAdd(&state[1], 1);
-    *smem_flag = (old == (int)gridDim.x - 1) ? 1 : 0;
-  }
-  named_bar_sync(bar_id, threads);
-  if (*smem_flag == 0) return;
-  const int e = *reinterpret_cast<volatile int*>(&state[0]) + 1;
-  if (tid < world) {
-    __threadfence_system();                     // cumulative: every CTA's stores were fenced before it counted in
-    st_release_sys(peer_sync[tid] + slot * 64 + my_rank, e);
-    const int* mine = peer_sync[my_rank] + slot * 64 + tid;
-    uint32_t polls = 0;
-    while (ld_acquire_sys(mine) < e) {
-      __nanosleep(64);
-      if (++polls > kMaxPolls) {
-        atomicExch(&g_device_status, TRB_ERR_TIMEOUT);
-        break;
-      }
-    }
-  }
-  named_bar_sync(bar_id, threads);
-  if (tid == 0) {
-    state[0] = e;
-    state[1] = 0;
-  }
-}
-
 __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t s) {
   __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&s));
   return *reinterpret_cast<uint32_t*>(&r);

@@ -57,10 +57,6 @@ struct GemmArgs {
   // epilogue.  Nobody waits for anybody.  nullptr: no split.
   float* ksplit_buf;
   int* ksplit_cnt;
-  // Sharded path with the cross-GPU barrier in this kernel's tail (nullptr: none): see rank_barrier_tail.
-  int* const* peer_sync;
-  int* sync_state;
-  int my_rank, world;
 };
 constexpr int kKsplitItems = 74;              // at most half a grid of tail items is split
 constexpr int kKsplitSlots = 148;             // pieces over all tail items
@@ -619,8 +615,7 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     fence_mbar_init();
   }
   pdl_wait();   // everything below reads what the kernels launched before this one wrote
-  if (a.mode == kSegTiles && a.n_seg_ptr != nullptr && *a.n_seg_ptr <= 0 && a.peer_sync == nullptr)
-    return;   // the router left this list empty
+  if (a.mode == kSegTiles && a.n_seg_ptr != nullptr && *a.n_seg_ptr <= 0) return;   // the router left this list empty
 
   int n_seg = a.n_seg_ptr ? *a.n_seg_ptr : a.n_seg;
   n_seg = max(0, min(n_seg, a.mode == kSegTiles ? a.n_seg : kMaxSegments));
@@ -726,9 +721,6 @@ delta_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     if (!w.ok) continue;
     ps = run_unit_body<Cfg, NBMAX>(a, smem, ps, wu, w);
   }
-  if (a.peer_sync != nullptr)   // every result row of this GPU is on its way: meet the other GPUs
-    rank_barrier_tail(a.peer_sync, 1, a.my_rank, a.world, a.sync_state, 6, Cfg::CTHREADS, tid,
-                      const_cast<int*>(dead) + 2);
 }
 
 }  // namespace trb

@@ -363,8 +363,7 @@ namespace trb {
 int sbmm_indexed_impl(const void* x, const void* qweights, const void* metas, const void* scales, const RouteSrc& src,
                       void* y, int num_tokens, int prob_m, int prob_k, int num_deltas, int groupsize, int mode,
                       void* scratch, size_t scratch_bytes, int dev, cudaStream_t stream,
-                      const void* y_peers = nullptr, int chunk_rows = 0, int phases = 3,
-                      const void* peer_sync = nullptr, void* sync_state = nullptr, int my_rank = 0, int world = 1) {
+                      const void* y_peers = nullptr, int chunk_rows = 0, int phases = 3) {
   // phases: bit 0 = router + gather (they write the scratch only, unless mode 0 zeroes rows of y),
   // bit 1 = the grouped kernels (they read the scratch and write y).
   if (num_deltas <= 0 || (phases & 3) == 0) return TRB_ERR_BAD_ARG;
@@ -431,10 +430,6 @@ int sbmm_indexed_impl(const void* x, const void* qweights, const void* metas, co
   a.xchg = src.chunk_base;
   a.xchg_row_bytes = src.row_bytes;
   a.chunk_rows = chunk_rows;
-  a.peer_sync = (int* const*)peer_sync;
-  a.sync_state = sync_state ? (int*)sync_state + 2 : nullptr;   // ints 2, 3: the grouped kernel's counters
-  a.my_rank = my_rank;
-  a.world = world;
   a.seg_delta = small.tile_delta; a.seg_start = small.tile_start; a.seg_count = small.tile_count;
   a.n_seg_ptr = counters + 1;
   a.n_seg = (int)cap_small;
@@ -475,14 +470,17 @@ extern "C" int trb_sbmm_indexed_phase(const void* x, const void* qweights, const
                            accumulate ? 1 : 0, scratch, scratch_bytes, dev, (cudaStream_t)stream_v, nullptr, 0, phase);
 }
 
-extern "C" int trb_shard_compute_sync(const void* recv_buf, const void* qweights, const void* metas, const void* scales,
-                                      void* y_work, int world, int cap, int prob_m, int prob_k, int num_local_deltas,
-                                      int groupsize, const void* peer_out_ptrs, int my_rank, void* scratch,
-                                      size_t scratch_bytes, const void* peer_sync_ptrs, void* sync_state, int dev,
-                                      void* stream_v) {
-  if (world < 1 || world > 64 || cap < 1 || !recv_buf || (!y_work && !peer_out_ptrs)) return TRB_ERR_BAD_ARG;
-  if ((peer_sync_ptrs != nullptr) != (sync_state != nullptr) || (peer_sync_ptrs != nullptr && peer_out_ptrs == nullptr))
-    return TRB_ERR_BAD_ARG;
+// Owner-side step of the sharded path: the received exchange buffer (world chunks of cap + 1 rows of K
+// halves, ids in each chunk's last row) goes through the router and the grouped kernel.  Plain form:
+// result rows land in the same slots of `y_work` (world * (cap + 1) rows of N halves), other rows are
+// left alone.  Peer form (peer_out_ptrs != NULL): every result row is stored into its source rank's
+// output tensor [cap, N] at the token's own row, y_work is not used.
+extern "C" int trb_shard_compute(const void* recv_buf, const void* qweights, const void* metas, const void* scales,
+                                 void* y_work, int world, int cap, int prob_m, int prob_k, int num_local_deltas,
+                                 int groupsize, const void* peer_out_ptrs, int my_rank, void* scratch,
+                                 size_t scratch_bytes, int dev, void* stream_v) {
+  (void)my_rank;
+  if (world < 1 || cap < 1 || !recv_buf || (!y_work && !peer_out_ptrs)) return TRB_ERR_BAD_ARG;
   // The id row of a chunk holds cap ids and the row count (plain form), plus cap token rows (peer form).
   if ((long long)(cap + 1) * 4 > (long long)prob_k * 2) return TRB_ERR_PROB_SHAPE;
   if (peer_out_ptrs && ((long long)(2 * cap + 2) * 4 > (long long)prob_k * 2 || cap >= (1 << 20))) return TRB_ERR_PROB_SHAPE;
@@ -493,22 +491,7 @@ extern "C" int trb_shard_compute_sync(const void* recv_buf, const void* qweights
   src.cap = cap;
   src.row_bytes = (long long)prob_k * 2;
   return sbmm_indexed_impl(recv_buf, qweights, metas, scales, src, y_work ? y_work : (void*)recv_buf, (int)rows, prob_m, prob_k, num_local_deltas,
-                           groupsize, 2, scratch, scratch_bytes, dev, (cudaStream_t)stream_v, peer_out_ptrs, cap + 1, 3,
-                           peer_sync_ptrs, sync_state, my_rank, world);
-}
-
-// Owner-side step of the sharded path: the received exchange buffer (world chunks of cap + 1 rows of K
-// halves, ids in each chunk's last row) goes through the router and the grouped kernel.  Plain form:
-// result rows land in the same slots of `y_work` (world * (cap + 1) rows of N halves), other rows are
-// left alone.  Peer form (peer_out_ptrs != NULL): every result row is stored into its source rank's
-// output tensor [cap, N] at the token's own row, y_work is not used.  The _sync form above also folds
-// the second cross-GPU barrier into the grouped kernel (see trb_shard_dispatch_sync).
-extern "C" int trb_shard_compute(const void* recv_buf, const void* qweights, const void* metas, const void* scales,
-                                 void* y_work, int world, int cap, int prob_m, int prob_k, int num_local_deltas,
-                                 int groupsize, const void* peer_out_ptrs, int my_rank, void* scratch,
-                                 size_t scratch_bytes, int dev, void* stream_v) {
-  return trb_shard_compute_sync(recv_buf, qweights, metas, scales, y_work, world, cap, prob_m, prob_k, num_local_deltas,
-                                groupsize, peer_out_ptrs, my_rank, scratch, scratch_bytes, nullptr, nullptr, dev, stream_v);
+                           groupsize, 2, scratch, scratch_bytes, dev, (cudaStream_t)stream_v, peer_out_ptrs, cap + 1);
 }
 
 extern "C" int trb_route(const void* indices, int num_tokens, int num_deltas, int tile_tokens, int index_offset,

@@ -32,9 +32,8 @@ __global__ void shard_pack_kernel(const uint4* __restrict__ x, const int* __rest
                                   int* __restrict__ slot_of, const int* __restrict__ bin_count,
                                   unsigned char* __restrict__ send, unsigned char* const* __restrict__ peers,
                                   int my_rank, uint4* __restrict__ y_zero, int N, int T, int K, int world, int cap,
-                                  int inline_plan, int* const* __restrict__ peer_sync, int* __restrict__ sync_state) {
+                                  int inline_plan) {
   __shared__ int sm_cnt[4];
-  __shared__ int sm_last;
   // Chunk for rank r: in the local send buffer at chunk index r, or (peer mode) straight in rank r's
   // receive buffer at chunk index my_rank, written over NVLink.
   pdl_wait();   // slot_of and bin_count come from the router launched just before
@@ -43,7 +42,6 @@ __global__ void shard_pack_kernel(const uint4* __restrict__ x, const int* __rest
     return peers ? peers[r] + (long long)my_rank * (cap + 1) * row_bytes : send + (long long)r * (cap + 1) * row_bytes;
   };
   const int b = blockIdx.x;
-  auto body = [&]() {
   if (b >= T) {
     const int r = b - T;
     if (r >= world) return;
@@ -95,12 +93,6 @@ __global__ void shard_pack_kernel(const uint4* __restrict__ x, const int* __rest
     ids[q] = indices[b] / world;
     if ((long long)(2 * cap + 2) * 4 <= row_bytes) ids[cap + 1 + q] = b;   // the token's own row, for peer-form results
   }
-  };
-  body();
-  // Peer form with the barrier folded in: when this kernel has completed, every rank's rows have
-  // arrived in this GPU's receive buffer.
-  if (peer_sync != nullptr)
-    rank_barrier_tail(peer_sync, 0, my_rank, world, sync_state, 1, (int)blockDim.x, (int)threadIdx.x, &sm_last);
 }
 
 // y[t] (+)= result row of token t's slot; tokens without a delta are zeroed unless accumulating.
@@ -137,28 +129,10 @@ extern "C" size_t trb_shard_buffer_rows(int num_tokens, int world) {
 }
 
 // Plan + pack: slot_of[T] (out), send buffer [world][T + 1][K] halves (out).  plan: int32 [8 + world].
-extern "C" int trb_shard_dispatch_sync(const void* x, const void* indices, int num_tokens, int prob_k, int world,
-                                       void* send_buf, const void* peer_recv_ptrs, int my_rank, void* y_zero, int prob_m,
-                                       void* slot_of, void* plan, const void* peer_sync_ptrs, void* sync_state, int dev,
-                                       void* stream_v);
-
 extern "C" int trb_shard_dispatch(const void* x, const void* indices, int num_tokens, int prob_k, int world,
                                   void* send_buf, const void* peer_recv_ptrs, int my_rank, void* y_zero, int prob_m,
                                   void* slot_of, void* plan, int dev, void* stream_v) {
-  return trb_shard_dispatch_sync(x, indices, num_tokens, prob_k, world, send_buf, peer_recv_ptrs, my_rank, y_zero, prob_m,
-                                 slot_of, plan, nullptr, nullptr, dev, stream_v);
-}
-
-// trb_shard_dispatch with the first cross-GPU barrier of the peer form inside the pack kernel:
-// peer_sync_ptrs = device array of `world` pointers to every rank's sync array (128 ints, zero at
-// start, peer-mapped memory), sync_state = 4 ints of this rank's own memory (zero at start).
-extern "C" int trb_shard_dispatch_sync(const void* x, const void* indices, int num_tokens, int prob_k, int world,
-                                       void* send_buf, const void* peer_recv_ptrs, int my_rank, void* y_zero, int prob_m,
-                                       void* slot_of, void* plan, const void* peer_sync_ptrs, void* sync_state, int dev,
-                                       void* stream_v) {
   using namespace trb;
-  if ((peer_sync_ptrs != nullptr) != (sync_state != nullptr)) return TRB_ERR_BAD_ARG;
-  if (peer_sync_ptrs != nullptr && peer_recv_ptrs == nullptr) return TRB_ERR_BAD_ARG;
   cudaStream_t stream = (cudaStream_t)stream_v;
   if (num_tokens == 0) return TRB_OK;
   if (num_tokens < 0 || world < 1 || world > 64 || prob_k <= 0 || prob_k % 8 != 0) return TRB_ERR_BAD_ARG;
@@ -190,7 +164,7 @@ extern "C" int trb_shard_dispatch_sync(const void* x, const void* indices, int n
   return cudaLaunchKernelEx(&lc, shard_pack_kernel, (const uint4*)x, (const int*)indices, (int*)slot_of,
                             (const int*)bin_count, (unsigned char*)send_buf, (unsigned char* const*)peer_recv_ptrs,
                             my_rank, (uint4*)y_zero, prob_m, num_tokens, prob_k, world, num_tokens,
-                            inline_plan, (int* const*)peer_sync_ptrs, (int*)sync_state) == cudaSuccess
+                            inline_plan) == cudaSuccess
              ? TRB_OK
              : TRB_ERR_CUDA;
 }

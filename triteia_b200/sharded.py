@@ -92,12 +92,10 @@ class FixedCapacityExchange:
 
     backend "cuda": the three steps are the C-ABI calls trb_shard_dispatch / trb_shard_compute /
     trb_shard_combine with an NCCL all-to-all (equal splits) after the first two.
-    backend "p2p": no collective and no barrier launch; the receive and return buffers are CUDA
-    symmetric memory (torch.distributed._symmetric_memory), the pack kernel and the grouped kernel's
-    epilogue store rows straight into the owner's receive buffer / the source's output tensor over
-    NVLink, and each of the two kernels ends with a cross-GPU barrier in its own tail (the CTA that
-    finishes last signals every peer and waits, bounded, for every peer's signal).
-    backend "p2p-barrier": the same with torch's symmetric-memory barrier launched after each step.  The returned tensor is this object's output
+    backend "p2p": no collective; the receive and return buffers are CUDA symmetric memory
+    (torch.distributed._symmetric_memory), the pack kernel and the grouped kernel's epilogue store
+    rows straight into the owner's receive buffer / the source's output tensor over NVLink, and a
+    cross-GPU barrier follows each of the two steps.  The returned tensor is this object's output
     buffer: the next call overwrites it.  backend "torch": the same buffer layout written with torch ops and a
     caller-supplied local_compute(x_rows, local_ids) -> rows; it exists so that the layout and the
     collectives can be tested on CPU ranks (gloo).
@@ -114,7 +112,7 @@ class FixedCapacityExchange:
         if self.T * 4 + 4 > k * dtype.itemsize:
             raise ValueError("the id row of a chunk must hold num_tokens + 1 int32 values")
         self.rank = dist.get_rank(group)
-        if backend in ("p2p", "p2p-barrier"):
+        if backend == "p2p":
             import torch.distributed._symmetric_memory as symm_mem
 
             grp = group if group is not None else dist.group.WORLD
@@ -125,14 +123,6 @@ class FixedCapacityExchange:
             self.h_recv = symm_mem.rendezvous(self.recv, grp)
             self.h_out = symm_mem.rendezvous(self.y_out, grp)
             self.send = self.y_work = self.y_back = None
-            self.h_sync = self.sync_state = None
-            if backend == "p2p":
-                self.sync = symm_mem.empty(128, dtype=torch.int32, device=device)
-                self.sync.zero_()
-                self.h_sync = symm_mem.rendezvous(self.sync, grp)
-                self.sync_state = torch.zeros(4, dtype=torch.int32, device=device)
-                torch.cuda.synchronize(device)
-                dist.barrier(group)                 # every rank's sync array is zero before anybody signals
         else:
             self.send = torch.zeros(rows, k, dtype=dtype, device=device)
             self.recv = torch.zeros(rows, k, dtype=dtype, device=device)
@@ -142,7 +132,7 @@ class FixedCapacityExchange:
         self.plan = torch.zeros(8 + self.world, dtype=torch.int32, device=device)
         self.q, self.m, self.s = qweights, metas, scales
         self.local_compute = local_compute
-        if backend in ("cuda", "p2p", "p2p-barrier"):
+        if backend in ("cuda", "p2p"):
             from ._lib import lib
             d_local, g, _ = scales.shape
             self.groupsize = -1 if g == 1 else k // g
@@ -195,33 +185,28 @@ class FixedCapacityExchange:
     def __call__(self, x, indices, base_out=None):
         """x [T, K], indices int32 [T] (global ids, -1 = none) -> y [T, N] (= base_out + delta part)."""
         assert x.shape[0] == self.T and x.shape[1] == self.K
-        if self.backend in ("cuda", "p2p", "p2p-barrier"):
+        if self.backend in ("cuda", "p2p"):
             from . import _lib
             from ._lib import lib, ptr, stream_of, dev_of
             dev, st = dev_of(x), stream_of(x)
             if indices.dtype != torch.int32:
                 indices = indices.to(torch.int32)
-            p2p = self.backend != "cuda"
-            fused = self.h_sync is not None if p2p else False      # barriers inside the kernels
-            sync_ptrs = self.h_sync.buffer_ptrs_dev if fused else None
-            _lib.check(lib.trb_shard_dispatch_sync(ptr(x), ptr(indices), self.T, self.K, self.world, ptr(self.send),
-                                                   self.h_recv.buffer_ptrs_dev if p2p else None, self.rank,
-                                                   ptr(self.y_out) if p2p else None, self.N,
-                                                   ptr(self.slot_of), ptr(self.plan), sync_ptrs,
-                                                   ptr(self.sync_state) if fused else None, dev, st), "shard_dispatch")
-            if p2p and not fused:
-                self.h_recv.barrier(channel=0)
-            elif not p2p:
-                dist.all_to_all_single(self.recv, self.send, group=self.group)
-            _lib.check(lib.trb_shard_compute_sync(ptr(self.recv), ptr(self.q), ptr(self.m), ptr(self.s),
-                                                  None if p2p else ptr(self.y_work), self.world, self.T, self.N,
-                                                  self.K, self.d_local, self.groupsize,
-                                                  self.h_out.buffer_ptrs_dev if p2p else None, self.rank,
-                                                  ptr(self.scratch), self.scratch.numel(), sync_ptrs,
-                                                  ptr(self.sync_state) if fused else None, dev, st), "shard_compute")
-            if p2p and not fused:
-                self.h_out.barrier(channel=0)
+            p2p = self.backend == "p2p"
+            _lib.check(lib.trb_shard_dispatch(ptr(x), ptr(indices), self.T, self.K, self.world, ptr(self.send),
+                                              self.h_recv.buffer_ptrs_dev if p2p else None, self.rank,
+                                              ptr(self.y_out) if p2p else None, self.N,
+                                              ptr(self.slot_of), ptr(self.plan), dev, st), "shard_dispatch")
             if p2p:
+                self.h_recv.barrier(channel=0)
+            else:
+                dist.all_to_all_single(self.recv, self.send, group=self.group)
+            _lib.check(lib.trb_shard_compute(ptr(self.recv), ptr(self.q), ptr(self.m), ptr(self.s),
+                                             None if p2p else ptr(self.y_work), self.world, self.T, self.N,
+                                             self.K, self.d_local, self.groupsize,
+                                             self.h_out.buffer_ptrs_dev if p2p else None, self.rank,
+                                             ptr(self.scratch), self.scratch.numel(), dev, st), "shard_compute")
+            if p2p:
+                self.h_out.barrier(channel=0)
                 if base_out is not None:
                     base_out += self.y_out[: self.T]
                     return base_out
