@@ -805,6 +805,66 @@ def run_stack(args, world, rank, dev, barrier, dist, layers):
                          "algorithmic_bytes": alg, "traffic": None}}
 
 
+# --------------------------------------------------------------------------- phases of one sharded step (N > 1)
+def run_shard_phases(args, world, rank, dev, barrier, dist):
+    """Where one step of the sharded headline workload spends its time: growing prefixes of the step
+    (pack kernel, + barrier, + router / gather / grouped kernel, + barrier) and two parts alone, each as
+    a CUDA graph replayed 50 times between barriers; per-step microseconds, max over ranks."""
+    import triteia_b200.ops as ops
+    from triteia_b200 import _lib, sharded
+    from triteia_b200._lib import lib, ptr, stream_of, dev_of
+
+    qs, metas, ss = ops.random_packed_deltas(D_PER_GPU, K, N_OUT, groupsize=GROUP, device=dev, seed=1000 + rank)
+    idx_np = make_indices(rank, TOKENS, D_PER_GPU * world)
+    idx = torch.from_numpy(idx_np).to(dev)
+    x = torch.randn(TOKENS, K, device=dev).half()
+    ex = sharded.FixedCapacityExchange(TOKENS, K, N_OUT, dev, backend="p2p", qweights=qs, metas=metas, scales=ss)
+
+    def pack():
+        _lib.check(lib.trb_shard_dispatch(ptr(x), ptr(idx), TOKENS, K, world, None, ex.h_recv.buffer_ptrs_dev, rank,
+                                          ptr(ex.y_out), N_OUT, ptr(ex.slot_of), ptr(ex.plan), dev_of(x), stream_of(x)), "pack")
+
+    def compute():
+        _lib.check(lib.trb_shard_compute(ptr(ex.recv), ptr(qs), ptr(metas), ptr(ss), None, world, TOKENS, N_OUT, K,
+                                         D_PER_GPU, GROUP, ex.h_out.buffer_ptrs_dev, rank, ptr(ex.scratch),
+                                         ex.scratch.numel(), dev_of(x), stream_of(x)), "compute")
+    b1, b2 = (lambda: ex.h_recv.barrier(channel=0)), (lambda: ex.h_out.barrier(channel=0))
+    variants = [("pack kernel", lambda: pack()), ("pack + barrier", lambda: (pack(), b1())),
+                ("pack + barrier + router, gather, grouped kernel", lambda: (pack(), b1(), compute())),
+                ("full step (+ barrier)", lambda: (pack(), b1(), compute(), b2())),
+                ("router, gather, grouped kernel alone", lambda: compute()), ("one barrier alone", lambda: b1())]
+    for _ in range(3):
+        ex(x, idx)
+    barrier()
+    out = {}
+    for name, fn in variants:
+        graph, _ = graph_of(fn, barrier)
+        for _ in range(5):
+            graph.replay()
+        ts = []
+        for _ in range(7):
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(50):
+                graph.replay()
+            b.record()
+            b.synchronize()
+            ts.append(a.elapsed_time(b) * 1e3 / 50)
+        t = torch.tensor([statistics.median(ts)], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out[name] = float(t.item())
+    if rank != 0:
+        return None
+    rows = int((idx_np >= 0).sum())
+    full = out["full step (+ barrier)"]
+    return {"metric": METRIC, "value": TOKENS * world / (full * 1e-6), "unit": UNIT, "n_gpus": world, "steps": 50,
+            "ms_per_step": full * 1e-3, "higher_is_better": True, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": WORKLOAD + "-sharded-step-phases", "us_per_step": out,
+                       "nvlink_bytes_per_rank_and_step": {"rows_out": int(rows * (world - 1) / world * K * 2),
+                                                          "results_back": int(rows * (world - 1) / world * N_OUT * 2)}}}
+
+
 # --------------------------------------------------------------------------- GPU arm
 def run_gpu_arm(args):
     import torch.distributed as dist
@@ -851,6 +911,10 @@ def run_gpu_arm(args):
             results[leg] = run_ldmm(args, dev)
         elif leg in ("prefill_up", "prefill_down") and world == 1:
             results[leg] = run_prefill(args, dev, leg.split("_")[1])
+        elif leg == "shard_phases":
+            if world < 2:
+                raise SystemExit("bench.py: --workload shard_phases needs --gpus 2 or more (torchrun)")
+            results[leg] = run_shard_phases(args, world, rank, dev, barrier, dist)
         free()
         barrier()
     clocks = sampler.stop() if rank == 0 else None
@@ -887,7 +951,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
     ap.add_argument("--no-legs", action="store_true", help="headline leg only (profiling runs)")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of CUDA-graph replays")
-    ap.add_argument("--workload", default="all", choices=["all", "decode", "prefill_up", "prefill_down", "ldmm", "stack"],
+    ap.add_argument("--workload", default="all", choices=["all", "decode", "prefill_up", "prefill_down", "ldmm", "stack", "shard_phases"],
                     help="all = the headline sbmm configuration with the other configurations as `legs` (default); "
                          "one name = that leg alone")
     ap.add_argument("--layers", type=int, default=2, help="stack: number of layers (2: 19 GB of deltas in all; 8 fits one GPU)")
