@@ -228,24 +228,24 @@ int trb_rotary_embedding(const void* positions, void* query, void* key, const vo
 int trb_row_checksum(const void* y, void* sums, int rows, int prob_m, int accumulate, int dev,
                      void* stream);
 
-/* One pass of a stack of n_linears independent delta linears over grouped rows, issued from C (the
- * host cost of a launch made from Python exceeds the run time of most of these kernels).  Rows
- * [class_row0[c], +class_rows[c]) form size class c with its own segment list (class_ids /
- * class_starts / class_counts, class_segs[c] entries, starts relative to the class's first row) and
- * its kernel: class_tile[c] = 8 (short segments: 8-row tiles of the mma.sp kernel) or 256 (long
- * segments: 256-row tiles of the tcgen05 kernel).  Per linear i every class
- * gets one segment-list launch on x_of[i] [rows, k[i]] -> y_of[i] [rows, n[i]], then y_of[i] is
- * folded into checksum [rows] fp32 (trb_row_checksum, accumulate).  ksplit: NULL, or
- * trb_sbmm_ksplit_bytes() bytes of working memory (256-byte aligned, first 512 bytes zero on entry
- * and again on exit) that lets under-filled launches cut their work items along K.  All arrays are
- * host arrays of device pointers / ints.  No counterpart in the reference. */
+/* One pass of a stack of n_linears independent delta linears over one routed batch, issued from C
+ * with no host read in between.  ids[r] (int32, device) selects the delta of row r in EVERY linear
+ * (ids outside [0, num_deltas): no delta, outputs count as zero), so rows are routed once: one router
+ * launch, one row gather per input width, then per linear the tcgen05 launch (segments of more than
+ * 32 rows; only when rows > 128), the mma.sp launch (8-row tiles, tail K split) and the fold of the
+ * output into the per-row checksum (trb_row_checksum semantics).  Host arrays of device pointers /
+ * ints: x_of_width[w] [rows, width[w]] fp16 in the caller's row order, xs_of_width[w] scratch of the
+ * same size, k[i] (one of width[]) and n[i] the shape of linear i, y_of[i] [rows, n[i]] fp16 scratch
+ * (buffers of one n may be shared).  y_last [rows, n[n_linears-1]]: output of the last linear in the
+ * caller's row order; checksum [rows] fp32, caller's row order, ADDED to.  scratch:
+ * trb_stack_scratch_bytes(rows, num_deltas) bytes, 256-byte aligned, no initial contents needed.
+ * No counterpart in the reference. */
+size_t trb_stack_scratch_bytes(int rows, int num_deltas);
 int trb_stack_pass(int n_linears, const void* const* q, const void* const* meta,
-                   const void* const* s, const int* k, const int* n, const void* const* x_of,
-                   void* const* y_of, int n_classes, const int* class_row0, const int* class_rows,
-                   const void* const* class_ids, const void* const* class_starts,
-                   const void* const* class_counts, const int* class_segs, const int* class_tile,
-                   void* checksum, int rows, int groupsize, void* ksplit, size_t ksplit_bytes, int dev,
-                   void* stream);
+                   const void* const* s, const int* k, const int* n, int n_widths, const int* width,
+                   const void* const* x_of_width, void* const* xs_of_width, void* const* y_of,
+                   void* y_last, const void* ids, int rows, int num_deltas, void* checksum,
+                   int groupsize, void* scratch, size_t scratch_bytes, int dev, void* stream);
 
 /* BGMV: Y[b, :] += scale * W[indices[b], layer_idx] @ X[b, :], W [M, L, h_out, h_in]
  * contiguous, indices int64 [B].  Replaces bgmv_kernel<feat_in, feat_out, T>

@@ -138,33 +138,3 @@ def test_sharded_stack_world2(tmp_path, case):
     for r in range(world):
         res = torch.load(os.path.join(str(tmp_path), f"s{r}.pt"))
         assert res["ok"], res
-
-
-def test_stack_plan_groups_rows_by_size_class_and_delta():
-    """Row order and per-class segment lists of the stack's local pass (pure torch, no GPU)."""
-    from triteia_b200.stack import DeltaStackShard
-
-    counts = {0: 40, 1: 3, 2: 9, 3: 1, 5: 33, 7: 8, 9: 32}          # delta id -> rows
-    ids = torch.cat([torch.full((c,), d, dtype=torch.int32) for d, c in counts.items()])
-    ids = ids[torch.randperm(ids.numel(), generator=torch.Generator().manual_seed(0))]
-    shard = DeltaStackShard.__new__(DeltaStackShard)                  # _plan needs no weights
-    order, classes = shard._plan(ids)
-    assert sorted(order.tolist()) == list(range(ids.numel()))
-    sorted_ids = ids[order]
-    seen, at_expected = set(), 0
-    lo = (0,) + tuple(b + 1 for b in DeltaStackShard.CLASS_BOUNDS)
-    hi = DeltaStackShard.CLASS_BOUNDS + (1 << 30,)
-    class_of = lambda c: next(i for i in range(len(hi)) if lo[i] <= c <= hi[i])
-    for at, n_rows, uniq, starts, cnts, tile in classes:
-        assert at == at_expected
-        at_expected += n_rows
-        cls = {class_of(int(c)) for c in cnts.tolist()}
-        assert len(cls) == 1                                          # one size class per launch
-        assert tile == DeltaStackShard.CLASS_TILES[cls.pop()]
-        assert uniq.tolist() == sorted(uniq.tolist())
-        for d, s, c in zip(uniq.tolist(), starts.tolist(), cnts.tolist()):
-            assert c == counts[d] and d not in seen
-            seen.add(d)
-            assert torch.all(sorted_ids[at + s: at + s + c] == d)     # starts are relative to the class
-        assert int(cnts.sum()) == n_rows
-    assert at_expected == ids.numel() and seen == set(counts)

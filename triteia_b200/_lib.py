@@ -45,7 +45,8 @@ SIGNATURES = {
     "trb_silu_and_mul": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),
     "trb_rotary_embedding": (_i, [_vp] * 5 + [_i, _i, ctypes.c_longlong, ctypes.c_longlong] + [_i] * 6 + [_vp]),
     "trb_row_checksum": (_i, [_vp] * 2 + [_i] * 4 + [_vp]),
-    "trb_stack_pass": (_i, [_i] + [_vp] * 7 + [_i] + [_vp] * 8 + [_i] * 2 + [_vp, _sz, _i, _vp]),
+    "trb_stack_scratch_bytes": (_sz, [_i, _i]),
+    "trb_stack_pass": (_i, [_i] + [_vp] * 5 + [_i, _vp] + [_vp] * 5 + [_i, _i, _vp, _i, _vp, _sz, _i, _vp]),
     "trb_bgmv": (_i, [_vp] * 4 + [_i] * 5 + [_f, _i, _i, _vp]),
     "trb_lora_bgmv_fused": (_i, [_vp] * 5 + [_i] * 6 + [_f, _i, _i, _vp]),
     "trb_lora_indexed": (_i, [_vp] * 5 + [_i] * 6 + [_f, _i, _i, _vp]),

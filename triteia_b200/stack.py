@@ -10,10 +10,11 @@ token's delta id selects the same delta in every linear, id -1 means "no delta" 
 Protocol of one pass (one exchange each way, whatever the number of layers):
   1. every rank sends each of its tokens that has a delta ONCE, as the row [x_4096 | x_11008],
      with its local delta id, to owner(id) = id % world (NCCL all-to-all; counts first);
-  2. the owner groups the received rows once, by segment size class and delta (sort + one segment
-     list per class; a handful of host reads per pass), then runs every linear of every layer on
-     the grouped rows with the segment-list kernel entry point, one launch per size class (no
-     router and no gather per linear), and folds each output into a per-token fp32 checksum;
+  2. the owner routes the received rows once on the device (router + one gather per input width: a
+     row's delta is the same in every linear), then runs every linear of every layer on the routed
+     rows from one C call with no host read (tcgen05 launch for long segments, mma.sp launch for
+     the rest, no router and no gather per linear), and folds each output into a per-token fp32
+     checksum;
   3. the last linear's output rows and the checksums travel back and are scattered into token order.
 The linears are independent (each reads the seeded activation of its input width), so the result
 does not depend on the number of ranks.
@@ -58,41 +59,6 @@ class DeltaStackShard:
         self.layers = layers
         self.n_last = layers[-1][-1].n
 
-    # Segments are handled in two size classes, one launch per class and linear: up to 32 rows ->
-    # 8-row tiles of the mma.sp kernel, longer ones -> 256-row tiles of the tcgen05 kernel.
-    CLASS_BOUNDS = (32,)
-    CLASS_TILES = (8, 256)
-
-    def _plan(self, local_ids):
-        """Rows ordered by (size class, delta id) and, per class, its row range and segment list."""
-        from .ops.matmul.sbmm import _segments
-
-        dev = local_ids.device
-        ids64 = local_ids.to(torch.int64)
-        counts = torch.bincount(ids64)
-        bounds = torch.tensor(self.CLASS_BOUNDS, device=dev)
-        cls_of = torch.bucketize(counts, bounds)                      # 0: <= 8 rows ... 3: > 32 rows
-        big = int(counts.numel()) + 1
-        order = torch.argsort(cls_of[ids64] * big + ids64, stable=True)
-        ids_sorted = local_ids[order].to(torch.int32).contiguous()
-        cls_sorted = cls_of[ids64][order]
-        cls_rows = torch.bincount(cls_sorted, minlength=len(self.CLASS_BOUNDS) + 1).tolist()   # host read (once per pass)
-        classes, at = [], 0
-        for ci, n_rows in enumerate(cls_rows):
-            if n_rows:
-                uniq, starts, cnts = _segments(ids_sorted[at:at + n_rows])   # sizes its outputs on the host
-                classes.append((at, n_rows, uniq, starts, cnts, self.CLASS_TILES[ci]))
-            at += n_rows
-        return order, classes
-
-    def _ksplit(self, dev):
-        """Working memory of the grouped kernel's tail K split (zero on entry, left zero by every launch)."""
-        from . import _lib
-
-        if getattr(self, "_ksplit_buf", None) is None or self._ksplit_buf.device != dev:
-            self._ksplit_buf = torch.zeros(_lib.lib.trb_sbmm_ksplit_bytes(), dtype=torch.uint8, device=dev)
-        return self._ksplit_buf
-
     def _static_arrays(self):
         """Host arrays of the per-linear device pointers and shapes (built once)."""
         import ctypes
@@ -106,6 +72,8 @@ class DeltaStackShard:
         return self._static
 
     def __call__(self, x_by_width, local_ids):
+        """One C call, no host read: the rows are routed once on the device (every linear uses the same
+        delta per row), gathered once per input width, and every linear runs on the routed rows."""
         import ctypes
         from . import _lib
 
@@ -114,29 +82,29 @@ class DeltaStackShard:
         if rows == 0:
             return (torch.empty(0, self.n_last, dtype=torch.float16, device=dev),
                     torch.empty(0, dtype=torch.float32, device=dev))
-        order, classes = self._plan(local_ids)
-        xs = {k: x.index_select(0, order).contiguous() for k, x in x_by_width.items()}
         lins, q_arr, m_arr, s_arr, k_arr, n_arr = self._static_arrays()
+        if local_ids.dtype != torch.int32:
+            local_ids = local_ids.to(torch.int32)
+        widths = sorted(x_by_width)
+        xs = [x_by_width[k].contiguous() for k in widths]
+        xs_sorted = [torch.empty_like(x) for x in xs]
         ybuf = {n: torch.empty(rows, n, dtype=torch.float16, device=dev) for n in {l.n for l in lins}}
+        y_last = torch.empty(rows, self.n_last, dtype=torch.float16, device=dev)
         checksum = torch.zeros(rows, dtype=torch.float32, device=dev)
-        vp_l, vp_c, ci_c = ctypes.c_void_p * len(lins), ctypes.c_void_p * len(classes), ctypes.c_int * len(classes)
-        x_arr = vp_l(*[_lib.ptr(xs[l.k]) for l in lins])
-        y_arr = vp_l(*[_lib.ptr(ybuf[l.n]) for l in lins])
+        num_deltas = int(lins[0].qweights.shape[0])
+        nbytes = _lib.lib.trb_stack_scratch_bytes(rows, num_deltas)
+        if getattr(self, "_scratch", None) is None or self._scratch.numel() < nbytes or self._scratch.device != dev:
+            self._scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        vp_l, vp_w, ci_w = ctypes.c_void_p * len(lins), ctypes.c_void_p * len(widths), ctypes.c_int * len(widths)
         groupsize = 128 if lins[0].scales.shape[1] > 1 else -1
         err = _lib.lib.trb_stack_pass(
-            len(lins), q_arr, m_arr, s_arr, k_arr, n_arr, x_arr, y_arr, len(classes),
-            ci_c(*[c[0] for c in classes]), ci_c(*[c[1] for c in classes]),
-            vp_c(*[_lib.ptr(c[2]) for c in classes]), vp_c(*[_lib.ptr(c[3]) for c in classes]),
-            vp_c(*[_lib.ptr(c[4]) for c in classes]), ci_c(*[int(c[2].numel()) for c in classes]),
-            ci_c(*[c[5] for c in classes]), _lib.ptr(checksum), rows, groupsize, _lib.ptr(self._ksplit(dev)),
-            _lib.lib.trb_sbmm_ksplit_bytes(), _lib.dev_of(checksum), _lib.stream_of(checksum))
+            len(lins), q_arr, m_arr, s_arr, k_arr, n_arr, len(widths), ci_w(*widths),
+            vp_w(*[_lib.ptr(x) for x in xs]), vp_w(*[_lib.ptr(x) for x in xs_sorted]),
+            vp_l(*[_lib.ptr(ybuf[l.n]) for l in lins]), _lib.ptr(y_last), _lib.ptr(local_ids), rows, num_deltas,
+            _lib.ptr(checksum), groupsize, _lib.ptr(self._scratch), self._scratch.numel(), _lib.dev_of(checksum),
+            _lib.stream_of(checksum))
         _lib.check(err, "stack_pass")
-        y = ybuf[self.n_last]
-        y_out = torch.empty_like(y)
-        y_out[order] = y
-        cs_out = torch.empty_like(checksum)
-        cs_out[order] = checksum
-        return y_out, cs_out
+        return y_last, checksum
 
 
 def stack_sharded(x_by_width, indices, local_stack, n_last, group=None):
