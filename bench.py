@@ -751,12 +751,13 @@ def run_stack(args, world, rank, dev, barrier, dist, layers):
     idx = idx_host.to(dev)
     y_host = torch.empty(T, 4096, dtype=torch.float16).pin_memory()
     cs_host = torch.empty(T, dtype=torch.float32).pin_memory()
-    step = lambda: stack.stack_sharded(xs, idx, local, 4096)
+    exchange = stack.FixedStackExchange(T, (4096, 11008), 4096, dev)
+    step = lambda: exchange(xs, idx, local)
 
     def step_e2e():
         xd = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
         idd = idx_host.to(dev, non_blocking=True)
-        y, cs = stack.stack_sharded(xd, idd, local, 4096)
+        y, cs = exchange(xd, idd, local)
         y_host.copy_(y, non_blocking=True)
         cs_host.copy_(cs, non_blocking=True)
         torch.cuda.current_stream().synchronize()
@@ -790,14 +791,17 @@ def run_stack(args, world, rank, dev, barrier, dist, layers):
     return {"metric": "stack_tokens_per_s", "value": T_total / (t_step * 1e-3), "unit": UNIT, "n_gpus": world,
             "steps": steps, "ms_per_step": t_step, "timing": spread(times), "higher_is_better": True,
             "scaling": "strong", "dtype": "f16", "data": "synthetic",
+            # own kernels per pass: pack, router, one gather per input width, per linear the 256-token-tile launch,
+            # the 8-token-tile launch and the checksum, and the combine
+            "gpu_launches": steps * (5 + 3 * len(stack.LLAMA_7B_FUSED_LINEARS) * L),
             "config": {"workload": f"stack-llama7b-linears-{L}layers-128deltas-512tok-zipf1.5-g128", "layers": L,
                        "tokens_total": T_total, "linears_per_pass": len(stack.LLAMA_7B_FUSED_LINEARS) * L, "linears": "qkv and gate_up fused as the reference's converter stores them", "ms_per_layer": t_step / L,
                        "distinct_deltas_touched": len(set(int(i) for i in ids_all)),
                        "touched_on_busiest_rank": int(touched_max), "build_s": t_build,
                        "l2": "inputs larger than L2 (every linear streams its touched deltas: 6-17 MB each, all distinct)",
                        "parallelism": "single GPU" if world == 1 else
-                       f"deltas sharded by id over {world} GPUs; one dispatch of [x4096|x11008] rows + ids "
-                       "and one combine (last output + checksums) per pass"},
+                       f"deltas sharded by id over {world} GPUs; one equal-split all-to-all of [x4096|x11008] rows + ids "
+                       "and one of last outputs + checksums per pass (fixed-capacity buffers, no host synchronisation)"},
             "e2e": {"value": T_total / (t_e2e * 1e-3), "unit": UNIT, "ms_per_step": t_e2e,
                     "h2d_bytes_per_step": int(T * (4096 + 11008) * 2 + T * 4), "d2h_bytes_per_step": int(T * 4096 * 2 + T * 4)},
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,

@@ -112,6 +112,8 @@ def _stack_worker(rank, world, port, out_dir):
             if call == 1:
                 idx[: T // 2] = 3            # a hot delta
             y, cs = stack.stack_sharded(xs, idx, local, linears[-1][2])
+            y2, cs2 = stack.FixedStackExchange(T, [k for k in xs], linears[-1][2], dev)(xs, idx, local)
+            assert torch.equal(y2, y) and torch.allclose(cs2, cs, rtol=1e-6, atol=1e-6)
             torch.cuda.synchronize()
             idx_np = idx.cpu().numpy()
             cs_ref = np.zeros(T, dtype=np.float64)

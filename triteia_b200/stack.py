@@ -142,6 +142,61 @@ def stack_sharded(x_by_width, indices, local_stack, n_last, group=None):
     return y, cs
 
 
+class FixedStackExchange:
+    """`stack_sharded` for CUDA ranks without counts on the host: fixed-capacity exchange buffers (as
+    sharded.FixedCapacityExchange: `world` chunks of T + 1 rows, the last row of a chunk carries the
+    rows' local ids and their number), packed by the library's pack kernel, two equal-split NCCL
+    all-to-alls per pass (rows + ids out; last output + checksums back, the checksums in the spare
+    row of every chunk), no host synchronisation.  The owner runs its stack over all world * T slots;
+    unused slots carry id -1 and cost nothing.  Buffers are allocated once per (T, widths, n_last)."""
+
+    def __init__(self, num_tokens, widths, n_last, device, group=None):
+        self.T, self.widths, self.n_last = int(num_tokens), sorted(int(w) for w in widths), int(n_last)
+        self.W = sum(self.widths)
+        self.group, self.world, self.rank = group, dist.get_world_size(group), dist.get_rank(group)
+        if self.T * 4 + 4 > self.W * 2 or self.T * 4 > self.n_last * 2:
+            raise ValueError("a row must hold num_tokens + 1 int32 ids, an output row num_tokens fp32 checksums")
+        rows = self.world * (self.T + 1)
+        z = lambda cols: torch.zeros(rows, cols, dtype=torch.float16, device=device)
+        self.send, self.recv, self.y_work, self.y_back = z(self.W), z(self.W), z(self.n_last), z(self.n_last)
+        self.slot_of = torch.zeros(max(self.T, 1), dtype=torch.int32, device=device)
+        self.plan = torch.zeros(8 + self.world, dtype=torch.int32, device=device)
+        self.col = torch.arange(self.T, device=device)
+
+    def __call__(self, x_by_width, indices, local_stack):
+        from . import _lib
+        from ._lib import lib, ptr, stream_of, dev_of
+
+        w, T = self.world, self.T
+        row = torch.cat([x_by_width[k] for k in self.widths], dim=1)          # each token travels once
+        if indices.dtype != torch.int32:
+            indices = indices.to(torch.int32)
+        dev, st = dev_of(row), stream_of(row)
+        _lib.check(lib.trb_shard_dispatch(ptr(row), ptr(indices), T, self.W, w, ptr(self.send), None, self.rank, None,
+                                          self.n_last, ptr(self.slot_of), ptr(self.plan), dev, st), "shard_dispatch")
+        dist.all_to_all_single(self.recv, self.send, group=self.group)
+        recv3 = self.recv.view(w, T + 1, self.W)
+        idrow = recv3[:, T, :].view(torch.int32)
+        local_ids = torch.where(self.col[None, :] < idrow[:, T:T + 1], idrow[:, :T],
+                                torch.full_like(idrow[:, :T], -1)).reshape(-1).contiguous()
+        parts, at = {}, 0
+        for k in self.widths:
+            parts[k] = recv3[:, :T, at:at + k].reshape(w * T, k)
+            at += k
+        y_w, cs_w = local_stack(parts, local_ids)
+        work3 = self.y_work.view(w, T + 1, self.n_last)
+        work3[:, :T] = y_w.view(w, T, self.n_last)
+        work3[:, T, :].view(torch.float32)[:, :T] = cs_w.view(w, T)
+        dist.all_to_all_single(self.y_back, self.y_work, group=self.group)
+        y = torch.empty(T, self.n_last, dtype=torch.float16, device=row.device)
+        _lib.check(lib.trb_shard_combine(ptr(self.y_back), ptr(self.slot_of), ptr(y), T, self.n_last, w, 0, dev, st),
+                   "shard_combine")
+        cs_all = self.y_back.view(w, T + 1, self.n_last)[:, T, :].view(torch.float32)[:, :T].reshape(-1)
+        slot = self.slot_of[:T].long()
+        cs = torch.where(slot >= 0, cs_all[slot.clamp(min=0)], torch.zeros((), device=row.device))
+        return y, cs
+
+
 def random_stack_shard(num_deltas, rank, world, num_layers, linears=LLAMA_7B_FUSED_LINEARS, groupsize=128, device="cuda",
                        seed=0):
     """Seeded synthetic shard: for every layer and linear the packed deltas with global ids
