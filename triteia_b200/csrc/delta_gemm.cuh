@@ -420,15 +420,16 @@ __device__ __forceinline__ PipeState run_unit_body(const GemmArgs& a, uint8_t* s
   // [kq*JW, (kq+1)*JW): it hands its partial sums of the other j's to their owners through shared
   // memory, adds the partners' partials to its own in a fixed order, and writes its columns.
   // The exchange runs in rounds of at most two token blocks (the buffer holds that much).
-  // Barrier 2 (before the stores) keeps a round's partials until every reader of the previous
-  // round is done; barrier 1 separates stores from loads.
+  // Only the KQ warps of a column block meet (two hardware barriers per column block): the one
+  // before the stores keeps a round's partials until every reader of the previous round is done,
+  // the other separates stores from loads.
   if constexpr (KQ > 1) {
     constexpr int CT = Cfg::CTHREADS;
     constexpr int LANES = SW * 32;
     constexpr int NBH = NB < 2 ? NB : 2;
 #pragma unroll
     for (int h0 = 0; h0 < NB; h0 += NBH) {
-      if (!first_item) named_bar_sync(2, CT);
+      if (!first_item) named_bar_sync(6 + 2 * cb, KQ * 32);
       first_item = false;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -442,7 +443,7 @@ __device__ __forceinline__ PipeState run_unit_body(const GemmArgs& a, uint8_t* s
             for (int c = 0; c < 4; ++c) dst[(nb * 4 + c) * LANES] = acc[j][h0 + nb][c];
         }
       }
-      named_bar_sync(1, CT);
+      named_bar_sync(7 + 2 * cb, KQ * 32);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         if (j / JW == kq) {
@@ -550,6 +551,7 @@ __device__ __forceinline__ PipeState run_unit_body(const GemmArgs& a, uint8_t* s
           *yp = o;
         }
       }
+      named_bar_sync(4, CT);   // the tile has been read: the buffer may take the next unit's partials
       return PipeState{st, phase, first_item};
     }
   }
