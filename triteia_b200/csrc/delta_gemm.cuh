@@ -102,7 +102,11 @@ struct GemmCfg {
   static constexpr int RED_OFF = STAGES * STAGE_BYTES;
   static constexpr int PREFIX_OFF = RED_OFF + RED_FLOATS * 4;
   static constexpr int BAR_OFF = PREFIX_OFF + (kMaxSegments + 2) * 4;
-  static constexpr int SMEM_BYTES = BAR_OFF + 2 * STAGES * 8 + 16;
+  // Staging of result tiles that leave for other GPUs: per column block 8 tokens x 64 halves, then
+  // the 8 tokens' destination rows.
+  static constexpr int STG_OFF = (BAR_OFF + 2 * STAGES * 8 + 16 + 15) / 16 * 16;
+  static constexpr int STG_BLOCK_BYTES = 8 * 64 * 2 + 32;
+  static constexpr int SMEM_BYTES = STG_OFF + SW * STG_BLOCK_BYTES;
   static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;  // slack to align the base to 1 KiB
 };
 
@@ -504,40 +508,37 @@ __device__ __forceinline__ PipeState run_unit_body(const GemmArgs& a, uint8_t* s
   }
   if constexpr (NB == 1 && KQ > 1) {
     if (a.y_peers != nullptr) {
-      // Results that leave for other GPUs go out in 16-byte pieces: the CTA's 8-token tile is put
-      // together in shared memory (the partner-exchange buffer is free once every owner has read its
-      // partials) and each thread stores eight consecutive features of one token over NVLink, instead
-      // of eight 2-byte stores per thread.
-      constexpr int CT = Cfg::CTHREADS;
-      constexpr int COLS = SW * 64;
-      static_assert(8 * COLS * 2 + 32 <= Cfg::RED_FLOATS * 4, "the staged tile fits the exchange buffer");
-      __half* tile = reinterpret_cast<__half*>(red);
-      int* trow = reinterpret_cast<int*>(tile + 8 * COLS);
-      named_bar_sync(4, CT);
+      // Results that leave for other GPUs go out in 16-byte pieces: the partner warps of a column
+      // block put their 8-token x 64-column tile together in shared memory, meet once on their own
+      // barrier, and each lane stores eight consecutive features of one token over NVLink, instead
+      // of eight 2-byte stores per lane.  Nothing here is CTA-wide.  The tile is written again only
+      // after the next unit's exchange barriers, which a partner reaches after its loads below.
+      __half* tile = reinterpret_cast<__half*>(smem + Cfg::STG_OFF + cb * Cfg::STG_BLOCK_BYTES);
+      int* trow = reinterpret_cast<int*>(tile + 8 * 64);
       if (col_ok) {
-        __half* tp = tile + cb * 64 + g8 * 8;
+        __half* tp = tile + g8 * 8;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           if (j / JW == kq) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-              tp[(2 * m4 + h) * COLS + j] = __float2half_rn(acc[j][0][h] * sfa[j % JW]);
-              tp[(2 * m4 + h) * COLS + j + 4] = __float2half_rn(acc[j][0][2 + h] * sfb[j % JW]);
+              tp[(2 * m4 + h) * 64 + j] = __float2half_rn(acc[j][0][h] * sfa[j % JW]);
+              tp[(2 * m4 + h) * 64 + j + 4] = __float2half_rn(acc[j][0][2 + h] * sfb[j % JW]);
             }
           }
         }
       }
-      if (warp == 0 && g8 == 0) {
+      if (kq == 0 && g8 == 0) {
         trow[2 * m4] = orow[0][0];
         trow[2 * m4 + 1] = orow[0][1];
       }
-      named_bar_sync(5, CT);
-      for (int p = warp * 32 + lane; p < COLS; p += CT) {       // 8 tokens x COLS / 8 pieces
-        const int t = p / (COLS / 8), c = (p % (COLS / 8)) * 8;
+      named_bar_sync(7 + 2 * cb, KQ * 32);
+      for (int p = kq * 32 + lane; p < 64; p += KQ * 32) {       // 8 tokens x 8 pieces
+        const int t = p >> 3, c = (p & 7) * 8;
         const int r = trow[t];
-        if (r >= 0 && w.col0 + c < a.N) {
-          uint4 o = *reinterpret_cast<const uint4*>(tile + t * COLS + c);
-          uint4* yp = reinterpret_cast<uint4*>(a.y_peers[r >> 20] + (size_t)(r & ((1 << 20) - 1)) * a.N + w.col0 + c);
+        if (r >= 0 && col_ok) {
+          uint4 o = *reinterpret_cast<const uint4*>(tile + t * 64 + c);
+          uint4* yp = reinterpret_cast<uint4*>(a.y_peers[r >> 20] + (size_t)(r & ((1 << 20) - 1)) * a.N + w.col0 + cb * 64 + c);
           if (a.accumulate) {
             const uint4 old = *yp;
             __half2* oh = reinterpret_cast<__half2*>(&o);
@@ -551,7 +552,6 @@ __device__ __forceinline__ PipeState run_unit_body(const GemmArgs& a, uint8_t* s
           *yp = o;
         }
       }
-      named_bar_sync(4, CT);   // the tile has been read: the buffer may take the next unit's partials
       return PipeState{st, phase, first_item};
     }
   }
