@@ -550,6 +550,24 @@ def test_ldmm_full_size_properties(cuda):
     ref = oracle.ldmm(idx[sub].cpu().numpy(), x[sub].cpu().numpy(), A.cpu().numpy(), B.cpu().numpy(), qs.cpu().numpy(),
                       metas.cpu().numpy(), ss.cpu().numpy(), base.cpu().numpy())
     check(yfull[sub], ref, mean_tol=None)
+    # 64 more rows over every id of the batch, three 128-column windows each (first, middle, last
+    # stripe): base + adapter or delta, stated with the oracle's column-block decoder
+    idx_np = idx.cpu().numpy()
+    more = np.array(_sampled_rows(idx_np, per_id=3, seed=2))
+    assert len(more) >= 64
+    x32 = x[torch.from_numpy(more).to(cuda)].float().cpu().numpy()
+    A32, B32, base32 = A.float().cpu().numpy(), B.float().cpu().numpy(), base.float().cpu().numpy()
+    for blk0 in (0, 86, N // 64 - 2):
+        c0, c1 = 64 * blk0, 64 * blk0 + 128
+        ref = x32 @ base32[c0:c1].T
+        delta_ids = np.where(idx_np[more] >= M, idx_np[more] - M, -1).astype(np.int32)
+        ref += oracle.sbmm_rows(qs, x[torch.from_numpy(more).to(cuda)], metas, ss, delta_ids, np.arange(len(more)), blk0, 2)
+        for i, t in enumerate(more):
+            a = idx_np[t]
+            if 0 <= a < M:
+                ref[i] += (x32[i] @ A32[a]) @ B32[a][:, c0:c1]
+        got = yfull[torch.from_numpy(more).to(cuda)][:, c0:c1].float().cpu().numpy()
+        assert oracle.row_rel_err(got, ref).max() <= 1e-2
 
 
 def test_sbmm_prefill_full_size_properties(cuda):
@@ -569,6 +587,15 @@ def test_sbmm_prefill_full_size_properties(cuda):
     ref = oracle.sbmm(qs.cpu().numpy()[[0, 1, 7, 15]], x[rows].cpu().numpy(), metas.cpu().numpy()[[0, 1, 7, 15]],
                       ss.cpu().numpy()[[0, 1, 7, 15]], np.array([0, 0, 1, 2, 3]))
     check(y[rows], ref)
+    # four rows of every segment, three 128-column windows (first, middle, last stripe)
+    idx_np = idx.cpu().numpy()
+    more = np.array(_sampled_rows(idx_np, per_id=4, seed=3))
+    assert len(more) == 4 * SEG
+    xm = x[torch.from_numpy(more).to(cuda)]
+    for blk0 in (0, 107, N // 64 - 2):
+        ref = oracle.sbmm_rows(qs, xm, metas, ss, idx_np[more], np.arange(len(more)), blk0, 2)
+        got = y[torch.from_numpy(more).to(cuda)][:, 64 * blk0:64 * blk0 + 128].float().cpu().numpy()
+        assert oracle.row_rel_err(got, ref).max() <= 1e-2
     small = torch.cat([torch.arange(0, 8), torch.arange(512, 520), torch.arange(8184, 8192)]).to(cuda)
     ys = ops.sbmm_4bit_2_4_native(qs, x[small].contiguous(), metas, ss, idx[small].contiguous())
     assert oracle.row_rel_err(ys.float().cpu().numpy(), y[small].float().cpu().numpy()).max() <= 2e-3
