@@ -1,9 +1,8 @@
 """Generate the golden fixtures under tests/golden/ from the reference's own Python code.
 
-Run once in a container that has the reference checkout (default: /root/reference,
-override with TRITEIA_REFERENCE=<path>):
+Run once where a checkout of the reference is at hand, with TRITEIA_REFERENCE pointing at it:
 
-    python tests/golden/make_golden.py
+    TRITEIA_REFERENCE=<path of the checkout> python tests/golden/make_golden.py
 
 The reference's Python host code is imported on CPU.  Three things are stubbed so
 that it imports without a GPU: the `triteia_cuda` extension module, `pynvml`
@@ -26,7 +25,9 @@ import types
 import numpy as np
 import torch
 
-REF = os.environ.get("TRITEIA_REFERENCE", "/root/reference")
+REF = os.environ.get("TRITEIA_REFERENCE")
+if not REF or not os.path.isdir(REF):
+    raise SystemExit("set TRITEIA_REFERENCE to a checkout of the reference")
 OUT = os.path.dirname(os.path.abspath(__file__))
 
 
