@@ -122,6 +122,9 @@ route_kernel(const RouteSrc src, int T, int D, int W, int TT, int* __restrict__ 
   for (int i = tid; i < bins * W; i += blockDim.x) hist[i] = 0;
   if (tid == 0) n_invalid = 0;
   __syncthreads();
+  // Launched with programmatic stream serialization: everything above overlaps the tail of the kernel
+  // before; the ids may come from it and the outputs may still be read by it, so wait here.
+  pdl_wait();
 
   const int piece = ((T + W - 1) / W + 31) / 32 * 32;   // tokens per warp, multiple of 32
   const int t_lo = warp * piece, t_hi = min(T, t_lo + piece);
@@ -286,9 +289,20 @@ int route_launch_src(const RouteSrc& src, int T, int D, int TT, int* perm, int* 
     if (cl.small_max < 1 || cl.tt_big < 1 || !cl.big.tile_delta || !cl.big.tile_start || !cl.big.tile_count)
       return TRB_ERR_BAD_ARG;
   }
-  route_kernel<<<1, threads, smem, stream>>>(src, T, D, W, TT, perm, seg_delta, seg_start, seg_count, tile_delta,
-                                                   tile_start, tile_count, counters, slot_of, slot_stride, bin_count, cl);
-  return cudaGetLastError() == cudaSuccess ? TRB_OK : TRB_ERR_CUDA;
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3(1);
+  lc.blockDim = dim3(threads);
+  lc.dynamicSmemBytes = smem;
+  lc.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // the kernel waits (pdl_wait) before its first global access
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = at;
+  lc.numAttrs = 1;
+  return cudaLaunchKernelEx(&lc, route_kernel, src, T, D, W, TT, perm, seg_delta, seg_start, seg_count, tile_delta,
+                            tile_start, tile_count, counters, slot_of, slot_stride, bin_count, cl) == cudaSuccess
+             ? TRB_OK
+             : TRB_ERR_CUDA;
 }
 
 int route_launch(const int* indices, int T, int D, int TT, int id_offset, int* perm, int* seg_delta, int* seg_start,
